@@ -1,0 +1,502 @@
+// Device collectives over the symmetric heap for sm_100a: sync/barrier,
+// broadcast, fcollect (allgather), alltoall, allreduce and reducescatter for
+// thread, warp, warpgroup and block scope, each usable by one CTA of a
+// multi-CTA launch on its own element slice with its own row of barrier flags.
+//
+// The fabric is flat (every peer one NVSwitch hop away, full bandwidth), so no
+// algorithm is a ring or a tree:
+//   sync        one round: store my epoch into every member's flag row, wait for theirs
+//               (dissemination with radix k only for thread/warp scope on big teams)
+//   allreduce   one-shot pull (latency), two-shot = pull-reduce my chunk + push it to all
+//               (bandwidth), NVLS one-shot / two-shot with multimem.ld_reduce / multimem.st
+//   reducescatter  pull-reduce my block, or multimem.ld_reduce of it
+//   fcollect / broadcast  push (vector stores) or multimem.st, then barrier; flag-in-data
+//               (LL) variant for small fcollect
+//   alltoall    push block p to PE p, then barrier
+// 16-bit floating types accumulate in fp32 across PEs and round once.
+// (reference behaviour: src/include/non_abi/device/coll/{barrier,reduce,reducescatter,fcollect,alltoall,broadcast}.cuh)
+#pragma once
+#include "device.cuh"
+#include "nvls.cuh"
+
+namespace bshmem {
+
+enum ReduceOp { OP_AND = 0, OP_OR = 1, OP_XOR = 2, OP_MIN = 3, OP_MAX = 4, OP_SUM = 5, OP_PROD = 6 };
+enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4 };
+enum FcollectAlgo { FC_AUTO = 0, FC_PUSH = 1, FC_LL = 2, FC_NVLS = 3 };
+enum RsAlgo { RS_AUTO = 0, RS_PULL = 1, RS_NVLS = 2 };
+enum BcastAlgo { BC_AUTO = 0, BC_PUSH = 1, BC_LL = 2, BC_NVLS = 3, BC_PULL = 4 };
+
+// ------------------------------------------------------------------ teams
+__device__ __forceinline__ const bshmemi_team_t* team_ptr(int team) {
+  if (team < 0 || team >= bshmemi_state_d.max_teams) return nullptr;
+  return ((const bshmemi_team_t*)bshmemi_state_d.team_pool) + team;
+}
+__device__ __forceinline__ int team_world_pe(const bshmemi_team_t* t, int i) {
+  return t->pe_of ? ((const int32_t*)t->pe_of)[i] : t->start + i * t->stride;
+}
+__device__ __forceinline__ int team_my_pe(int team) {
+  const bshmemi_team_t* t = team_ptr(team);
+  return t ? t->my_pe : -1;
+}
+__device__ __forceinline__ int team_n_pes(int team) {
+  const bshmemi_team_t* t = team_ptr(team);
+  return t && t->my_pe >= 0 ? t->size : -1;
+}
+__device__ __forceinline__ int team_translate_pe(int src_team, int src_pe, int dst_team) {
+  const bshmemi_team_t* s = team_ptr(src_team);
+  const bshmemi_team_t* d = team_ptr(dst_team);
+  if (!s || !d || src_pe < 0 || src_pe >= s->size) return -1;
+  const int world = team_world_pe(s, src_pe);
+  if (!d->pe_of) {
+    const int off = world - d->start;
+    if (off < 0 || off % d->stride) return -1;
+    const int idx = off / d->stride;
+    return idx < d->size ? idx : -1;
+  }
+  for (int i = 0; i < d->size; ++i)
+    if (((const int32_t*)d->pe_of)[i] == world) return i;
+  return -1;
+}
+
+// ------------------------------------------------------------------ sync / barrier
+// One-round sync.  Returns 0, or 1 if a member did not arrive within the wait bound.
+template <int SCOPE>
+__device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  group_sync<SCOPE>();
+  if (size <= 1) return 0;
+  uint64_t* epochs = (uint64_t*)t->epochs;
+  const uint64_t epoch = epochs[slot] + 1;
+  uint64_t* flags = (uint64_t*)t->sync_base + (size_t)slot * size;
+  int err = 0;
+  const int k = SCOPE == SCOPE_BLOCK || SCOPE == SCOPE_WARPGROUP || size <= 32 ? size : bshmemi_state_d.barrier_dissem_kval;
+  if (k >= size) {
+    for (int i = rank; i < size; i += G)
+      if (i != me) st_release_sys(translate(flags + me, team_world_pe(t, i)), epoch);
+    for (int i = rank; i < size; i += G)
+      if (i != me) err |= wait_ge_u64(flags + i, epoch, BSHMEM_WHERE_BARRIER);
+  } else {
+    // Radix-k dissemination: in round r talk to the PEs at distance j*k^r, j = 1..k-1.
+    // Flag index r*(k-1)+(j-1) never exceeds `size` for k >= 2.
+    int round = 0;
+    for (int dist = 1; dist < size; dist *= k, ++round) {
+      for (int j = 1 + rank; j < k; j += G) {
+        if ((long)j * dist >= size) continue;
+        const int to = (me + j * dist) % size;
+        st_release_sys(translate(flags + round * (k - 1) + (j - 1), team_world_pe(t, to)), epoch);
+      }
+      for (int j = 1 + rank; j < k; j += G) {
+        if ((long)j * dist >= size) continue;
+        err |= wait_ge_u64(flags + round * (k - 1) + (j - 1), epoch, BSHMEM_WHERE_BARRIER);
+      }
+      group_sync<SCOPE>();
+    }
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[slot] = epoch;
+  return err;
+}
+// Barrier = completion of this group's earlier puts (quiet) + sync.
+template <int SCOPE>
+__device__ __forceinline__ int team_barrier(const bshmemi_team_t* t, int slot = 0) {
+  group_sync<SCOPE>();
+  if (group_rank<SCOPE>() == 0) fence_sys();
+  return team_sync<SCOPE>(t, slot);
+}
+
+// ------------------------------------------------------------------ element arithmetic
+template <class T> struct Acc { typedef T type; };
+template <> struct Acc<__half> { typedef float type; };
+template <> struct Acc<__nv_bfloat16> { typedef float type; };
+template <class T> __device__ __forceinline__ typename Acc<T>::type to_acc(T v) { return v; }
+template <> __device__ __forceinline__ float to_acc<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_acc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <class T> __device__ __forceinline__ T from_acc(typename Acc<T>::type v) { return v; }
+template <> __device__ __forceinline__ __half from_acc<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <class A, int OP>
+__device__ __forceinline__ A combine(A a, A b) {
+  if (OP == OP_SUM) return a + b;
+  if (OP == OP_PROD) return a * b;
+  if (OP == OP_MIN) return b < a ? b : a;
+  if (OP == OP_MAX) return b > a ? b : a;
+  // Bitwise operators exist for integer types only; the dispatcher never
+  // instantiates them for floating types, the casts keep the template well formed.
+  if (OP == OP_AND) return (A)((unsigned long long)a & (unsigned long long)b);
+  if (OP == OP_OR) return (A)((unsigned long long)a | (unsigned long long)b);
+  return (A)((unsigned long long)a ^ (unsigned long long)b);
+}
+
+template <class T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
+
+// acc[] op= the N elements packed in v
+template <class T, int OP>
+__device__ __forceinline__ void accumulate(typename Acc<T>::type* acc, uint4 v, bool first) {
+  constexpr int N = VecOf<T>::N;
+  T e[N];
+  memcpy(e, &v, 16);
+#pragma unroll
+  for (int j = 0; j < N; ++j) acc[j] = first ? to_acc<T>(e[j]) : combine<typename Acc<T>::type, OP>(acc[j], to_acc<T>(e[j]));
+}
+template <class T>
+__device__ __forceinline__ uint4 pack(const typename Acc<T>::type* acc) {
+  constexpr int N = VecOf<T>::N;
+  T e[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) e[j] = from_acc<T>(acc[j]);
+  uint4 v;
+  memcpy(&v, e, 16);
+  return v;
+}
+
+// Reduces elements [lo, hi) of `src` over all members by pulling from each
+// member's copy, starting with the PE after me so that the members do not all
+// read the same peer at once.  `src_off` shifts the source (reducescatter).
+// Result goes to dst[i - lo + dst_off]; with PUSH_ALL it is stored to every
+// member's dst (two-shot second phase fused into the first).
+template <class T, int OP, int SCOPE, bool PUSH_ALL>
+__device__ __forceinline__ void pull_reduce_range(const bshmemi_team_t* t, T* dst, const T* src, size_t lo, size_t hi) {
+  typedef typename Acc<T>::type A;
+  constexpr int N = VecOf<T>::N;
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const bool vec_ok = (((uintptr_t)(src + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
+  size_t nvec = vec_ok ? (hi - lo) / N : 0;
+  for (size_t v = rank; v < nvec; v += G) {
+    const size_t i = lo + v * N;
+    A acc[N];
+    for (int s = 0; s < size; ++s) {
+      const int p = (me + 1 + s) % size;
+      const uint4 x = *(const uint4*)translate(src + i, team_world_pe(t, p));
+      accumulate<T, OP>(acc, x, s == 0);
+    }
+    const uint4 out = pack<T>(acc);
+    if (PUSH_ALL) {
+      for (int s = 0; s < size; ++s) *(uint4*)translate(dst + i, team_world_pe(t, (me + s) % size)) = out;
+    } else {
+      *(uint4*)(dst + i) = out;
+    }
+  }
+  for (size_t i = lo + nvec * N + rank; i < hi; i += G) {  // ragged tail or unaligned buffers
+    A acc = A();
+    for (int s = 0; s < size; ++s) {
+      const int p = (me + 1 + s) % size;
+      const A x = to_acc<T>(*translate(src + i, team_world_pe(t, p)));
+      acc = s == 0 ? x : combine<A, OP>(acc, x);
+    }
+    const T out = from_acc<T>(acc);
+    if (PUSH_ALL) {
+      for (int s = 0; s < size; ++s) *translate(dst + i, team_world_pe(t, (me + s) % size)) = out;
+    } else {
+      dst[i] = out;
+    }
+  }
+}
+
+// Splits [0, n) into `parts` contiguous pieces on vector boundaries.
+template <class T>
+__device__ __forceinline__ void split_range(size_t n, int parts, int which, size_t* lo, size_t* hi) {
+  constexpr size_t N = VecOf<T>::N;
+  const size_t nvec = (n + N - 1) / N;
+  const size_t per = (nvec + parts - 1) / parts;
+  size_t a = per * which * N, b = per * (which + 1) * N;
+  *lo = a < n ? a : n;
+  *hi = b < n ? b : n;
+}
+
+// ------------------------------------------------------------------ allreduce
+// `src` and `dst` are symmetric; in-place is allowed (it then uses two-shot).
+// Works on elements [lo, hi) so that CTA c of a multi-CTA launch can own a slice
+// (with slot = c).  Returns non-zero if a sync timed out.
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, const T* src, size_t lo, size_t hi, int slot, int algo) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  constexpr int N = VecOf<T>::N;
+  if (size == 1) {
+    if (dst != src) memcpy_group<SCOPE>(dst + lo, src + lo, (hi - lo) * sizeof(T));
+    group_sync<SCOPE>();
+    return 0;
+  }
+  const size_t bytes = (hi - lo) * sizeof(T);
+  const bool nvls_ok = OP == OP_SUM && MultimemSum<T>::supported && t->has_nvls && (bytes % 16) == 0 &&
+                       (((uintptr_t)(src + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
+  if (algo == RED_AUTO) algo = bshmemi_state_d.reduce_algo;
+  if (algo == RED_AUTO) {
+    if (nvls_ok) algo = ((hi - lo) <= bshmemi_state_d.reduce_nvls_threshold && dst != src) ? RED_NVLS_ONESHOT : RED_NVLS_TWOSHOT;
+    else algo = (bytes <= bshmemi_state_d.reduce_oneshot_threshold && dst != src) ? RED_ONESHOT_PULL : RED_TWOSHOT;
+  }
+  if ((algo == RED_NVLS_ONESHOT || algo == RED_NVLS_TWOSHOT) && !nvls_ok) algo = RED_TWOSHOT;
+  if ((algo == RED_ONESHOT_PULL || algo == RED_NVLS_ONESHOT) && dst == src) algo = algo == RED_NVLS_ONESHOT ? RED_NVLS_TWOSHOT : RED_TWOSHOT;
+
+  int err = team_sync<SCOPE>(t, slot);  // every member's source is ready
+  if (algo == RED_ONESHOT_PULL) {
+    pull_reduce_range<T, OP, SCOPE, false>(t, dst, src, lo, hi);
+    err |= team_sync<SCOPE>(t, slot);  // sources may be overwritten again
+  } else if (algo == RED_TWOSHOT) {
+    size_t a, b;
+    split_range<T>(hi - lo, size, me, &a, &b);
+    pull_reduce_range<T, OP, SCOPE, true>(t, dst, src, lo + a, lo + b);
+    err |= team_barrier<SCOPE>(t, slot);  // my pushes have landed, theirs too
+  } else if (algo == RED_NVLS_ONESHOT) {
+    const char* mc_src = (const char*)t->mc_base + ((uint64_t)(src + lo) - bshmemi_state_d.heap_base);
+    const size_t nvec = (hi - lo) / N;
+    for (size_t v = rank; v < nvec; v += G) ((uint4*)(dst + lo))[v] = MultimemSum<T>::ld(mc_src + v * 16);
+    err |= team_sync<SCOPE>(t, slot);
+  } else {  // NVLS two-shot: reduce my chunk in the switch, multicast the result
+    size_t a, b;
+    split_range<T>(hi - lo, size, me, &a, &b);
+    const char* mc_src = (const char*)t->mc_base + ((uint64_t)(src + lo + a) - bshmemi_state_d.heap_base);
+    char* mc_dst = (char*)t->mc_base + ((uint64_t)(dst + lo + a) - bshmemi_state_d.heap_base);
+    const size_t nvec = (b - a) / N;
+    size_t v = rank;
+    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {  // four reductions in flight per thread
+      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
+      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
+      multimem_st_v4(mc_dst + v * 16, r0);
+      multimem_st_v4(mc_dst + (v + G) * 16, r1);
+      multimem_st_v4(mc_dst + (v + 2 * (size_t)G) * 16, r2);
+      multimem_st_v4(mc_dst + (v + 3 * (size_t)G) * 16, r3);
+    }
+    for (; v < nvec; v += G) multimem_st_v4(mc_dst + v * 16, MultimemSum<T>::ld(mc_src + v * 16));
+    err |= team_barrier<SCOPE>(t, slot);
+  }
+  return err;
+}
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int allreduce(int team, T* dst, const T* src, size_t n) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  return allreduce_range<T, OP, SCOPE>(t, dst, src, 0, n, 0, RED_AUTO);
+}
+
+// ------------------------------------------------------------------ reducescatter
+// src holds size*nreduce elements, dst nreduce: dst = sum over members of their block `my_pe`.
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int reducescatter_range(const bshmemi_team_t* t, T* dst, const T* src, size_t nreduce, size_t lo, size_t hi, int slot, int algo) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  constexpr int N = VecOf<T>::N;
+  const T* my_block = src + (size_t)me * nreduce;
+  if (size == 1) {
+    memcpy_group<SCOPE>(dst + lo, my_block + lo, (hi - lo) * sizeof(T));
+    group_sync<SCOPE>();
+    return 0;
+  }
+  const size_t bytes = (hi - lo) * sizeof(T);
+  const bool nvls_ok = OP == OP_SUM && MultimemSum<T>::supported && t->has_nvls && (bytes % 16) == 0 &&
+                       (((uintptr_t)(my_block + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
+  if (algo == RS_AUTO) algo = bshmemi_state_d.reducescatter_algo;
+  if (algo == RS_AUTO) algo = nvls_ok ? RS_NVLS : RS_PULL;
+  if (algo == RS_NVLS && !nvls_ok) algo = RS_PULL;
+  int err = team_sync<SCOPE>(t, slot);
+  if (algo == RS_NVLS) {
+    const char* mc_src = (const char*)t->mc_base + ((uint64_t)(my_block + lo) - bshmemi_state_d.heap_base);
+    const size_t nvec = (hi - lo) / N;
+    size_t v = rank;
+    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {
+      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
+      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
+      ((uint4*)(dst + lo))[v] = r0;
+      ((uint4*)(dst + lo))[v + G] = r1;
+      ((uint4*)(dst + lo))[v + 2 * (size_t)G] = r2;
+      ((uint4*)(dst + lo))[v + 3 * (size_t)G] = r3;
+    }
+    for (; v < nvec; v += G) ((uint4*)(dst + lo))[v] = MultimemSum<T>::ld(mc_src + v * 16);
+  } else {
+    // dst is indexed from 0 while the source block starts at me*nreduce: shift dst.
+    pull_reduce_range<T, OP, SCOPE, false>(t, dst - (size_t)me * nreduce, src, (size_t)me * nreduce + lo, (size_t)me * nreduce + hi);
+  }
+  err |= team_sync<SCOPE>(t, slot);
+  return err;
+}
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int reducescatter(int team, T* dst, const T* src, size_t nreduce) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  return reducescatter_range<T, OP, SCOPE>(t, dst, src, nreduce, 0, nreduce, 0, RS_AUTO);
+}
+
+// ------------------------------------------------------------------ fcollect (allgather)
+// Flag-in-data packets: each 8-byte unit carries 4 bytes of payload and the
+// 4-byte generation number of this call, so arrival of the data is its own
+// signal and no barrier is needed.  Two generations of buffer alternate.
+template <int SCOPE>
+__device__ __forceinline__ int fcollect_ll(const bshmemi_team_t* t, void* dst, const void* src, size_t bytes, int slot) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS;  // collective generations live after the barrier epochs
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[slot] + 1;
+  const uint32_t flag = (uint32_t)gen;
+  const size_t words = bytes / 4;
+  const size_t half = t->ll_bytes / 2;
+  uint64_t* buf = (uint64_t*)(t->ll_base + (gen & 1) * half);  // [size][words] packets
+  const uint32_t* s32 = (const uint32_t*)src;
+  for (size_t i = rank; i < words * size; i += G) {
+    const int p = (int)(i / words);
+    const size_t w = i % words;
+    const uint64_t packet = ((uint64_t)flag << 32) | s32[w];
+    *(volatile uint64_t*)translate(buf + (size_t)me * words + w, team_world_pe(t, p)) = packet;
+  }
+  int err = 0;
+  uint32_t* d32 = (uint32_t*)dst;
+  const uint64_t start = global_timer_ns(), limit = bshmemi_state_d.wait_timeout_ns;
+  for (size_t i = rank; i < words * size; i += G) {
+    const volatile uint64_t* slot_ptr = buf + i;
+    uint64_t packet = *slot_ptr;
+    uint32_t spins = 0;
+    while ((uint32_t)(packet >> 32) != flag) {
+      packet = *slot_ptr;
+      if ((++spins & 0xff) == 0 && global_timer_ns() - start > limit) {
+        record_timeout((const void*)slot_ptr, flag, packet >> 32, BSHMEM_WHERE_COLL);
+        err = 1;
+        break;
+      }
+    }
+    d32[i] = (uint32_t)packet;
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[slot] = gen;
+  return err;
+}
+
+template <int SCOPE>
+__device__ __forceinline__ int fcollect_bytes(const bshmemi_team_t* t, void* dst, const void* src, size_t block_bytes, size_t lo, size_t hi, int slot, int algo) {
+  // Member m's block lands at dst + m*block_bytes; this call moves bytes [lo, hi) of every block.
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const size_t bytes = hi - lo;
+  if (size == 1) {
+    if (dst != src) memcpy_group<SCOPE>((char*)dst + lo, (const char*)src + lo, bytes);
+    group_sync<SCOPE>();
+    return 0;
+  }
+  const bool aligned16 = ((((uintptr_t)dst + (size_t)me * block_bytes + lo) | ((uintptr_t)src + lo) | bytes) & 15) == 0;
+  if (algo == FC_AUTO) algo = bshmemi_state_d.fcollect_algo;
+  const bool ll_ok = lo == 0 && hi == block_bytes && (bytes & 3) == 0 && ((uintptr_t)src & 3) == 0 && ((uintptr_t)dst & 3) == 0 &&
+                     2 * bytes * size <= t->ll_bytes / 2;
+  const bool nvls_ok = t->has_nvls && aligned16;
+  if (algo == FC_AUTO) {
+    if (ll_ok && bytes <= bshmemi_state_d.fcollect_ll_threshold) algo = FC_LL;
+    else if (nvls_ok && bytes * size <= bshmemi_state_d.fcollect_nvls_threshold) algo = FC_NVLS;
+    else algo = FC_PUSH;
+  }
+  if (algo == FC_LL && !ll_ok) algo = FC_PUSH;
+  if (algo == FC_NVLS && !nvls_ok) algo = FC_PUSH;
+  if (algo == FC_LL) return fcollect_ll<SCOPE>(t, dst, src, bytes, slot);
+  char* my_slot = (char*)dst + (size_t)me * block_bytes + lo;
+  if (algo == FC_NVLS) {
+    char* mc = (char*)t->mc_base + ((uint64_t)my_slot - bshmemi_state_d.heap_base);
+    const uint4* s = (const uint4*)((const char*)src + lo);
+    for (size_t v = rank; v < bytes / 16; v += G) multimem_st_v4(mc + v * 16, s[v]);
+  } else {
+    for (int sft = 0; sft < size; ++sft) {
+      const int p = (me + 1 + sft) % size;  // my own copy last
+      memcpy_group<SCOPE>(translate(my_slot, team_world_pe(t, p)), (const char*)src + lo, bytes);
+    }
+  }
+  return team_barrier<SCOPE>(t, slot);
+}
+template <class T, int SCOPE>
+__device__ __forceinline__ int fcollect(int team, T* dst, const T* src, size_t nelems) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  return fcollect_bytes<SCOPE>(t, dst, src, nelems * sizeof(T), 0, nelems * sizeof(T), 0, FC_AUTO);
+}
+
+// ------------------------------------------------------------------ alltoall
+template <int SCOPE>
+__device__ __forceinline__ int alltoall_bytes(const bshmemi_team_t* t, void* dst, const void* src, size_t block_bytes, size_t lo, size_t hi, int slot) {
+  const int size = t->size, me = t->my_pe;
+  for (int sft = 0; sft < size; ++sft) {
+    const int p = (me + 1 + sft) % size;
+    char* remote = translate((char*)dst + (size_t)me * block_bytes + lo, team_world_pe(t, p));
+    memcpy_group<SCOPE>(remote, (const char*)src + (size_t)p * block_bytes + lo, hi - lo);
+  }
+  return team_barrier<SCOPE>(t, slot);
+}
+template <class T, int SCOPE>
+__device__ __forceinline__ int alltoall(int team, T* dst, const T* src, size_t nelems) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  return alltoall_bytes<SCOPE>(t, dst, src, nelems * sizeof(T), 0, nelems * sizeof(T), 0);
+}
+
+// ------------------------------------------------------------------ broadcast
+template <int SCOPE>
+__device__ __forceinline__ int broadcast_bytes(const bshmemi_team_t* t, void* dst, const void* src, size_t lo, size_t hi, int root, int slot, int algo) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const size_t bytes = hi - lo;
+  if (algo == BC_AUTO) algo = bshmemi_state_d.bcast_algo;
+  const bool nvls_ok = t->has_nvls && ((((uintptr_t)dst + lo) | ((uintptr_t)src + lo) | bytes) & 15) == 0;
+  if (algo == BC_AUTO || algo == BC_LL) algo = nvls_ok ? BC_NVLS : BC_PUSH;
+  if (algo == BC_NVLS && !nvls_ok) algo = BC_PUSH;
+  if (algo == BC_PULL) {
+    int err = team_sync<SCOPE>(t, slot);  // the root's source is ready
+    if (me != root || dst != src) memcpy_group<SCOPE>((char*)dst + lo, translate((const char*)src + lo, team_world_pe(t, root)), bytes);
+    return err | team_sync<SCOPE>(t, slot);
+  }
+  if (me == root) {
+    if (algo == BC_NVLS) {
+      char* mc = (char*)t->mc_base + ((uint64_t)dst + lo - bshmemi_state_d.heap_base);
+      const uint4* s = (const uint4*)((const char*)src + lo);
+      for (size_t v = rank; v < bytes / 16; v += G) multimem_st_v4(mc + v * 16, s[v]);
+    } else {
+      for (int sft = 1; sft <= size; ++sft) {
+        const int p = (me + sft) % size;
+        if (p == me && dst == src) continue;
+        memcpy_group<SCOPE>(translate((char*)dst + lo, team_world_pe(t, p)), (const char*)src + lo, bytes);
+      }
+    }
+  }
+  return team_barrier<SCOPE>(t, slot);
+}
+template <class T, int SCOPE>
+__device__ __forceinline__ int broadcast(int team, T* dst, const T* src, size_t nelems, int root) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  return broadcast_bytes<SCOPE>(t, dst, src, 0, nelems * sizeof(T), root, 0, BC_AUTO);
+}
+
+// ------------------------------------------------------------------ maxloc
+// Block-wide reduction of (value, index) pairs: every member pushes its pair into
+// slot `my_pe` of each member's scratch, a barrier orders them, each member scans.
+template <int SCOPE>
+__device__ __forceinline__ int maxloc_double2(int team, double2* dst, const double2* src) {
+  const bshmemi_team_t* t = team_ptr(team);
+  if (!t || t->my_pe < 0) { report_error(BSHMEM_ERR_BAD_TEAM); return 1; }
+  const int size = t->size, me = t->my_pe;
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[0] + 1;
+  double2* slots = (double2*)(t->scratch_base + (gen & 1) * t->scratch_bytes);
+  const double2 mine = *src;
+  for (int p = group_rank<SCOPE>(); p < size; p += group_size<SCOPE>()) {
+    double2* r = translate(slots + me, team_world_pe(t, p));
+    *(volatile double*)&r->x = mine.x;
+    *(volatile double*)&r->y = mine.y;
+  }
+  int err = team_barrier<SCOPE>(t, 0);
+  if (group_rank<SCOPE>() == 0) {
+    double2 best;
+    best.x = *(volatile double*)&slots[0].x;
+    best.y = *(volatile double*)&slots[0].y;
+    for (int p = 1; p < size; ++p) {
+      double2 c;
+      c.x = *(volatile double*)&slots[p].x;
+      c.y = *(volatile double*)&slots[p].y;
+      if (c.x > best.x || (c.x == best.x && c.y < best.y)) best = c;
+    }
+    *dst = best;
+    epochs[0] = gen;
+  }
+  group_sync<SCOPE>();
+  return err;
+}
+
+}  // namespace bshmem

@@ -1,0 +1,378 @@
+#include <string.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <sstream>
+
+#include "../util/cuda_dl.h"
+#include "../util/env.h"
+#include "../util/log.h"
+#include "../util/nvtx.h"
+#include "runtime.h"
+
+namespace bshmem {
+
+Runtime& rt() {
+  static Runtime* r = new Runtime();  // never destroyed: device modules may unregister late
+  return *r;
+}
+
+bool is_initialized() { return rt().init_status >= INIT_IS_INITIALIZED; }
+
+std::string TopoRecord::describe() const {
+  std::ostringstream os;
+  os << device_count << "x " << name << " (sm_" << cc_major << cc_minor << ", " << sm_count << " SMs), PCI " << pci_bus_id
+     << ", NVLink v" << nvlink_version << " x" << nvlink_links << (nvswitch ? " via NVSwitch" : "")
+     << ", peers ld/st " << (all_peers_ldst ? "all" : "partial") << ", atomics " << (all_peers_atomics ? "all" : "partial")
+     << ", multicast " << (multicast_supported ? "yes" : "no");
+  return os.str();
+}
+
+int probe_topology(Runtime& r) {
+  TopoRecord& t = r.topo;
+  t.device = r.device;
+  cudaGetDeviceCount(&t.device_count);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, r.device) != cudaSuccess) return ST_INTERNAL;
+  t.name = prop.name;
+  t.cc_major = prop.major;
+  t.cc_minor = prop.minor;
+  t.sm_count = prop.multiProcessorCount;
+  char bus[32] = "";
+  cudaDeviceGetPCIBusId(bus, sizeof(bus), r.device);
+  t.pci_bus_id = bus;
+  t.uuid.assign((const char*)&prop.uuid, 16);
+  const CuTable* d = cu();
+  if (d) {
+    CUdevice dev;
+    if (d->cuDeviceGet_(&dev, r.device) == CUDA_SUCCESS) {
+      int v = 0;
+      d->cuDeviceGetAttribute_(&v, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev);
+      t.multicast_supported = v != 0;
+      d->cuDeviceGetAttribute_(&v, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED, dev);
+      t.vmm_supported = v != 0;
+      d->cuDeviceGetAttribute_(&v, CU_DEVICE_ATTRIBUTE_CAN_USE_64_BIT_STREAM_MEM_OPS_V1, dev);
+      t.stream_memops = v != 0;
+    }
+  }
+  NvlinkInfo nv = nvml_probe_nvlink(bus);
+  t.nvlink_links = nv.active_links;
+  t.nvlink_version = nv.link_version;
+  t.nvswitch = nv.all_links_to_switch;
+  return ST_SUCCESS;
+}
+
+// Fills `reach` for every PE from the all-gathered PeInfo: which peers this GPU
+// can load/store to and do native atomics on
+// (reference: src/host/transport/p2p/p2p.cpp, nvshmemt_p2p_can_reach_peer).
+static int build_reach_map(Runtime& r) {
+  TopoRecord& t = r.topo;
+  t.reach.assign(r.npes, 0);
+  const bool no_p2p = options().DISABLE_P2P;
+  for (int pe = 0; pe < r.npes; ++pe) {
+    const PeInfo& p = r.pe_info[pe];
+    uint8_t bits = 0;
+    if (p.host_hash == r.pe_info[r.mype].host_hash) {
+      if (memcmp(p.uuid, r.pe_info[r.mype].uuid, 16) == 0) {
+        bits = 7;  // the same GPU: plain addresses work
+      } else if (!no_p2p) {
+        // Find the local ordinal of the peer's GPU by PCI bus id.
+        int peer_dev = -1;
+        if (cudaDeviceGetByPCIBusId(&peer_dev, p.pci_bus_id) == cudaSuccess && peer_dev >= 0) {
+          int can = 0, atom = 0;
+          cudaDeviceCanAccessPeer(&can, r.device, peer_dev);
+          cudaDeviceGetP2PAttribute(&atom, cudaDevP2PAttrNativeAtomicSupported, r.device, peer_dev);
+          if (can) bits |= 1;
+          if (can && atom) bits |= 2;
+        }
+      }
+    }
+    t.reach[pe] = bits;
+    if (!(bits & 1)) t.all_peers_ldst = false;
+    if (!(bits & 2)) t.all_peers_atomics = false;
+  }
+  return ST_SUCCESS;
+}
+
+int push_device_state() {
+  Runtime& r = rt();
+  if (!r.have_gpu) return ST_SUCCESS;
+  for (auto& m : r.modules) {
+    void* addr = m.first();
+    if (!addr) continue;
+    cudaError_t e = cudaMemcpy(addr, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      ERROR_PRINT("copying the device state into module %s failed: %s", m.second.c_str(), cudaGetErrorString(e));
+      return ST_INTERNAL;
+    }
+  }
+  return ST_SUCCESS;
+}
+
+// ------------------------------------------------------------------ watchdog
+// Replaces the reference's proxy thread for a load/store-only job: it services
+// device-side nvshmem_global_exit and reports (or, when asked, acts on) device
+// wait time-outs.  Device code never spins for ever, so the watchdog never has
+// to kill the process to unblock a kernel
+// (reference: src/host/proxy/proxy.cpp, minimal proxy, progress_timeout_polling).
+static void watchdog_main(Runtime* r) {
+  pthread_setname_np(pthread_self(), "bshmem-watchdog");
+  while (!r->watchdog_stop.load()) {
+    bshmemi_status_t* s = r->status_host;
+    if (s) {
+      uint32_t bits = s->error_bits;
+      uint32_t fresh = bits & ~r->reported_errors.load();
+      if (fresh) {
+        r->reported_errors.fetch_or(fresh);
+        if (fresh & BSHMEM_ERR_WAIT_TIMEOUT)
+          ERROR_PRINT("PE %d: a device-side wait timed out (where=%u addr=%#llx expected=%llu found=%llu); the kernel returned with an error status",
+                      r->mype, s->timeout_where, (unsigned long long)s->timeout_addr, (unsigned long long)s->timeout_expected,
+                      (unsigned long long)s->timeout_found);
+        if (fresh & ~BSHMEM_ERR_WAIT_TIMEOUT & ~BSHMEM_ERR_GLOBAL_EXIT)
+          ERROR_PRINT("PE %d: device code reported error bits %#x", r->mype, fresh);
+        if ((fresh & BSHMEM_ERR_WAIT_TIMEOUT) && options().WATCHDOG_ABORT) {
+          if (r->boot_live && r->boot.global_exit) r->boot.global_exit(-1, &r->boot);
+          _exit(-1);
+        }
+      }
+      if (s->global_exit_req) {
+        int code = s->global_exit_code;
+        INFO(SUB_INIT, "PE %d: device code called nvshmem_global_exit(%d)", r->mype, code);
+        if (r->boot_live && r->boot.global_exit) r->boot.global_exit(code, &r->boot);
+        _exit(code);
+      }
+    }
+    std::this_thread::sleep_for(std::chrono::milliseconds(5));
+  }
+}
+
+void watchdog_start(Runtime& r) {
+  if (options().DISABLE_WATCHDOG) return;
+  r.watchdog_stop.store(false);
+  r.watchdog = std::thread(watchdog_main, &r);
+}
+
+void watchdog_stop(Runtime& r) {
+  r.watchdog_stop.store(true);
+  if (r.watchdog.joinable()) r.watchdog.join();
+}
+
+// ------------------------------------------------------------------ init
+static void print_options_if_asked(const Runtime& r) {
+  const Options& o = options();
+  if (o.VERSION && r.mype == 0) printf("%s version %d.%d.%d\n", BSHMEM_VENDOR_STRING, BSHMEM_MAJOR, BSHMEM_MINOR, BSHMEM_PATCH);
+  if (o.INFO && r.mype == 0) {
+    for (auto& i : options_describe(o)) {
+      if (i.cat == OptCat::Hidden && !o.INFO_HIDDEN) continue;
+      printf("%-40s %s%s\n", i.name, i.value.c_str(), i.set ? "  (set)" : "");
+    }
+  }
+}
+
+int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_hint, bool hostlib_only, int boot_mode) {
+  Runtime& r = rt();
+  if (r.init_status >= INIT_IS_INITIALIZED) return ST_SUCCESS;
+  NvtxRange nvtx(NVTX_INIT, "nvshmem_init");
+  std::vector<std::string> bad;
+  Options tmp;
+  if (options_init(&tmp, &bad) != 0) {
+    for (auto& b : bad) ERROR_PRINT("invalid value in environment: %s", b.c_str());
+    return ST_INVALID_VALUE;
+  }
+  options_reload();
+  log_init();
+  nvtx_init();
+  const Options& o = options();
+  r.hostlib_only = hostlib_only;
+
+  int st = bootstrap_init(boot_mode, id, rank, nranks, &r.boot);
+  if (st != BOOT_OK) {
+    ERROR_PRINT("bootstrap failed: %s", bootstrap_strerror(st));
+    return ST_INTERNAL;
+  }
+  r.boot_live = true;
+  r.mype = r.boot.pg_rank;
+  r.npes = r.boot.pg_size;
+  r.mype_node = r.boot.mype_node;
+  r.npes_node = r.boot.npes_node;
+  r.init_status = INIT_IS_BOOTSTRAPPED;
+  log_set_pe(r.mype);
+  print_options_if_asked(r);
+
+  // ---- which back end
+  int ndev = 0;
+  bool gpu = cu() != nullptr && cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0;
+  std::string be = o.HEAP_BACKEND;
+  std::transform(be.begin(), be.end(), be.begin(), ::toupper);
+  bool use_vmm = be == "VMM" || (be == "AUTO" && gpu && !o.DISABLE_CUDA_VMM);
+  if (use_vmm && !gpu) {
+    ERROR_PRINT("NVSHMEM_HEAP_BACKEND=VMM needs a CUDA device");
+    return ST_GPU_NOT_SELECTED;
+  }
+  r.have_gpu = use_vmm;
+  if (use_vmm) {
+    if (device_hint >= 0) r.device = device_hint;
+    else if (cudaGetDevice(&r.device) != cudaSuccess) r.device = 0;
+    if (cudaSetDevice(r.device) != cudaSuccess || cudaFree(nullptr) != cudaSuccess) {
+      ERROR_PRINT("cannot select CUDA device %d", r.device);
+      return ST_GPU_NOT_SELECTED;
+    }
+    log_set_device(r.device);
+    if (probe_topology(r) != ST_SUCCESS) return ST_INTERNAL;
+  }
+
+  // ---- who is where
+  PeInfo mine{};
+  mine.pid = (int32_t)getpid();
+  mine.device = r.device;
+  mine.host_hash = host_hash();
+  strncpy(mine.pci_bus_id, r.topo.pci_bus_id.c_str(), sizeof(mine.pci_bus_id) - 1);
+  if (r.topo.uuid.size() == 16) memcpy(mine.uuid, r.topo.uuid.data(), 16);
+  else snprintf(mine.uuid, sizeof(mine.uuid), "host-%d", r.mype);
+  r.pe_info.resize(r.npes);
+  if (r.boot.allgather(&mine, r.pe_info.data(), sizeof(PeInfo), &r.boot) != 0) return ST_INTERNAL;
+  if (use_vmm) {
+    build_reach_map(r);
+    if (!r.topo.all_peers_ldst) {
+      ERROR_PRINT("PE %d cannot load/store to every peer; only NVLink/NVSwitch-connected jobs on one node are supported (no remote transport is built)", r.mype);
+      return ST_NOT_SUPPORTED;
+    }
+    INFO(SUB_TOPO, "topology: %s", r.topo.describe().c_str());
+  }
+
+  // ---- heap
+  size_t stride = o.MAX_MEMORY_PER_GPU, initial = o.SYMMETRIC_SIZE, gran = o.CUMEM_GRANULARITY;
+  if (use_vmm) {
+    r.heap = make_vmm_heap(!o.DISABLE_NVLS);
+  } else {
+    r.heap = make_host_heap();
+    if (!o.CUMEM_GRANULARITY_set) gran = (size_t)1 << 20;
+    if (!o.MAX_MEMORY_PER_GPU_set) stride = std::max<size_t>((size_t)4 << 30, initial * 4);
+  }
+  st = r.heap->init(&r.boot, r.device, stride, initial, gran);
+  if (st != HEAP_OK) {
+    ERROR_PRINT("symmetric heap (%s) initialisation failed with status %d", r.heap->kind(), st);
+    return st == HEAP_ERR_OOM ? ST_OUT_OF_MEMORY : ST_INTERNAL;
+  }
+
+  // ---- status block + device state
+  if (use_vmm) {
+    if (cudaHostAlloc((void**)&r.status_host, sizeof(bshmemi_status_t), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return ST_OUT_OF_MEMORY;
+    memset((void*)r.status_host, 0, sizeof(bshmemi_status_t));
+    void* dptr = nullptr;
+    cudaHostGetDevicePointer(&dptr, r.status_host, 0);
+    r.dstate.status = (uint64_t)dptr;
+    int least = 0, greatest = 0;
+    cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    cudaStreamCreateWithPriority(&r.stream, cudaStreamNonBlocking, greatest);
+    r.peer_streams.resize(std::min(r.npes, 8));
+    for (auto& s : r.peer_streams) cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    r.peer_stream_used.assign(r.peer_streams.size(), false);
+    cudaEventCreateWithFlags(&r.ev_a, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&r.ev_b, cudaEventDisableTiming);
+  } else {
+    r.status_host = new bshmemi_status_t();
+    memset((void*)r.status_host, 0, sizeof(bshmemi_status_t));
+    r.dstate.status = (uint64_t)r.status_host;
+  }
+  bshmemi_state_t& d = r.dstate;
+  d.version = (BSHMEM_MAJOR << 16) | (BSHMEM_MINOR << 8) | BSHMEM_PATCH;
+  d.mype = r.mype;
+  d.npes = r.npes;
+  d.mype_node = r.mype_node;
+  d.npes_node = r.npes_node;
+  d.max_teams = r.max_teams = (int)std::max<long>(o.MAX_TEAMS, 8);
+  d.job_connectivity = !use_vmm ? BSHMEM_JOB_HOST_ONLY : (r.topo.all_peers_atomics ? BSHMEM_JOB_GPU_LDST_ATOMICS : BSHMEM_JOB_GPU_LDST);
+  d.heap_base = (uint64_t)r.heap->base();
+  d.heap_stride = r.heap->stride();
+  d.heap_size = r.heap->backed();
+  d.mc_base = (uint64_t)r.heap->mc_base();
+  d.nvls_world = r.heap->mc_base() != nullptr;
+  d.wait_timeout_ns = (uint64_t)o.WAIT_TIMEOUT_MS * 1000000ull;
+  d.reduce_algo = (int)o.REDUCE_ALGO;
+  d.fcollect_algo = (int)o.FCOLLECT_ALGO;
+  d.reducescatter_algo = (int)o.REDUCESCATTER_ALGO;
+  d.bcast_algo = (int)o.BCAST_ALGO;
+  d.barrier_dissem_kval = (int)std::max<long>(o.BARRIER_DISSEM_KVAL, 2);
+  d.barrier_tg_dissem_kval = (int)std::max<long>(o.BARRIER_TG_DISSEM_KVAL, 2);
+  d.bcast_tree_kval = (int)std::max<long>(o.BCAST_TREE_KVAL, 2);
+  d.debug_checks = o.ENABLE_ERROR_CHECKS;
+  d.reduce_nvls_threshold = o.REDUCE_NVLS_THRESHOLD;
+  d.reduce_oneshot_threshold = o.REDUCE_ONESHOT_THRESHOLD;
+  d.fcollect_ll_threshold = o.FCOLLECT_LL_THRESHOLD;
+  d.fcollect_nvls_threshold = o.FCOLLECT_NVLS_THRESHOLD;
+  d.reducescatter_nvls_threshold = o.REDUCESCATTER_NVLS_THRESHOLD;
+
+  // ---- teams (first symmetric allocation), then publish the state
+  st = teams_init(r);
+  if (st != ST_SUCCESS) return st;
+  d.heap_size = r.heap->backed();
+  st = push_device_state();
+  if (st != ST_SUCCESS) return st;
+  watchdog_start(r);
+  r.init_status = INIT_IS_INITIALIZED;
+  if (r.boot.barrier(&r.boot) != 0) return ST_INTERNAL;
+  st = host_barrier_all_blocking();  // first cross-GPU traffic: proves the mappings
+  if (st != ST_SUCCESS) return st;
+  INFO(SUB_INIT, "PE %d of %d initialised: heap %s, %zu bytes backed, NVLS %s", r.mype, r.npes, r.heap->kind(), r.heap->backed(),
+       d.nvls_world ? "on" : "off");
+  return ST_SUCCESS;
+}
+
+int runtime_finalize() {
+  Runtime& r = rt();
+  if (r.init_status < INIT_IS_BOOTSTRAPPED) return ST_SUCCESS;
+  NvtxRange nvtx(NVTX_INIT, "nvshmem_finalize");
+  if (r.init_status >= INIT_IS_INITIALIZED) {
+    if (r.have_gpu) cudaDeviceSynchronize();
+    host_barrier_all_blocking();
+    if (log_enabled(LOG_INFO, SUB_INIT))
+      INFO(SUB_INIT, "PE %d counters: put %llu (%llu B) get %llu (%llu B) signal %llu coll %llu barrier %llu alloc %llu", r.mype,
+           (unsigned long long)r.n_put, (unsigned long long)r.bytes_put, (unsigned long long)r.n_get, (unsigned long long)r.bytes_get,
+           (unsigned long long)r.n_signal, (unsigned long long)r.n_coll, (unsigned long long)r.n_barrier, (unsigned long long)r.n_alloc);
+  }
+  watchdog_stop(r);
+  teams_finalize(r);
+  if (r.have_gpu) {
+    cudaDeviceSynchronize();
+    if (r.stream) cudaStreamDestroy(r.stream);
+    for (auto s : r.peer_streams) cudaStreamDestroy(s);
+    r.peer_streams.clear();
+    if (r.ev_a) cudaEventDestroy(r.ev_a);
+    if (r.ev_b) cudaEventDestroy(r.ev_b);
+    r.stream = nullptr;
+    r.ev_a = r.ev_b = nullptr;
+  }
+  if (r.heap) {
+    r.heap->finalize();
+    r.heap.reset();
+  }
+  if (r.status_host) {
+    if (r.have_gpu) cudaFreeHost((void*)r.status_host);
+    else delete r.status_host;
+    r.status_host = nullptr;
+  }
+  if (r.boot_live) {
+    r.boot.barrier(&r.boot);
+    r.boot.finalize(&r.boot);
+    r.boot_live = false;
+  }
+  r.init_status = INIT_NOT_INITIALIZED;
+  r.reported_errors.store(0);
+  memset(&r.dstate, 0, sizeof(r.dstate));
+  return ST_SUCCESS;
+}
+
+}  // namespace bshmem
+
+extern "C" void bshmemi_register_module(void* (*getter)(), const char* name) {
+  bshmem::Runtime& r = bshmem::rt();
+  for (auto& m : r.modules)
+    if (m.first == getter) return;
+  r.modules.emplace_back(getter, name ? name : "?");
+  if (r.init_status >= bshmem::INIT_IS_INITIALIZED && r.have_gpu) {
+    void* addr = getter();
+    if (addr) cudaMemcpy(addr, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice);
+  }
+}

@@ -1,0 +1,124 @@
+"""In-tree build of the native libraries with nvcc, for sm_100a only.
+
+Targets (all land in ``nvshmem_b200/lib``):
+
+* ``libbshmem_host.so``   – host library: bootstrap, heap, teams, host API, on-stream collectives
+* ``libbshmem_fused.so``  – fused tcgen05 GEMM + collective kernels and the MoE dispatch/combine kernels
+* ``libbshmem_devtest.so``– kernels that exercise the device API (used by the test-suite and perftest)
+* ``nvshmem-info``        – prints version, build options and environment variables
+
+Objects are rebuilt when a source or any header is newer.  ``python -m
+nvshmem_b200.utils.build`` builds everything; ``--verbose`` adds ``-Xptxas -v``.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+CSRC = ROOT / "csrc"
+LIB = ROOT / "nvshmem_b200" / "lib"
+OBJ = ROOT / "build" / "obj"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function",
+          "-I", str(CSRC / "include"), "-I", str(CSRC / "src")]
+
+
+def nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found")
+    return exe
+
+
+def _headers_mtime() -> float:
+    newest = 0.0
+    for pat in ("**/*.h", "**/*.cuh", "**/*.hpp"):
+        for p in CSRC.glob(pat):
+            newest = max(newest, p.stat().st_mtime)
+    return newest
+
+
+def _compile(src: Path, extra: list[str], verbose: bool, hdr_mtime: float) -> Path:
+    rel = src.relative_to(CSRC)
+    obj = OBJ / (str(rel).replace("/", "__") + ".o")
+    obj.parent.mkdir(parents=True, exist_ok=True)
+    if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
+        return obj
+    cmd = [nvcc(), "-c", str(src), "-o", str(obj)] + COMMON + extra
+    if src.suffix == ".cu":
+        cmd += ARCH_FLAGS
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {rel}:\n{res.stdout}\n{res.stderr}")
+    if verbose and res.stderr:
+        sys.stderr.write(f"--- {rel}\n{res.stderr}\n")
+    elif res.stderr.strip():
+        # keep warnings visible but short
+        lines = [l for l in res.stderr.splitlines() if "warning" in l.lower()]
+        if lines:
+            sys.stderr.write(f"--- {rel}: {len(lines)} warning(s)\n")
+    return obj
+
+
+def _link(objs: list[Path], out: Path, shared: bool, libs: list[str]) -> None:
+    out.parent.mkdir(parents=True, exist_ok=True)
+    if out.exists() and all(out.stat().st_mtime > o.stat().st_mtime for o in objs):
+        return
+    cmd = [nvcc(), "-o", str(out)] + [str(o) for o in objs] + ARCH_FLAGS + libs
+    if shared:
+        cmd += ["-shared"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link of {out.name} failed:\n{res.stdout}\n{res.stderr}")
+
+
+def _sources(*dirs: str) -> list[Path]:
+    out: list[Path] = []
+    for d in dirs:
+        out += sorted((CSRC / "src" / d).glob("*.cpp")) + sorted((CSRC / "src" / d).glob("*.cu"))
+    return out
+
+
+def build_all(verbose: bool = False, jobs: int | None = None, only: str | None = None) -> dict[str, Path]:
+    """Builds every native target and returns their paths."""
+    hdr = _headers_mtime()
+    jobs = jobs or min(8, os.cpu_count() or 4)
+    groups = {
+        "host": (_sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), LIB / "libbshmem_host.so", True, ["-ldl", "-lpthread", "-lrt"]),
+        "fused": (_sources("fused"), LIB / "libbshmem_fused.so", True, ["-ldl"]),
+        "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
+        "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
+    }
+    built: dict[str, Path] = {}
+    for name, (srcs, out, shared, libs) in groups.items():
+        if only and name != only:
+            continue
+        if not srcs:
+            continue
+        with ThreadPoolExecutor(jobs) as ex:
+            objs = list(ex.map(lambda s: _compile(s, [], verbose, hdr), srcs))
+        _link(objs, out, shared, libs)
+        built[name] = out
+    return built
+
+
+def main() -> None:
+    verbose = "--verbose" in sys.argv
+    only = None
+    for a in sys.argv[1:]:
+        if a.startswith("--only="):
+            only = a.split("=", 1)[1]
+    for name, path in build_all(verbose=verbose, only=only).items():
+        print(f"{name}: {path}")
+
+
+if __name__ == "__main__":
+    main()
