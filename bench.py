@@ -1,0 +1,246 @@
+#!/usr/bin/env python
+"""Headline benchmark: row-parallel GEMM fused with reduce-scatter (config (d) of the work list).
+
+Per rank: x[M=8192, K=3584] @ w[N=8192, K=3584]^T in bf16 with fp32 accumulation, summed over the
+ranks and scattered by rows (weak scaling: the K-slice per rank is fixed, so per-GPU work is
+constant).  The metric is the whole-job TFLOP/s = n_gpus * 2*M*N*K / step time.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+For N > 1 launch with torchrun (one rank per GPU); rank 0 prints one JSON line.
+Timing: CUDA events on the launching stream around exactly K steps, barrier +
+synchronize on both sides, max over ranks.  Inputs rotate through several
+buffer sets whose total size exceeds the 126 MB L2.  SM clocks and throttle
+reasons are sampled with nvidia-smi during the timed region.
+
+The `e2e` number drives the same step through the public Python API with the
+activations of every step coming from pinned host memory (copy overlapped on a
+second stream) and a checksum of the result read back to the host every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+M, N, K_LOCAL = 8192, 8192, 3584
+BASELINE_VALUE = None  # the reference publishes no number for this metric
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sets", type=int, default=3, help="input buffer sets rotated between steps")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clock, power and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """Runs the unmodified reference build (baseline/_ref) for the same metric: cuBLAS GEMM
+    (torch.matmul) followed by the reference library's own bf16 sum reducescatter on the stream."""
+    from baseline import reference_bench
+    return reference_bench.run(args, M, N, K_LOCAL)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        try:
+            line = reference_arm(args)
+        except Exception as e:  # the reference arm must never take the driver down
+            line = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import nvshmem_b200.core as nv
+    from nvshmem_b200.ops import fused_gemm as fg
+
+    if world > 1:
+        nv.init(device=local_rank, initializer_method="torch")
+    else:
+        nv.init(device=local_rank, uid=nv.get_unique_id(), rank=0, nranks=1)
+
+    torch.manual_seed(1234 + rank)
+    sets = max(1, args.sets)
+    xs = [torch.randn(M, K_LOCAL, device=dev, dtype=torch.float32).mul_(1.0).to(torch.bfloat16) for _ in range(sets)]
+    ws = [torch.randn(N, K_LOCAL, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16) for _ in range(sets)]
+    op = fg.GemmReduceScatter(M, N, mode="rs")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-timed kernel path
+    for i in range(max(3, args.warmup)):
+        op(xs[i % sets], ws[i % sets])
+    barrier()
+    fg.check_errors(dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(args.steps):
+        op(xs[i % sets], ws[i % sets])
+    end.record()
+    barrier()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop()
+    fg.check_errors(dev)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    flops_per_rank = 2.0 * M * N * K_LOCAL
+    value = world * flops_per_rank / (ms_per_step * 1e-3) / 1e12
+
+    # ---------------- end to end: pinned host input every step, checksum read back every step
+    host_x = [torch.randn(M, K_LOCAL, dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty(M, K_LOCAL, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    main_stream = torch.cuda.current_stream()
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_steps(n):
+        # Step i's input is copied on the copy stream while step i-1 computes.
+        with torch.cuda.stream(copy_stream):
+            dev_x[0].copy_(host_x[0], non_blocking=True)
+            copied[0].record(copy_stream)
+        for i in range(n):
+            cur, nxt = i & 1, (i + 1) & 1
+            if i + 1 < n:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(consumed[nxt])
+                    dev_x[nxt].copy_(host_x[nxt], non_blocking=True)
+                    copied[nxt].record(copy_stream)
+            main_stream.wait_event(copied[cur])
+            out = op(dev_x[cur], ws[i % sets])
+            consumed[cur].record(main_stream)
+            host_out.copy_(out.float().sum().reshape(1), non_blocking=True)
+            main_stream.synchronize()  # the result of every step reaches the host
+        return float(host_out.item())
+
+    e2e_steps(3)
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_steps(args.steps)
+    t1.record()
+    barrier()
+    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms_per_step = float(e2e_ms.item()) / args.steps
+    e2e_value = world * flops_per_rank / (e2e_ms_per_step * 1e-3) / 1e12
+    fg.check_errors(dev)
+
+    line = {
+        "metric": "fused_gemm_reduce_scatter_tflops",
+        "value": round(value, 2),
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None,
+        "dtype": "bf16",
+        "data": "synthetic (seeded randn activations, N(0,0.02) weights, random init)",
+        "impl": "ours",
+        "config": {"model": "tp_row_parallel_gemm_reduce_scatter", "M": M, "N": N, "K_per_rank": K_LOCAL, "global_batch": M, "seq_len": 1,
+                   "parallelism": f"tp{world}", "l2": f"inputs rotate over {sets} buffer sets ({sets * (M + N) * K_LOCAL * 2 >> 20} MiB > 126 MiB L2)"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms_per_step, 5), "h2d_bytes_per_step": M * K_LOCAL * 2,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": args.steps,  # one fused tcgen05 kernel per step (libbshmem_fused.so)
+    }
+    op.close()
+    nv.finalize()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

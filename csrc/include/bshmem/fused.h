@@ -1,0 +1,59 @@
+// C interface of the fused GEMM + collective kernels (libbshmem_fused.so).
+// The library is self-contained: it takes raw device pointers (local ones and,
+// for the collective modes, the peers' mapped addresses of the same symmetric
+// buffers) and a stream, and allocates nothing.
+#pragma once
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSHMEM_FUSED_MAX_PES 8
+
+enum { BSHMEM_FUSED_PLAIN = 0, BSHMEM_FUSED_RS = 1, BSHMEM_FUSED_AR = 2, BSHMEM_FUSED_AG = 3 };
+enum {
+  BSHMEM_FUSED_OK = 0,
+  BSHMEM_FUSED_ERR_ARGS = 1,
+  BSHMEM_FUSED_ERR_SHAPE = 2,      /* M % (128*npes), N % 256 or K % 64 is not zero */
+  BSHMEM_FUSED_ERR_ALIGNMENT = 3,  /* a base address or row pitch is not 16-byte aligned */
+  BSHMEM_FUSED_ERR_DRIVER = 4
+};
+
+typedef struct {
+  /* C[M,N] = A[M,K] * B[N,K]^T, all bf16 row-major.
+   * PLAIN: A, B, out local.
+   * RS   : every PE holds a K-slice; out is this PE's [M/npes, N] block of the sum over PEs.
+   * AR   : as RS, but out is the full [M, N] sum on every PE (out_peer[] = each PE's out).
+   * AG   : A is this PE's gathered [M, K] buffer (symmetric); rows [rank*M/npes, …) hold this PE's shard on
+   *        entry and the kernel fills the peers' copies (ag_peer[] = each PE's gathered buffer). */
+  const void* A;
+  const void* B;
+  void* out;
+  int M, N, K;
+  int rank, npes, mode;
+  uint64_t epoch;            /* call counter of this buffer set, starting at 1, identical on all PEs */
+  uint32_t wait_limit_ms;    /* bound of every in-kernel wait; 0 = 10 s */
+  int max_ctas;              /* 0 = one per SM */
+  int n_comm;                /* AG: CTAs that only send (0 = 16) */
+  int* error_flag;           /* device int, OR-ed with 1 (GEMM CTA gave up) / 2 (sender gave up) */
+  /* RS / AR */
+  void* recv_local;                           /* [npes][M/npes][N] bf16 receive slots (pick the half of this call's parity) */
+  void* recv_peer[BSHMEM_FUSED_MAX_PES];      /* the same buffer on each PE */
+  uint64_t* flags_local;                      /* [npes][(M/npes/128)*(N/256)] */
+  uint64_t* flags_peer[BSHMEM_FUSED_MAX_PES];
+  void* out_peer[BSHMEM_FUSED_MAX_PES];       /* AR only */
+  /* AG */
+  void* ag_peer[BSHMEM_FUSED_MAX_PES];
+  uint64_t* ag_flags_local;                   /* [npes][M/npes/128] arrival counters */
+  uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
+} bshmem_fused_args_t;
+
+/* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */
+int bshmem_fused_gemm(const bshmem_fused_args_t* args, cudaStream_t stream);
+int bshmem_fused_gemm_smem_bytes(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -261,7 +261,8 @@ uint32_t nvshmemx_b200_timeout_info(bshmemi_status_t* out);
 void nvshmemx_b200_set_wait_timeout_ms(long ms);
 /* One-line description of the probed topology, valid until the next call. */
 const char* nvshmemx_b200_topology(void);
-/* Heap facts: 0 base of the local window, 1 stride, 2 backed bytes, 3 multicast base, 4 chunks, 5 bytes in use. */
+/* Heap facts: 0 base of the local window, 1 stride, 2 backed bytes, 3 multicast base, 4 chunks, 5 bytes in use,
+ * 6 digest of the allocation history, 7 whether the heap is GPU memory. */
 uint64_t nvshmemx_b200_heap_info(int what);
 /* Explicit algorithm choice for benchmarks (0 = automatic). */
 int nvshmemx_b200_reduce_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t n, int dtype, int op, int algo, cudaStream_t s);

@@ -1,0 +1,491 @@
+// Fused tensor-parallel GEMM + collective for sm_100a, hand-written on
+// tcgen05 / tensor memory / TMA.
+//
+//   C[M,N] = A[M,K] · B[N,K]^T      A, B, C bf16 (both operands K-major), fp32 accumulation in TMEM
+//
+// One persistent CTA per SM, 256 threads, warp-specialised:
+//   warp 0    TMA producer   4-stage ring of {A 128x64, B 256x64} tiles (128-byte swizzle)
+//   warp 1    MMA issuer     one thread issues tcgen05.mma 128x256x16, accumulators double-buffered in TMEM (2 x 256 columns)
+//   warp 2    TMEM allocator
+//   warps 4-7 epilogue       tcgen05.ld -> fp32 registers -> (+ peers' partial tiles) -> bf16 -> swizzled smem -> TMA store
+// and the collective rides on the epilogue, tile by tile, over peer memory:
+//   MODE_RS  row-parallel GEMM -> reduce-scatter.  Tiles whose rows belong to another PE are computed first
+//            (nearest destination first, so that each PE feeds a different peer at any time) and TMA-stored as
+//            bf16 partials straight into that PE's receive slot, followed by a release flag per tile.  The PE's own
+//            rows come last: their epilogue waits for the seven flags of the tile and adds the seven partials to
+//            the TMEM accumulator before the single rounding to bf16.  No separate reduction pass exists.
+//   MODE_AR  same, but the finished tile is TMA-stored into every PE's output (allreduce).
+//   MODE_AG  all-gather -> column-parallel GEMM.  A few extra CTAs push this PE's activation shard into every
+//            peer's gathered buffer with bulk copies (nearest peer first) and bump a counter per 128-row block;
+//            the producer warp consumes shards in arrival order (own, then rank-1, rank-2, …) and only waits when a
+//            block has not landed.  Remote data is always read from this GPU's own memory.
+//   MODE_PLAIN  no collective (also what 1 PE runs).
+// Every wait (mbarrier, flag) is bounded; on expiry the CTA unwinds, frees its tensor memory and sets `error_flag`.
+// No load uses a cluster-wide broadcast form, so the same binary runs on any number of GPUs.
+// (reference for the capability: examples/gemm_allreduce/*, which fuses a CUTLASS GEMM with an NVLS allreduce)
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "../../include/bshmem/fused.h"
+#include "../../include/bshmem/tcgen05.cuh"
+
+namespace bshmem {
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2;
+constexpr int EPI_COLS = 64, EPI_BUF = BM * EPI_COLS * 2, EPI_BUFS = 2;
+constexpr int TMEM_COLS = 512, ACC_COLS = BN;
+constexpr int NTHREADS = 256, EPI_THREADS = 128, EPI_WARP0 = 4;
+constexpr int COMM_PIECE = 16384, COMM_BUFS = 8, COMM_AHEAD = 4;
+constexpr int SMEM_TILES = STAGES * (A_STAGE + B_STAGE) + EPI_BUFS * EPI_BUF;
+constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+static_assert(COMM_PIECE * COMM_BUFS <= SMEM_TILES, "the sender's ring must fit in the GEMM's shared memory");
+
+struct alignas(64) FusedParams {
+  CUtensorMap tmA, tmB;
+  CUtensorMap tmOut[BSHMEM_FUSED_MAX_PES];   // PLAIN/RS/AG: [0] is the local output; AR: output of each PE
+  CUtensorMap tmRecv[BSHMEM_FUSED_MAX_PES];  // RS/AR: my slot in the receive buffer of each PE
+  const __nv_bfloat16* recv_local;           // [npes][M/npes][N] partials received from each PE
+  uint64_t* flags_local;                     // [npes][tiles per PE]
+  uint64_t* flags_peer[BSHMEM_FUSED_MAX_PES];
+  const char* ag_src;                        // my shard inside my gathered buffer
+  char* ag_dst[BSHMEM_FUSED_MAX_PES];        // the same shard inside each PE's gathered buffer
+  uint64_t* ag_flags_local;                  // [npes][m-tiles per shard]
+  uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
+  int* error_flag;
+  uint64_t epoch, wait_limit_ns, ag_unit_bytes;
+  int M, N, K, rank, npes, mode, n_comm, ag_parts, ag_tiles_per_unit;
+};
+
+struct TileInfo {
+  int m_tile, n_tile;   // position in the full output
+  int peer;             // RS/AR: PE that owns the rows; AG: PE whose shard holds the rows
+  int m_local;          // m-tile index inside that PE's block of rows
+  int idx_in_peer;      // tile number inside the block (flag index)
+};
+
+// Tile order.  Blocks of rows are visited peer by peer (RS/AR: rank+1, rank+2, …, own last; AG: own, rank-1, …);
+// inside a block m runs fastest so that concurrently running CTAs share B tiles through L2.
+__device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
+  const int tiles_n = p.N / BN;
+  const int tmr = (p.M / p.npes) / BM;
+  const int per_peer = tmr * tiles_n;
+  const int o = t / per_peer, within = t % per_peer;
+  TileInfo ti;
+  if (p.mode == BSHMEM_FUSED_AG) ti.peer = (p.rank - o + p.npes) % p.npes;
+  else ti.peer = (p.rank + 1 + o) % p.npes;
+  ti.m_local = within % tmr;
+  ti.n_tile = within / tmr;
+  ti.m_tile = ti.peer * tmr + ti.m_local;
+  ti.idx_in_peer = within;
+  return ti;
+}
+
+__device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t want, uint64_t limit_ns, volatile int* abort_flag) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+  if (v >= want) return true;
+  const uint64_t start = timer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= want) return true;
+    if ((++spins & 31) == 0) {
+      if (*abort_flag) return false;
+      if (timer_ns() - start > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ all-gather sender (MODE_AG, extra CTAs)
+__device__ void ag_sender(const FusedParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  if (threadIdx.x != 0) return;
+  const int unit = blockIdx.x;  // one unit of my shard per sender CTA
+  const size_t unit_off = (size_t)unit * p.ag_unit_bytes;
+  const int pieces = (int)(p.ag_unit_bytes / COMM_PIECE);
+  const int tmr = (p.M / p.npes) / BM;
+  uint32_t phase_bits = 0;  // one parity bit per ring slot
+  for (int o = 1; o < p.npes && !*abort_flag; ++o) {
+    const int peer = (p.rank + o) % p.npes;
+    const char* src = p.ag_src + unit_off;
+    char* dst = p.ag_dst[peer] + unit_off;
+    const int ahead = pieces < COMM_AHEAD ? pieces : COMM_AHEAD;
+    for (int q = 0; q < ahead; ++q) {
+      mbar_expect_tx(&bars[q % COMM_BUFS], COMM_PIECE);
+      bulk_load(smem + (q % COMM_BUFS) * COMM_PIECE, src + (size_t)q * COMM_PIECE, COMM_PIECE, &bars[q % COMM_BUFS]);
+    }
+    for (int q = 0; q < pieces; ++q) {
+      const int nxt = q + COMM_AHEAD;
+      if (nxt < pieces) {
+        // Ring slot of piece `nxt` was last used by piece nxt-COMM_BUFS, stored COMM_BUFS-COMM_AHEAD iterations ago.
+        bulk_wait_read<COMM_BUFS - COMM_AHEAD - 1>();
+        mbar_expect_tx(&bars[nxt % COMM_BUFS], COMM_PIECE);
+        bulk_load(smem + (nxt % COMM_BUFS) * COMM_PIECE, src + (size_t)nxt * COMM_PIECE, COMM_PIECE, &bars[nxt % COMM_BUFS]);
+      }
+      const int slot = q % COMM_BUFS;
+      if (!mbar_wait(&bars[slot], (phase_bits >> slot) & 1, p.wait_limit_ns, abort_flag)) break;
+      phase_bits ^= 1u << slot;
+      bulk_store(dst + (size_t)q * COMM_PIECE, smem + slot * COMM_PIECE, COMM_PIECE);
+      bulk_commit();
+    }
+    bulk_wait<0>();  // every byte of the unit has been written to the peer
+    fence_proxy_async_all();
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    // Tell the peer which 128-row blocks are (partly) complete.
+    const int first_tile = p.ag_parts > 1 ? unit / p.ag_parts : unit * p.ag_tiles_per_unit;
+    const int ntiles = p.ag_parts > 1 ? 1 : p.ag_tiles_per_unit;
+    for (int j = 0; j < ntiles; ++j) {
+      uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + first_tile + j;
+      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)1) : "memory");
+    }
+  }
+  bulk_wait<0>();
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_constant__ FusedParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE;
+  uint8_t* sE = sB + STAGES * B_STAGE;
+  uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
+  uint64_t* full = bars;                    // [STAGES]  (the sender CTAs use [0, COMM_BUFS) of the same array)
+  uint64_t* empty = bars + STAGES;          // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_sender = p.mode == BSHMEM_FUSED_AG && (int)blockIdx.x < p.n_comm;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if (is_sender) {
+      for (int i = 0; i < COMM_BUFS; ++i) mbar_init(&bars[i], 1);
+    } else {
+      for (int i = 0; i < STAGES; ++i) {
+        mbar_init(&full[i], 1);
+        mbar_init(&empty[i], 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&acc_full[i], 1);
+        mbar_init(&acc_empty[i], EPI_THREADS);
+      }
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (is_sender) {
+    __syncthreads();
+    ag_sender(p, smem, bars, abort_flag);
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 2);
+    return;
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_n = p.N / BN;
+  const int total_tiles = (p.M / BM) * tiles_n;
+  const int kblocks = p.K / BK;
+  const int first = (int)blockIdx.x - (p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0);
+  const int step = (int)gridDim.x - (p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0);
+  const int tmr = (p.M / p.npes) / BM;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&p.tmA);
+      tma_prefetch_desc(&p.tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = first; t < total_tiles && !*abort_flag; t += step) {
+        const TileInfo ti = tile_info(p, t);
+        if (p.mode == BSHMEM_FUSED_AG && ti.peer != p.rank) {
+          // The 128 rows of this tile arrive from `peer`; all of K comes with them.
+          if (!wait_flag_ge(p.ag_flags_local + (size_t)ti.peer * tmr + ti.m_local, p.epoch * (uint64_t)p.ag_parts, p.wait_limit_ns, abort_flag)) break;
+          fence_proxy_async_all();  // peer-written data (generic proxy) before my TMA reads (async proxy)
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, p.wait_limit_ns, abort_flag)) break;
+          mbar_expect_tx(&full[stage], A_STAGE + B_STAGE);
+          tma_load_2d(sA + stage * A_STAGE, &p.tmA, &full[stage], kb * BK, ti.m_tile * BM);
+          tma_load_2d(sB + stage * B_STAGE, &p.tmB, &full[stage], kb * BK, ti.n_tile * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int t = first; t < total_tiles && !*abort_flag; t += step) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.wait_limit_ns, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.wait_limit_ns, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t da = umma_desc_k_sw128(smem_u32(sA + stage * A_STAGE));
+          const uint64_t db = umma_desc_k_sw128(smem_u32(sB + stage * B_STAGE));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // Advancing K inside the 128-byte swizzle atom: +32 bytes = +2 in descriptor address units.
+            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (warp >= EPI_WARP0) {
+    // ---------------- epilogue
+    const int ew = warp - EPI_WARP0;                 // TMEM lane quarter of this warp
+    const int row = ew * 32 + lane;                  // row of the tile handled by this thread
+    const bool issuer = threadIdx.x == EPI_WARP0 * 32;
+    const bool reduce_mode = (p.mode == BSHMEM_FUSED_RS || p.mode == BSHMEM_FUSED_AR) && p.npes > 1;
+    int acc = 0;
+    uint32_t acc_phase = 0, chunk_counter = 0;
+    for (int t = first; t < total_tiles; t += step) {
+      const TileInfo ti = tile_info(p, t);
+      const bool own = !reduce_mode || ti.peer == p.rank;
+      uint32_t ok = mbar_wait(&acc_full[acc], acc_phase, p.wait_limit_ns, abort_flag) ? 1u : 0u;
+      if (reduce_mode && own && issuer && ok) {
+        // Partials of this tile from every other PE must have landed in my receive slots.
+        for (int s = 0; s < p.npes && ok; ++s)
+          if (s != p.rank && !wait_flag_ge(p.flags_local + (size_t)s * (tmr * tiles_n) + ti.idx_in_peer, p.epoch, p.wait_limit_ns, abort_flag)) ok = 0;
+      }
+      // One vote per tile keeps the 128 epilogue threads together: either all go on or all leave.
+      if (!named_bar_and(1, EPI_THREADS, ok)) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+#pragma unroll 1
+      for (int c = 0; c < BN / EPI_COLS; ++c) {
+        float f[EPI_COLS];
+        tmem_ld_32x32(t_row + c * EPI_COLS, (uint32_t*)f);
+        tmem_ld_32x32(t_row + c * EPI_COLS + 32, (uint32_t*)f + 32);
+        tmem_ld_wait();
+        if (c == BN / EPI_COLS - 1) {
+          // All of this accumulator is in registers: hand the TMEM buffer back to the MMA warp.
+          tc_fence_before_sync();
+          mbar_arrive(&acc_empty[acc]);
+        }
+        if (reduce_mode && own) {
+          const size_t rows_per_pe = (size_t)p.M / p.npes;
+          const size_t grow = (size_t)ti.m_local * BM + row;
+          const size_t col0 = (size_t)ti.n_tile * BN + (size_t)c * EPI_COLS;
+          for (int s = 0; s < p.npes; ++s) {
+            if (s == p.rank) continue;
+            const uint4* src = (const uint4*)(p.recv_local + ((size_t)s * rows_per_pe + grow) * p.N + col0);
+#pragma unroll
+            for (int j = 0; j < EPI_COLS / 8; ++j) {
+              const uint4 v = src[j];
+              const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 x = __bfloat1622float2(h[e]);
+                f[j * 8 + 2 * e] += x.x;
+                f[j * 8 + 2 * e + 1] += x.y;
+              }
+            }
+          }
+        }
+        // Staging buffer (chunk_counter & 1) must have been drained by the TMA store issued two chunks ago.
+        uint8_t* buf = sE + (chunk_counter & 1) * EPI_BUF;
+        if (issuer) bulk_wait_read<1>();
+        named_bar_sync(1, EPI_THREADS);
+        // Row `row` of the chunk is 128 bytes = 8 x 16-byte pieces; piece j goes to slot j ^ (row & 7) (128-byte swizzle).
+#pragma unroll
+        for (int j = 0; j < EPI_COLS / 8; ++j) {
+          uint4 v;
+          __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[j * 8 + 2 * e], f[j * 8 + 2 * e + 1]);
+          *(uint4*)(buf + row * 128 + ((j ^ (row & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, EPI_THREADS);
+        if (issuer) {
+          const int x = ti.n_tile * BN + c * EPI_COLS;
+          if (!own) {
+            tma_store_2d(&p.tmRecv[ti.peer], buf, x, ti.m_local * BM);
+          } else if (p.mode == BSHMEM_FUSED_AR && p.npes > 1) {
+            for (int q = 0; q < p.npes; ++q) tma_store_2d(&p.tmOut[(p.rank + q) % p.npes], buf, x, ti.m_tile * BM);
+          } else if (p.mode == BSHMEM_FUSED_RS) {
+            tma_store_2d(&p.tmOut[0], buf, x, ti.m_local * BM);
+          } else {
+            tma_store_2d(&p.tmOut[0], buf, x, ti.m_tile * BM);
+          }
+          bulk_commit();
+        }
+        ++chunk_counter;
+      }
+      if (!own && issuer) {
+        // The four stores of the tile are complete at the destination; publish the tile.
+        bulk_wait<0>();
+        fence_proxy_async_all();
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        uint64_t* f = p.flags_peer[ti.peer] + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(p.epoch) : "memory");
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (issuer) bulk_wait<0>();
+  }
+
+  // ---------------- teardown
+  if (*abort_flag) {
+    // Give copies that are still in flight time to land before the CTA's shared memory goes away.
+    const uint64_t t0 = timer_ns();
+    while (timer_ns() - t0 < 200000) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 1);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+// Row-major bf16 matrix [rows, cols], box [box_rows, 64 columns], 128-byte swizzle.
+static int make_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return BSHMEM_FUSED_ERR_DRIVER;
+  if (((uintptr_t)base & 15) || (cols * 2) % 16) return BSHMEM_FUSED_ERR_ALIGNMENT;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : BSHMEM_FUSED_ERR_DRIVER;
+}
+
+static int g_attr_set_for_device = -1;
+
+}  // namespace bshmem
+
+using namespace bshmem;
+
+extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stream) {
+  if (!a || !a->A || !a->B || !a->out || !a->error_flag) return BSHMEM_FUSED_ERR_ARGS;
+  const int npes = a->npes, mode = a->mode;
+  if (npes < 1 || npes > BSHMEM_FUSED_MAX_PES || a->rank < 0 || a->rank >= npes) return BSHMEM_FUSED_ERR_ARGS;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->M % (BM * npes) || a->N % BN || a->K % BK) return BSHMEM_FUSED_ERR_SHAPE;
+  FusedParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.N = a->N; p.K = a->K; p.rank = a->rank; p.npes = npes; p.mode = mode;
+  p.epoch = a->epoch;
+  p.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
+  p.error_flag = a->error_flag;
+  const int rows_per_pe = a->M / npes;
+  const int tmr = rows_per_pe / BM;
+  int st = make_map(&p.tmA, a->A, a->M, a->K, BM);
+  if (!st) st = make_map(&p.tmB, a->B, a->N, a->K, BN);
+  if (st) return st;
+  const bool reduce_mode = (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1;
+  if (mode == BSHMEM_FUSED_AR && npes > 1) {
+    for (int q = 0; q < npes && !st; ++q) {
+      if (!a->out_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
+      st = make_map(&p.tmOut[q], a->out_peer[q], a->M, a->N, BM);
+    }
+  } else {
+    st = make_map(&p.tmOut[0], a->out, mode == BSHMEM_FUSED_RS ? rows_per_pe : a->M, a->N, BM);
+  }
+  if (st) return st;
+  if (reduce_mode) {
+    if (!a->recv_local || !a->flags_local) return BSHMEM_FUSED_ERR_ARGS;
+    p.recv_local = (const __nv_bfloat16*)a->recv_local;
+    p.flags_local = a->flags_local;
+    for (int q = 0; q < npes && !st; ++q) {
+      if (q == a->rank) continue;
+      if (!a->recv_peer[q] || !a->flags_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
+      // My slot (index `rank`) inside PE q's receive buffer.
+      const char* slot = (const char*)a->recv_peer[q] + (size_t)a->rank * rows_per_pe * a->N * 2;
+      st = make_map(&p.tmRecv[q], slot, rows_per_pe, a->N, BM);
+      p.flags_peer[q] = a->flags_peer[q];
+    }
+    if (st) return st;
+  }
+  int device = 0, sms = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  int grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
+  if (mode == BSHMEM_FUSED_AG && npes > 1) {
+    if (!a->ag_flags_local) return BSHMEM_FUSED_ERR_ARGS;
+    int n_comm = a->n_comm > 0 ? a->n_comm : 16;
+    // One unit of the shard per sender CTA; units and 128-row blocks must nest.
+    while (n_comm > 1 && !((n_comm % tmr == 0 && BM % (rows_per_pe / n_comm) == 0 && rows_per_pe % n_comm == 0) || tmr % n_comm == 0)) --n_comm;
+    const size_t shard_bytes = (size_t)rows_per_pe * a->K * 2;
+    p.n_comm = n_comm;
+    p.ag_unit_bytes = shard_bytes / n_comm;
+    if (p.ag_unit_bytes % COMM_PIECE) return BSHMEM_FUSED_ERR_SHAPE;
+    p.ag_parts = n_comm >= tmr ? n_comm / tmr : 1;
+    p.ag_tiles_per_unit = n_comm >= tmr ? 1 : tmr / n_comm;
+    p.ag_src = (const char*)a->A + (size_t)a->rank * shard_bytes;
+    p.ag_flags_local = a->ag_flags_local;
+    for (int q = 0; q < npes; ++q) {
+      if (q == a->rank) continue;
+      if (!a->ag_peer[q] || !a->ag_flags_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
+      p.ag_dst[q] = (char*)a->ag_peer[q] + (size_t)a->rank * shard_bytes;
+      p.ag_flags_peer[q] = a->ag_flags_peer[q];
+    }
+    if (grid - n_comm < 1) return BSHMEM_FUSED_ERR_ARGS;
+  }
+  if (g_attr_set_for_device != device) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "bshmem_fused_gemm: cannot reserve %d bytes of shared memory: %s\n", SMEM_BYTES, cudaGetErrorString(e));
+      return BSHMEM_FUSED_ERR_DRIVER;
+    }
+    g_attr_set_for_device = device;
+  }
+  gemm_fused_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "bshmem_fused_gemm: launch failed: %s\n", cudaGetErrorString(e));
+    return BSHMEM_FUSED_ERR_DRIVER;
+  }
+  return 0;
+}
+
+extern "C" int bshmem_fused_gemm_smem_bytes(void) { return SMEM_BYTES; }

@@ -693,6 +693,7 @@ uint64_t nvshmemx_b200_heap_info(int what) {
     case 4: return (uint64_t)r.heap->chunks();
     case 5: return r.heap->allocator().bytes_in_use();
     case 6: return r.heap->allocator().history_digest();
+    case 7: return r.have_gpu ? 1 : 0;
     default: return 0;
   }
 }

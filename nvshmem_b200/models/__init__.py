@@ -1,0 +1,2 @@
+"""Model blocks that run on the fused tensor-parallel and expert-parallel kernels."""
+from .tp_mlp import TensorParallelMLP  # noqa: F401

@@ -1,0 +1,2 @@
+"""Torch-facing operators built on the fused sm_100a kernels."""
+from .fused_gemm import (FusedGemmError, gemm, GemmReduceScatter, AllGatherGemm, fused_lib)  # noqa: F401

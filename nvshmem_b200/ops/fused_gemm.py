@@ -1,0 +1,233 @@
+"""Tensor-parallel GEMMs fused with their collective (``libbshmem_fused.so``).
+
+* :func:`gemm` – plain ``x @ w.T`` on the tcgen05 kernel (what one GPU runs).
+* :class:`GemmReduceScatter` – row-parallel linear: every rank multiplies its K-slice and the
+  kernel's epilogue pushes partial tiles into the owning rank's receive slots and reduces there
+  (``mode="rs"``), or additionally broadcasts the reduced tile to all ranks (``mode="ar"``).
+* :class:`AllGatherGemm` – column-parallel linear: sender CTAs spread the local activation shard
+  to all peers while the GEMM consumes shards as they land.
+
+Weights use torch's Linear layout ``[out_features, in_features]``; activations are ``[tokens,
+in_features]``; everything is bf16 with fp32 accumulation.  The collective variants keep their
+buffers in the symmetric heap; a call counter (epoch) replaces flag resets.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..bindings import host as H
+
+MAX_PES = 8
+MODES = {"plain": 0, "rs": 1, "ar": 2, "ag": 3}
+_lib = None
+
+
+class FusedGemmError(RuntimeError):
+    pass
+
+
+class _Args(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("out", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("rank", C.c_int), ("npes", C.c_int),
+                ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
+                ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
+                ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES)]
+
+
+_ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
+
+
+def fused_lib() -> C.CDLL:
+    """Loads the fused-kernel library; a missing library is an error (no fallback path exists)."""
+    global _lib
+    if _lib is None:
+        path = H.lib_path("libbshmem_fused.so")
+        if not path.exists():
+            raise ImportError(f"{path} is missing: build it with `python -m nvshmem_b200.utils.build`")
+        _lib = C.CDLL(str(path))
+        _lib.bshmem_fused_gemm.restype = C.c_int
+        _lib.bshmem_fused_gemm.argtypes = [C.POINTER(_Args), C.c_void_p]
+    return _lib
+
+
+_err_flags: dict[int, torch.Tensor] = {}
+
+
+def _error_flag(device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _err_flags:
+        _err_flags[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err_flags[idx]
+
+
+def check_errors(device=None) -> None:
+    """Raises if a fused kernel gave up on a wait since the last check (synchronises the device)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    flag = _error_flag(device)
+    v = int(flag.item())
+    if v:
+        flag.zero_()
+        raise FusedGemmError(f"a fused kernel abandoned a bounded wait (code {v}): a peer did not deliver its tiles in time")
+
+
+def _launch(args: _Args, stream) -> None:
+    st = fused_lib().bshmem_fused_gemm(C.byref(args), C.c_void_p(stream))
+    if st != 0:
+        raise FusedGemmError(f"bshmem_fused_gemm: {_ERRORS.get(st, st)}")
+
+
+def _check_operands(x: torch.Tensor, w: torch.Tensor) -> None:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise FusedGemmError("operands must be bfloat16")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise FusedGemmError(f"shape mismatch: x {tuple(x.shape)} w {tuple(w.shape)}")
+    if not x.is_contiguous() or not w.is_contiguous():
+        raise FusedGemmError("operands must be contiguous")
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """``x[M,K] @ w[N,K].T`` -> bf16 ``[M,N]`` on the tcgen05/TMEM kernel."""
+    _check_operands(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    a = _Args()
+    a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.M, a.N, a.K, a.rank, a.npes, a.mode = M, N, K, 0, 1, MODES["plain"]
+    a.epoch, a.max_ctas = 1, max_ctas
+    a.error_flag = _error_flag(x.device).data_ptr()
+    _launch(a, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+class GemmReduceScatter:
+    """Row-parallel GEMM fused with reduce-scatter (or all-reduce) over the world team.
+
+    ``forward(x, w)``: ``x`` is ``[M, K_local]``, ``w`` ``[N, K_local]``; returns this rank's
+    ``[M/npes, N]`` rows of the summed product (``mode="rs"``) or the whole ``[M, N]`` (``"ar"``).
+    The output tensor is owned by the object and overwritten by the next call.
+    """
+
+    def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0):
+        from .. import core
+        self.core = core
+        self.rank, self.npes = core.my_pe(), core.n_pes()
+        if self.npes > MAX_PES:
+            raise FusedGemmError(f"at most {MAX_PES} PEs")
+        self.M, self.N, self.mode = M, N, mode
+        self.wait_limit_ms = wait_limit_ms
+        self.rows = M // self.npes
+        self.epoch = 0
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        tiles = (self.rows // 128) * (N // 256)
+        if self.npes > 1:
+            # two generations of receive slots: a fast peer may already be pushing call k+1
+            self.recv = core.tensor((2, self.npes, self.rows, N), torch.bfloat16)
+            self.flags = core.tensor((self.npes * max(tiles, 1),), torch.int64, zero=True)
+        else:
+            self.recv = self.flags = None
+        if mode == "ar" and self.npes > 1:
+            self.out = core.tensor((M, N), torch.bfloat16)
+        else:
+            self.out = torch.empty(self.rows if mode == "rs" else M, N, dtype=torch.bfloat16, device=dev)
+        self._peer = {}
+        if self.npes > 1:
+            for q in range(self.npes):
+                self._peer[q] = (core.peer_ptr(self.recv, q), core.peer_ptr(self.flags, q), core.peer_ptr(self.out, q) if mode == "ar" else 0)
+            core.barrier_all()
+            torch.cuda.synchronize()
+
+    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        _check_operands(x, w)
+        if x.shape[0] != self.M or w.shape[0] != self.N:
+            raise FusedGemmError("operand shapes differ from the ones this object was built for")
+        self.epoch += 1
+        a = _Args()
+        a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), self.out.data_ptr()
+        a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, self.N, x.shape[1], self.rank, self.npes, MODES[self.mode]
+        a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
+        a.error_flag = _error_flag(self.device).data_ptr()
+        if self.npes > 1:
+            half = (self.epoch & 1) * self.npes * self.rows * self.N * 2
+            a.recv_local = self.recv.data_ptr() + half
+            a.flags_local = self.flags.data_ptr()
+            for q in range(self.npes):
+                a.recv_peer[q] = self._peer[q][0] + half
+                a.flags_peer[q] = self._peer[q][1]
+                a.out_peer[q] = self._peer[q][2]
+        _launch(a, torch.cuda.current_stream().cuda_stream)
+        return self.out
+
+    __call__ = forward
+
+    def close(self) -> None:
+        if self.npes > 1:
+            torch.cuda.synchronize()
+            self.core.free_tensor(self.recv)
+            self.core.free_tensor(self.flags)
+            if self.mode == "ar":
+                self.core.free_tensor(self.out)
+            self.recv = self.flags = None
+
+
+class AllGatherGemm:
+    """Column-parallel GEMM fused with the all-gather of its activations.
+
+    Write this rank's ``[M/npes, K]`` shard into :attr:`shard` (a view of the symmetric gathered
+    buffer), then ``forward(w)`` with ``w`` ``[N_local, K]`` returns ``[M, N_local]``.  A world sync
+    is issued on the stream before each launch so that no peer overwrites a buffer still being read.
+    """
+
+    def __init__(self, M: int, K: int, n_comm: int = 16, wait_limit_ms: int = 0):
+        from .. import core
+        self.core = core
+        self.rank, self.npes = core.my_pe(), core.n_pes()
+        if self.npes > MAX_PES:
+            raise FusedGemmError(f"at most {MAX_PES} PEs")
+        self.M, self.K, self.n_comm, self.wait_limit_ms = M, K, n_comm, wait_limit_ms
+        self.rows = M // self.npes
+        self.epoch = 0
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        if self.npes > 1:
+            self.gathered = core.tensor((M, K), torch.bfloat16)
+            self.flags = core.tensor((self.npes * max(self.rows // 128, 1),), torch.int64, zero=True)
+            self._peer = {q: (core.peer_ptr(self.gathered, q), core.peer_ptr(self.flags, q)) for q in range(self.npes)}
+            core.barrier_all()
+            torch.cuda.synchronize()
+        else:
+            self.gathered = torch.empty(M, K, dtype=torch.bfloat16, device=self.device)
+            self.flags = None
+        self.shard = self.gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
+        self.out = None
+
+    def forward(self, w: torch.Tensor) -> torch.Tensor:
+        _check_operands(self.gathered, w)
+        N = w.shape[0]
+        if self.out is None or self.out.shape[1] != N:
+            self.out = torch.empty(self.M, N, dtype=torch.bfloat16, device=self.device)
+        self.epoch += 1
+        a = _Args()
+        a.A, a.B, a.out = self.gathered.data_ptr(), w.data_ptr(), self.out.data_ptr()
+        a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, N, self.K, self.rank, self.npes, MODES["ag"]
+        a.epoch, a.wait_limit_ms, a.n_comm = self.epoch, self.wait_limit_ms, self.n_comm
+        a.error_flag = _error_flag(self.device).data_ptr()
+        if self.npes > 1:
+            a.ag_flags_local = self.flags.data_ptr()
+            for q in range(self.npes):
+                a.ag_peer[q] = self._peer[q][0]
+                a.ag_flags_peer[q] = self._peer[q][1]
+            self.core.sync_all()  # every rank has finished reading the previous gathered buffer
+        _launch(a, torch.cuda.current_stream().cuda_stream)
+        return self.out
+
+    __call__ = forward
+
+    def close(self) -> None:
+        if self.npes > 1:
+            torch.cuda.synchronize()
+            self.core.free_tensor(self.gathered)
+            self.core.free_tensor(self.flags)
+            self.gathered = self.flags = None
