@@ -11,6 +11,15 @@
 #include "bshmem/state.h"
 #include "bshmem/types.h"
 
+/* Calls that exist on both sides are declared __host__ __device__ under nvcc: the host
+ * definition lives in the host library, the device definition in bshmem/device_api.cuh
+ * (visible only to the device compilation pass). */
+#ifdef __CUDACC__
+#define BSHMEM_HD __host__ __device__
+#else
+#define BSHMEM_HD
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -79,10 +88,10 @@ int nvshmemx_set_attr_uniqueid_args(int myrank, int nranks, const nvshmemx_uniqu
 int nvshmemx_init_status(void);
 void nvshmem_finalize(void);
 void nvshmemx_hostlib_finalize(void);
-void nvshmem_global_exit(int status);
+BSHMEM_HD void nvshmem_global_exit(int status);
 void nvshmem_query_thread(int* provided);
-int nvshmem_my_pe(void);
-int nvshmem_n_pes(void);
+BSHMEM_HD int nvshmem_my_pe(void);
+BSHMEM_HD int nvshmem_n_pes(void);
 void nvshmem_info_get_version(int* major, int* minor);
 void nvshmem_info_get_name(char* name);
 void nvshmemx_vendor_get_version_info(int* major, int* minor, int* patch);
@@ -96,8 +105,8 @@ void* nvshmem_malloc(size_t size);
 void* nvshmem_calloc(size_t count, size_t size);
 void* nvshmem_align(size_t alignment, size_t size);
 void nvshmem_free(void* ptr);
-void* nvshmem_ptr(const void* dest, int pe);
-void* nvshmemx_mc_ptr(nvshmem_team_t team, const void* ptr);
+BSHMEM_HD void* nvshmem_ptr(const void* dest, int pe);
+BSHMEM_HD void* nvshmemx_mc_ptr(nvshmem_team_t team, const void* ptr);
 int nvshmemx_buffer_register(void* addr, size_t length);
 int nvshmemx_buffer_unregister(void* addr);
 void nvshmemx_buffer_unregister_all(void);
@@ -105,10 +114,10 @@ void* nvshmemx_buffer_register_symmetric(void* buf_ptr, size_t size, int flags);
 int nvshmemx_buffer_unregister_symmetric(void* mmap_ptr, size_t size);
 
 /* ---------------------------------------------------------------- teams */
-int nvshmem_team_my_pe(nvshmem_team_t team);
-int nvshmem_team_n_pes(nvshmem_team_t team);
+BSHMEM_HD int nvshmem_team_my_pe(nvshmem_team_t team);
+BSHMEM_HD int nvshmem_team_n_pes(nvshmem_team_t team);
 void nvshmem_team_get_config(nvshmem_team_t team, nvshmem_team_config_t* config);
-int nvshmem_team_translate_pe(nvshmem_team_t src_team, int src_pe, nvshmem_team_t dest_team);
+BSHMEM_HD int nvshmem_team_translate_pe(nvshmem_team_t src_team, int src_pe, nvshmem_team_t dest_team);
 int nvshmem_team_split_strided(nvshmem_team_t parent, int pe_start, int pe_stride, int pe_size, const nvshmem_team_config_t* config, long config_mask, nvshmem_team_t* new_team);
 int nvshmem_team_split_2d(nvshmem_team_t parent, int xrange, const nvshmem_team_config_t* xaxis_config, long xaxis_mask, nvshmem_team_t* xaxis_team,
                           const nvshmem_team_config_t* yaxis_config, long yaxis_mask, nvshmem_team_t* yaxis_team);
@@ -117,19 +126,19 @@ int nvshmemx_team_get_uniqueid(nvshmemx_team_uniqueid_t* uniqueid);
 int nvshmemx_team_init(nvshmem_team_t* team, nvshmem_team_config_t* config, long config_mask, int npes, int pe_idx_in_team);
 
 /* ---------------------------------------------------------------- ordering, signals, waits */
-void nvshmem_quiet(void);
-void nvshmem_fence(void);
+BSHMEM_HD void nvshmem_quiet(void);
+BSHMEM_HD void nvshmem_fence(void);
 void nvshmemx_quiet_on_stream(cudaStream_t stream);
-uint64_t nvshmem_signal_fetch(uint64_t* sig_addr);
-void nvshmemx_signal_op(uint64_t* sig_addr, uint64_t signal, int sig_op, int pe);
+BSHMEM_HD uint64_t nvshmem_signal_fetch(uint64_t* sig_addr);
+BSHMEM_HD void nvshmemx_signal_op(uint64_t* sig_addr, uint64_t signal, int sig_op, int pe);
 void nvshmemx_signal_op_on_stream(uint64_t* sig_addr, uint64_t signal, int sig_op, int pe, cudaStream_t stream);
 void nvshmemx_signal_wait_until_on_stream(uint64_t* sig_addr, int cmp, uint64_t cmp_value, cudaStream_t stream);
 
 /* ---------------------------------------------------------------- untyped RMA */
-void nvshmem_putmem(void* dest, const void* source, size_t bytes, int pe);
-void nvshmem_getmem(void* dest, const void* source, size_t bytes, int pe);
-void nvshmem_putmem_nbi(void* dest, const void* source, size_t bytes, int pe);
-void nvshmem_getmem_nbi(void* dest, const void* source, size_t bytes, int pe);
+BSHMEM_HD void nvshmem_putmem(void* dest, const void* source, size_t bytes, int pe);
+BSHMEM_HD void nvshmem_getmem(void* dest, const void* source, size_t bytes, int pe);
+BSHMEM_HD void nvshmem_putmem_nbi(void* dest, const void* source, size_t bytes, int pe);
+BSHMEM_HD void nvshmem_getmem_nbi(void* dest, const void* source, size_t bytes, int pe);
 void nvshmemx_putmem_on_stream(void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
 void nvshmemx_getmem_on_stream(void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
 void nvshmemx_putmem_nbi_on_stream(void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
@@ -139,14 +148,14 @@ void nvshmemx_putmem_signal_nbi_on_stream(void* dest, const void* source, size_t
 
 /* ---------------------------------------------------------------- typed RMA: put/get/p/g/iput/iget, nbi, on_stream, signal */
 #define BSHMEM_DECL_RMA(N, T)                                                                                          \
-  void nvshmem_##N##_p(T* dest, const T value, int pe);                                                                \
-  T nvshmem_##N##_g(const T* src, int pe);                                                                             \
-  void nvshmem_##N##_put(T* dest, const T* src, size_t nelems, int pe);                                                \
-  void nvshmem_##N##_get(T* dest, const T* src, size_t nelems, int pe);                                                \
-  void nvshmem_##N##_put_nbi(T* dest, const T* src, size_t nelems, int pe);                                            \
-  void nvshmem_##N##_get_nbi(T* dest, const T* src, size_t nelems, int pe);                                            \
-  void nvshmem_##N##_iput(T* dest, const T* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);                 \
-  void nvshmem_##N##_iget(T* dest, const T* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);                 \
+  BSHMEM_HD void nvshmem_##N##_p(T* dest, const T value, int pe);                                                                \
+  BSHMEM_HD T nvshmem_##N##_g(const T* src, int pe);                                                                             \
+  BSHMEM_HD void nvshmem_##N##_put(T* dest, const T* src, size_t nelems, int pe);                                                \
+  BSHMEM_HD void nvshmem_##N##_get(T* dest, const T* src, size_t nelems, int pe);                                                \
+  BSHMEM_HD void nvshmem_##N##_put_nbi(T* dest, const T* src, size_t nelems, int pe);                                            \
+  BSHMEM_HD void nvshmem_##N##_get_nbi(T* dest, const T* src, size_t nelems, int pe);                                            \
+  BSHMEM_HD void nvshmem_##N##_iput(T* dest, const T* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);                 \
+  BSHMEM_HD void nvshmem_##N##_iget(T* dest, const T* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);                 \
   void nvshmemx_##N##_p_on_stream(T* dest, const T value, int pe, cudaStream_t s);                                     \
   T nvshmemx_##N##_g_on_stream(const T* src, int pe, cudaStream_t s);                                                  \
   void nvshmemx_##N##_put_on_stream(T* dest, const T* src, size_t nelems, int pe, cudaStream_t s);                     \
@@ -161,12 +170,12 @@ BSHMEM_RMA_TYPES(BSHMEM_DECL_RMA)
 #undef BSHMEM_DECL_RMA
 
 #define BSHMEM_DECL_SIZED(BITS, T)                                                                                     \
-  void nvshmem_put##BITS(void* dest, const void* src, size_t nelems, int pe);                                          \
-  void nvshmem_get##BITS(void* dest, const void* src, size_t nelems, int pe);                                          \
-  void nvshmem_put##BITS##_nbi(void* dest, const void* src, size_t nelems, int pe);                                    \
-  void nvshmem_get##BITS##_nbi(void* dest, const void* src, size_t nelems, int pe);                                    \
-  void nvshmem_iput##BITS(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);           \
-  void nvshmem_iget##BITS(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);           \
+  BSHMEM_HD void nvshmem_put##BITS(void* dest, const void* src, size_t nelems, int pe);                                          \
+  BSHMEM_HD void nvshmem_get##BITS(void* dest, const void* src, size_t nelems, int pe);                                          \
+  BSHMEM_HD void nvshmem_put##BITS##_nbi(void* dest, const void* src, size_t nelems, int pe);                                    \
+  BSHMEM_HD void nvshmem_get##BITS##_nbi(void* dest, const void* src, size_t nelems, int pe);                                    \
+  BSHMEM_HD void nvshmem_iput##BITS(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);           \
+  BSHMEM_HD void nvshmem_iget##BITS(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);           \
   void nvshmemx_put##BITS##_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);             \
   void nvshmemx_get##BITS##_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);             \
   void nvshmemx_put##BITS##_signal_on_stream(void* dest, const void* src, size_t nelems, uint64_t* sig, uint64_t signal, int sig_op, int pe, cudaStream_t s);
@@ -183,22 +192,22 @@ BSHMEM_WAIT_TYPES(BSHMEM_DECL_WAIT)
 
 /* ---------------------------------------------------------------- host atomics (carried out by a one-thread kernel) */
 #define BSHMEM_DECL_AMO_STD(N, T)                                      \
-  void nvshmem_##N##_atomic_inc(T* target, int pe);                    \
-  T nvshmem_##N##_atomic_fetch_inc(T* target, int pe);                 \
-  void nvshmem_##N##_atomic_add(T* target, T value, int pe);           \
-  T nvshmem_##N##_atomic_fetch_add(T* target, T value, int pe);        \
-  T nvshmem_##N##_atomic_compare_swap(T* target, T cond, T value, int pe);
+  BSHMEM_HD void nvshmem_##N##_atomic_inc(T* target, int pe);                    \
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch_inc(T* target, int pe);                 \
+  BSHMEM_HD void nvshmem_##N##_atomic_add(T* target, T value, int pe);           \
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch_add(T* target, T value, int pe);        \
+  BSHMEM_HD T nvshmem_##N##_atomic_compare_swap(T* target, T cond, T value, int pe);
 #define BSHMEM_DECL_AMO_EXT(N, T)                                      \
-  T nvshmem_##N##_atomic_fetch(const T* target, int pe);               \
-  void nvshmem_##N##_atomic_set(T* target, T value, int pe);           \
-  T nvshmem_##N##_atomic_swap(T* target, T value, int pe);
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch(const T* target, int pe);               \
+  BSHMEM_HD void nvshmem_##N##_atomic_set(T* target, T value, int pe);           \
+  BSHMEM_HD T nvshmem_##N##_atomic_swap(T* target, T value, int pe);
 #define BSHMEM_DECL_AMO_BIT(N, T)                                      \
-  void nvshmem_##N##_atomic_and(T* target, T value, int pe);           \
-  T nvshmem_##N##_atomic_fetch_and(T* target, T value, int pe);        \
-  void nvshmem_##N##_atomic_or(T* target, T value, int pe);            \
-  T nvshmem_##N##_atomic_fetch_or(T* target, T value, int pe);         \
-  void nvshmem_##N##_atomic_xor(T* target, T value, int pe);           \
-  T nvshmem_##N##_atomic_fetch_xor(T* target, T value, int pe);
+  BSHMEM_HD void nvshmem_##N##_atomic_and(T* target, T value, int pe);           \
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch_and(T* target, T value, int pe);        \
+  BSHMEM_HD void nvshmem_##N##_atomic_or(T* target, T value, int pe);            \
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch_or(T* target, T value, int pe);         \
+  BSHMEM_HD void nvshmem_##N##_atomic_xor(T* target, T value, int pe);           \
+  BSHMEM_HD T nvshmem_##N##_atomic_fetch_xor(T* target, T value, int pe);
 BSHMEM_STANDARD_AMO_TYPES(BSHMEM_DECL_AMO_STD)
 BSHMEM_EXTENDED_AMO_TYPES(BSHMEM_DECL_AMO_EXT)
 BSHMEM_BITWISE_AMO_TYPES(BSHMEM_DECL_AMO_BIT)
@@ -207,26 +216,26 @@ BSHMEM_BITWISE_AMO_TYPES(BSHMEM_DECL_AMO_BIT)
 #undef BSHMEM_DECL_AMO_BIT
 
 /* ---------------------------------------------------------------- collectives: blocking and on-stream */
-void nvshmem_barrier_all(void);
-int nvshmem_barrier(nvshmem_team_t team);
-void nvshmem_sync_all(void);
-int nvshmem_team_sync(nvshmem_team_t team);
+BSHMEM_HD void nvshmem_barrier_all(void);
+BSHMEM_HD int nvshmem_barrier(nvshmem_team_t team);
+BSHMEM_HD void nvshmem_sync_all(void);
+BSHMEM_HD int nvshmem_team_sync(nvshmem_team_t team);
 void nvshmemx_barrier_all_on_stream(cudaStream_t stream);
 int nvshmemx_barrier_on_stream(nvshmem_team_t team, cudaStream_t stream);
 void nvshmemx_sync_all_on_stream(cudaStream_t stream);
 int nvshmemx_team_sync_on_stream(nvshmem_team_t team, cudaStream_t stream);
-int nvshmem_alltoallmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes);
-int nvshmem_fcollectmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes);
-int nvshmem_broadcastmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes, int root);
+BSHMEM_HD int nvshmem_alltoallmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes);
+BSHMEM_HD int nvshmem_fcollectmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes);
+BSHMEM_HD int nvshmem_broadcastmem(nvshmem_team_t team, void* dest, const void* src, size_t bytes, int root);
 int nvshmemx_alltoallmem_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t bytes, cudaStream_t s);
 int nvshmemx_fcollectmem_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t bytes, cudaStream_t s);
 int nvshmemx_broadcastmem_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t bytes, int root, cudaStream_t s);
 int nvshmemx_double2_maxloc_reduce_on_stream(nvshmem_team_t team, double2* dest, const double2* src, size_t nreduce, cudaStream_t s);
 
 #define BSHMEM_DECL_COLL(N, T)                                                                                         \
-  int nvshmem_##N##_alltoall(nvshmem_team_t team, T* dest, const T* src, size_t nelems);                               \
-  int nvshmem_##N##_fcollect(nvshmem_team_t team, T* dest, const T* src, size_t nelems);                               \
-  int nvshmem_##N##_broadcast(nvshmem_team_t team, T* dest, const T* src, size_t nelems, int root);                    \
+  BSHMEM_HD int nvshmem_##N##_alltoall(nvshmem_team_t team, T* dest, const T* src, size_t nelems);                               \
+  BSHMEM_HD int nvshmem_##N##_fcollect(nvshmem_team_t team, T* dest, const T* src, size_t nelems);                               \
+  BSHMEM_HD int nvshmem_##N##_broadcast(nvshmem_team_t team, T* dest, const T* src, size_t nelems, int root);                    \
   int nvshmemx_##N##_alltoall_on_stream(nvshmem_team_t team, T* dest, const T* src, size_t nelems, cudaStream_t s);    \
   int nvshmemx_##N##_fcollect_on_stream(nvshmem_team_t team, T* dest, const T* src, size_t nelems, cudaStream_t s);    \
   int nvshmemx_##N##_broadcast_on_stream(nvshmem_team_t team, T* dest, const T* src, size_t nelems, int root, cudaStream_t s);
@@ -234,8 +243,8 @@ BSHMEM_RMA_TYPES(BSHMEM_DECL_COLL)
 #undef BSHMEM_DECL_COLL
 
 #define BSHMEM_DECL_REDUCE_OP(N, T, OPNAME)                                                                            \
-  int nvshmem_##N##_##OPNAME##_reduce(nvshmem_team_t team, T* dest, const T* src, size_t nreduce);                     \
-  int nvshmem_##N##_##OPNAME##_reducescatter(nvshmem_team_t team, T* dest, const T* src, size_t nreduce);              \
+  BSHMEM_HD int nvshmem_##N##_##OPNAME##_reduce(nvshmem_team_t team, T* dest, const T* src, size_t nreduce);                     \
+  BSHMEM_HD int nvshmem_##N##_##OPNAME##_reducescatter(nvshmem_team_t team, T* dest, const T* src, size_t nreduce);              \
   int nvshmemx_##N##_##OPNAME##_reduce_on_stream(nvshmem_team_t team, T* dest, const T* src, size_t nreduce, cudaStream_t s); \
   int nvshmemx_##N##_##OPNAME##_reducescatter_on_stream(nvshmem_team_t team, T* dest, const T* src, size_t nreduce, cudaStream_t s);
 #define BSHMEM_DECL_BITWISE(N, T) BSHMEM_DECL_REDUCE_OP(N, T, and) BSHMEM_DECL_REDUCE_OP(N, T, or) BSHMEM_DECL_REDUCE_OP(N, T, xor)

@@ -30,8 +30,10 @@ class _OpCache:
             self.rs[key] = fg.GemmReduceScatter(M, N, mode="rs")
         return self.rs[key]
 
-    def all_gather(self, M: int, K: int) -> fg.AllGatherGemm:
-        key = (M, K)
+    def all_gather(self, M: int, K: int, owner=None) -> fg.AllGatherGemm:
+        """`owner` keeps a private gathered buffer (a layer's forward input must survive until its
+        backward); without it the buffer is shared by every user of the shape (transient use)."""
+        key = (M, K, id(owner) if owner is not None else None)
         if key not in self.ag:
             self.ag[key] = fg.AllGatherGemm(M, K)
         return self.ag[key]
@@ -49,9 +51,9 @@ def _t(x: torch.Tensor) -> torch.Tensor:
 
 class _ColumnParallelFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x_shard, weight, cache: _OpCache, M: int):
+    def forward(ctx, x_shard, weight, cache: _OpCache, M: int, owner):
         K = x_shard.shape[1]
-        ag = cache.all_gather(M, K)
+        ag = cache.all_gather(M, K, owner)
         ag.shard.copy_(x_shard)
         y = ag(weight).clone()
         ctx.save_for_backward(weight)
@@ -69,7 +71,7 @@ class _ColumnParallelFn(torch.autograd.Function):
         # dX_shard[M/n, K] = reduce_scatter(dY[M, Nl] @ W[Nl, K])
         rs = ctx.cache.reduce_scatter(ctx.M, ctx.K)
         dx = rs(dy, _t(weight)).clone()
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
 class _RowParallelFn(torch.autograd.Function):
@@ -109,7 +111,7 @@ class ColumnParallelLinear(torch.nn.Module):
         self.weight = torch.nn.Parameter(w.to(torch.bfloat16))
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
-        return _ColumnParallelFn.apply(x_shard, self.weight, self.cache, self.tokens)
+        return _ColumnParallelFn.apply(x_shard, self.weight, self.cache, self.tokens, self)
 
 
 class RowParallelLinear(torch.nn.Module):

@@ -1,0 +1,37 @@
+"""Host-side logic as real OS processes on CPU: bootstrap, heap bookkeeping, host RMA, atomics, teams,
+and host-made failures.  No GPU is used (gloo backend, host-memory heap)."""
+import pytest
+
+from tests._mp import run_workers
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 8])
+def test_bootstrap_collectives(n):
+    run_workers("bootstrap_raw", n)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_alloc_symmetry_seeded_sequence(n):
+    run_workers("alloc_symmetry", n, env={"NVSHMEM_SYMMETRIC_SIZE": "8M"})
+
+
+def test_alloc_symmetry_with_error_checks():
+    run_workers("alloc_symmetry", 2, env={"NVSHMEM_SYMMETRIC_SIZE": "8M", "NVSHMEM_ENABLE_ERROR_CHECKS": "1"})
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_host_rma_and_atomics(n):
+    run_workers("host_rma_and_atomics", n)
+
+
+@pytest.mark.parametrize("n", [1, 2, 5])
+def test_teams(n):
+    run_workers("teams", n)
+
+
+def test_root_drops_a_registration_everyone_times_out():
+    run_workers("bootstrap_missing_rank", 3, env={"NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "1500"}, timeout=120)
+
+
+def test_rank_that_never_joins_gives_error_status():
+    run_workers("rank_never_joins", 3, env={"NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "1500"}, timeout=120)

@@ -1,0 +1,73 @@
+"""Multi-PE tests on real GPUs: one child process per GPU (2 to 4 of them), NCCL only for the test
+harness' own gathers.  NVLS is off unless a test is about it: a rank that died with its memory bound
+to a multicast object has disturbed other GPUs on shared hosts."""
+import pytest
+
+from tests._mp import run_workers
+from tests.conftest import gpu_count
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+NG = min(gpu_count(), 4)
+need2 = pytest.mark.skipif(gpu_count() < 2, reason="needs two or more GPUs")
+NO_NVLS = {"NVSHMEM_DISABLE_NVLS": "1", "NCCL_NVLS_ENABLE": "0"}
+
+
+@need2
+def test_alloc_symmetry_gpu():
+    run_workers("alloc_symmetry", NG, gpu=True, env=NO_NVLS)
+
+
+@need2
+def test_host_rma_and_atomics_gpu():
+    run_workers("host_rma_and_atomics", NG, gpu=True, env=NO_NVLS)
+
+
+@need2
+def test_teams_gpu():
+    run_workers("teams", NG, gpu=True, env=NO_NVLS)
+
+
+@need2
+def test_device_rma():
+    run_workers("device_rma", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_device_signals_atomics_barriers():
+    run_workers("device_signals_amo_barrier", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_collectives_on_stream():
+    run_workers("collectives_on_stream", NG, gpu=True, env=NO_NVLS, timeout=900)
+
+
+@need2
+def test_collectives_on_stream_nvls():
+    run_workers("collectives_on_stream", NG, gpu=True, env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
+
+
+@need2
+def test_collectives_in_cuda_graph():
+    run_workers("collectives_in_graph", NG, gpu=True, env=NO_NVLS)
+
+
+@need2
+def test_device_collectives_and_tiles():
+    run_workers("device_collectives_and_tiles", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_fused_gemm_collectives():
+    run_workers("fused_gemm_collectives", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_tp_mlp_matches_single_device():
+    run_workers("tp_mlp_matches_single_device", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_rank_leaves_between_steps():
+    run_workers("rank_leaves_between_steps", NG, gpu=True, env=NO_NVLS)

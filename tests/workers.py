@@ -1,0 +1,802 @@
+"""Worker bodies of the multi-process tests.  `python -m tests.workers <name>` runs one of them as
+rank RANK of WORLD_SIZE; with BSHMEM_TEST_GPU=1 each rank uses GPU LOCAL_RANK (NCCL + VMM heap),
+otherwise the gloo backend and the host-memory heap, which needs no GPU."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import random
+import sys
+
+import torch
+import torch.distributed as dist
+
+GPU = os.environ.get("BSHMEM_TEST_GPU") == "1"
+RANK = int(os.environ.get("RANK", "0"))
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+WORKERS = {}
+
+
+def worker(fn):
+    WORKERS[fn.__name__] = fn
+    return fn
+
+
+def setup():
+    import nvshmem_b200.core as nv
+    if GPU:
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+        nv.init(device=int(os.environ["LOCAL_RANK"]), initializer_method="torch")
+    else:
+        dist.init_process_group("gloo")
+        nv.init(initializer_method="torch")
+    return nv
+
+
+def teardown(nv):
+    if GPU:
+        torch.cuda.synchronize()
+    nv.finalize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gather_objects(obj):
+    out = [None] * WORLD
+    dist.all_gather_object(out, obj)
+    return out
+
+
+# ====================================================================== host-only (also valid on GPU)
+@worker
+def alloc_symmetry():
+    """Seeded 64-call malloc/align/free sequence: every PE must see identical offsets."""
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    rng = random.Random(20240611)
+    base = lib.nvshmemx_b200_heap_info(0)
+    live, trace = [], []
+    for i in range(64):
+        if live and rng.random() < 0.4:
+            p = live.pop(rng.randrange(len(live)))
+            lib.nvshmem_free(p)
+            trace.append(("free", p - base))
+        else:
+            size = int(2 ** rng.uniform(3, 24))
+            align = rng.choice([64, 256, 4096])
+            p = lib.nvshmem_align(align, size)
+            assert p and (p - base) % max(align, 512) == 0, (i, size, align, p)
+            live.append(p)
+            trace.append(("alloc", p - base, size, align))
+    traces = gather_objects(trace)
+    assert all(t == traces[0] for t in traces), "offsets differ between PEs"
+    digests = gather_objects(lib.nvshmemx_b200_heap_info(6))
+    assert len(set(digests)) == 1
+    for p in live:
+        lib.nvshmem_free(p)
+    lib.nvshmem_barrier_all()
+    teardown(nv)
+
+
+@worker
+def host_rma_and_atomics():
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    n = WORLD
+    buf = lib.nvshmem_calloc(4096, 8)
+    right, left = (RANK + 1) % n, (RANK - 1) % n
+    src = (C.c_long * 8)(*[RANK * 100 + k for k in range(8)])
+    lib.nvshmem_putmem(buf, src, 64, right)
+    lib.nvshmem_barrier_all()
+    got = (C.c_long * 8)()
+    lib.nvshmem_getmem(got, buf, 64, RANK)
+    assert list(got) == [left * 100 + k for k in range(8)], list(got)
+    # get from the right neighbour: it holds what I wrote
+    lib.nvshmem_getmem(got, buf, 64, right)
+    assert list(got) == [RANK * 100 + k for k in range(8)]
+    # p / g
+    lib.nvshmem_long_p(buf + 1024, 7000 + RANK, right)
+    lib.nvshmem_barrier_all()
+    assert lib.nvshmem_long_g(buf + 1024, RANK) == 7000 + left
+    # strided: every 2nd source element into every 3rd slot on the left neighbour
+    strided = (C.c_long * 8)(*range(10, 18))
+    lib.nvshmem_long_iput(buf + 2048, strided, 3, 2, 4, left)
+    lib.nvshmem_barrier_all()
+    lib.nvshmem_getmem(got, buf + 2048, 64, RANK)
+    assert [got[0], got[3], got[6]] == [10, 12, 14]
+    # atomics on PE 0
+    lib.nvshmem_barrier_all()
+    old = lib.nvshmem_long_atomic_fetch_add(buf + 3072, RANK + 1, 0)
+    olds = gather_objects(old)
+    lib.nvshmem_barrier_all()
+    total = lib.nvshmem_long_atomic_fetch(buf + 3072, 0)
+    assert total == n * (n + 1) // 2, total
+    assert sorted(olds)[0] == 0 and len(set(olds)) == n
+    winner = lib.nvshmem_long_atomic_compare_swap(buf + 3080, 0, RANK + 1, 0)
+    winners = gather_objects(winner)
+    assert winners.count(0) == 1
+    mask = lib.nvshmem_uint64_atomic_fetch_or(buf + 3088, 1 << RANK, 0)
+    lib.nvshmem_barrier_all()
+    assert lib.nvshmem_uint64_atomic_fetch_or(buf + 3088, 0, 0) == (1 << n) - 1
+    # signals from the host
+    sig = lib.nvshmem_calloc(1, 8)
+    stream = torch.cuda.current_stream().cuda_stream if GPU else 0
+    lib.nvshmemx_signal_op_on_stream(sig, 5, H.SIGNAL_SET, right, stream)
+    lib.nvshmemx_signal_op_on_stream(sig, 2, H.SIGNAL_ADD, right, stream)
+    if GPU:
+        torch.cuda.synchronize()
+    lib.nvshmem_barrier_all()
+    assert lib.nvshmem_signal_fetch(sig) == 7
+    lib.nvshmem_free(sig)
+    lib.nvshmem_free(buf)
+    teardown(nv)
+
+
+@worker
+def teams():
+    nv = setup()
+    n = WORLD
+    T = nv.Teams
+    assert nv.team_my_pe(T.TEAM_WORLD) == RANK and nv.team_n_pes(T.TEAM_WORLD) == n
+    assert nv.team_n_pes(T.TEAM_NODE) == n and nv.team_n_pes(T.TEAM_SHARED) == n
+    assert nv.team_n_pes(T.TEAM_SAME_MYPE_NODE) == 1
+    # even PEs
+    even = nv.team_split_strided(T.TEAM_WORLD, 0, 2, (n + 1) // 2)
+    if RANK % 2 == 0:
+        assert even >= 6 and nv.team_my_pe(even) == RANK // 2 and nv.team_n_pes(even) == (n + 1) // 2
+        assert nv.team_translate_pe(even, nv.team_my_pe(even), T.TEAM_WORLD) == RANK
+        assert nv.team_translate_pe(T.TEAM_WORLD, RANK, even) == RANK // 2
+        if n > 1:
+            assert nv.team_translate_pe(T.TEAM_WORLD, 1, even) == -1
+        from nvshmem_b200.bindings import host as H
+        assert H.load().nvshmem_team_sync(even) == 0
+    else:
+        assert even == T.TEAM_INVALID
+    # create/destroy loop: slots are recycled
+    seen = set()
+    for _ in range(6):
+        t = nv.team_split_strided(T.TEAM_WORLD, 0, 1, n)
+        seen.add(t)
+        nv.team_destroy(t)
+    assert len(seen) <= 2
+    if RANK % 2 == 0:
+        nv.team_destroy(even)
+    # 2-D split
+    if n >= 4:
+        xt, yt = nv.team_split_2d(T.TEAM_WORLD, 2)
+        assert nv.team_n_pes(xt) == min(2, n - (RANK // 2) * 2) and nv.team_my_pe(xt) == RANK % 2
+        assert nv.team_my_pe(yt) == RANK // 2
+        nv.team_destroy(xt)
+        nv.team_destroy(yt)
+    # unique-id team of the odd PEs (arbitrary membership)
+    if n >= 3:
+        from nvshmem_b200.bindings import host as H
+        uid = gather_objects(nv.get_team_unique_id())[0]
+        members = [p for p in range(n) if p % 2 == 1]
+        cfg = H.TeamConfig(uniqueid=uid)
+        if RANK in members:
+            t = nv.team_init(cfg, 0, len(members), members.index(RANK))
+            assert nv.team_n_pes(t) == len(members) and nv.team_translate_pe(t, members.index(RANK), T.TEAM_WORLD) == RANK
+            nv.team_destroy(t)
+        else:
+            assert nv.team_init(cfg, 0, 0, -1) == T.TEAM_INVALID
+    nv.barrier_all() if GPU else None
+    teardown(nv)
+
+
+@worker
+def bootstrap_raw():
+    """The UID bootstrap alone (no heap): allgather / alltoall / barrier with odd sizes."""
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    dist.init_process_group("gloo")
+    payload = [None]
+    if RANK == 0:
+        uid = H.UniqueId()
+        assert lib.nvshmemx_get_uniqueid(C.byref(uid)) == 0
+        payload = [uid.to_bytes()]
+    dist.broadcast_object_list(payload, src=0)
+    uid = H.UniqueId.from_bytes(payload[0])
+    lib.bshmem_test_boot_init.restype = C.c_void_p
+    st = C.c_int(-1)
+    h = lib.bshmem_test_boot_init(C.byref(uid), RANK, WORLD, C.byref(st))
+    assert h and st.value == 0, st.value
+    h = C.c_void_p(h)
+    for nbytes in (1, 8, 33, 4096, 300000):
+        send = bytes([(RANK * 7 + i) % 251 for i in range(nbytes)])
+        recv = C.create_string_buffer(nbytes * WORLD)
+        assert lib.bshmem_test_boot_allgather(h, send, recv, nbytes) == 0
+        for r in range(WORLD):
+            assert recv.raw[r * nbytes:(r + 1) * nbytes] == bytes([(r * 7 + i) % 251 for i in range(nbytes)]), (nbytes, r)
+        a2a_send = b"".join(bytes([(RANK * 16 + p + i) % 256 for i in range(nbytes)]) for p in range(WORLD))
+        a2a_recv = C.create_string_buffer(nbytes * WORLD)
+        assert lib.bshmem_test_boot_alltoall(h, a2a_send, a2a_recv, nbytes) == 0
+        for p in range(WORLD):
+            assert a2a_recv.raw[p * nbytes:(p + 1) * nbytes] == bytes([(p * 16 + RANK + i) % 256 for i in range(nbytes)]), (nbytes, p)
+        assert lib.bshmem_test_boot_barrier(h) == 0
+    mn, nn = C.c_int(), C.c_int()
+    lib.bshmem_test_boot_node_info(h, C.byref(mn), C.byref(nn))
+    assert nn.value == WORLD and mn.value == RANK
+    lib.bshmem_test_boot_finalize(h)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@worker
+def bootstrap_missing_rank():
+    """Host-side fault injection: the root drops the last rank's registration, so nobody gets an
+    address table; every rank's init returns a time-out status within the bound, none exits or hangs."""
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    dist.init_process_group("gloo")
+    payload = [None]
+    if RANK == 0:
+        lib.bshmem_test_boot_drop_rank(WORLD - 1)
+        uid = H.UniqueId()
+        assert lib.nvshmemx_get_uniqueid(C.byref(uid)) == 0
+        payload = [uid.to_bytes()]
+    dist.broadcast_object_list(payload, src=0)
+    uid = H.UniqueId.from_bytes(payload[0])
+    lib.bshmem_test_boot_init.restype = C.c_void_p
+    lib.bshmem_test_boot_strerror.restype = C.c_char_p
+    st = C.c_int(-1)
+    h = lib.bshmem_test_boot_init(C.byref(uid), RANK, WORLD, C.byref(st))
+    assert not h and st.value in (2, 5), (st.value, lib.bshmem_test_boot_strerror(st.value))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@worker
+def rank_never_joins():
+    """One rank never calls init: the others get a time-out status from init (short bound) and carry on."""
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    dist.init_process_group("gloo")
+    payload = [None]
+    if RANK == 0:
+        uid = H.UniqueId()
+        assert lib.nvshmemx_get_uniqueid(C.byref(uid)) == 0
+        payload = [uid.to_bytes()]
+    dist.broadcast_object_list(payload, src=0)
+    if RANK != WORLD - 1:
+        uid = H.UniqueId.from_bytes(payload[0])
+        st = lib.nvshmemx_b200_init_uid(C.byref(uid), RANK, WORLD, -1)
+        assert st != 0
+        assert lib.nvshmemx_init_status() != 2
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+# ====================================================================== GPU: device API
+def _devtest():
+    from nvshmem_b200.bindings import host as H
+    H.load()
+    lib = C.CDLL(str(H.lib_path("libbshmem_devtest.so")))
+    return lib
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@worker
+def device_rma():
+    nv = setup()
+    dt = _devtest()
+    n = WORLD
+    right = (RANK + 1) % n
+    cap = 1 << 16
+    dst = nv.tensor((cap,), torch.uint8)
+    srcsym = nv.tensor((cap,), torch.uint8)
+    local = torch.empty(cap, dtype=torch.uint8, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(77 + RANK)
+    sizes = list(range(1, 40)) + [63, 64, 65, 127, 128, 129, 255, 256, 257, 1000, 4096, 4097, 30001]
+    for scope in (0, 1, 2):
+        for nbi in (0, 1):
+            for size in (sizes if scope == 2 else sizes[::3]):
+                for off_d, off_s in ((0, 0), (1, 1), (3, 5), (16, 8), (8, 16)):
+                    if size + max(off_d, off_s) > cap:
+                        continue
+                    local.random_(0, 256, generator=g)
+                    dst.zero_()
+                    nv.barrier_all()
+                    assert dt.devtest_put(C.c_void_p(dst.data_ptr() + off_d), C.c_void_p(local.data_ptr() + off_s), C.c_size_t(size), right, scope, nbi, _stream()) == 0
+                    nv.barrier_all()
+                    torch.cuda.synchronize()
+                    # what landed here came from the left neighbour: compare through a gather of sources
+                    want = [torch.empty_like(local) for _ in range(n)]
+                    dist.all_gather(want, local)
+                    left = (RANK - 1) % n
+                    assert torch.equal(dst[off_d:off_d + size], want[left][off_s:off_s + size]), (scope, nbi, size, off_d, off_s)
+                    assert int(dst[off_d + size:off_d + size + 8].sum()) == 0 and (off_d == 0 or int(dst[:off_d].sum()) == 0), "wrote outside the target range"
+    # get: pull from the right neighbour's symmetric buffer
+    for scope in (0, 1, 2):
+        for size in (1, 7, 64, 257, 4097, 30001):
+            srcsym.random_(0, 256, generator=g)
+            local.zero_()
+            nv.barrier_all()
+            assert dt.devtest_get(C.c_void_p(local.data_ptr()), C.c_void_p(srcsym.data_ptr()), C.c_size_t(size), right, scope, 0, _stream()) == 0
+            torch.cuda.synchronize()
+            want = [torch.empty_like(srcsym) for _ in range(n)]
+            dist.all_gather(want, srcsym)
+            assert torch.equal(local[:size], want[right][:size]), (scope, size)
+            nv.barrier_all()
+    # typed calls
+    nelem = 1024
+    fdst, idst, ddst, hdst = nv.tensor((nelem,), torch.float32), nv.tensor((4,), torch.int32), nv.tensor((nelem,), torch.float64, zero=True), nv.tensor((nelem,), torch.bfloat16)
+    fsrc = torch.rand(nelem, device="cuda") + RANK
+    dsrc = torch.arange(nelem, device="cuda", dtype=torch.float64) + 1000 * RANK
+    hsrc = (torch.rand(nelem, device="cuda") + RANK).to(torch.bfloat16)
+    gout = torch.zeros(4, dtype=torch.int32, device="cuda")
+    nv.barrier_all()
+    assert dt.devtest_typed(C.c_void_p(fdst.data_ptr()), C.c_void_p(fsrc.data_ptr()), C.c_void_p(idst.data_ptr()), C.c_void_p(ddst.data_ptr()), C.c_void_p(dsrc.data_ptr()),
+                            C.c_void_p(hdst.data_ptr()), C.c_void_p(hsrc.data_ptr()), C.c_size_t(nelem), right, C.c_void_p(gout.data_ptr()), _stream()) == 0
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    left = (RANK - 1) % n
+    fs = [torch.empty_like(fsrc) for _ in range(n)]
+    dist.all_gather(fs, fsrc)
+    hs = [torch.empty_like(hsrc) for _ in range(n)]
+    dist.all_gather(hs, hsrc)
+    assert torch.equal(fdst, fs[left]) and torch.equal(hdst, hs[left])
+    assert int(idst[0]) == 1000 + left
+    want_d = torch.zeros(nelem, dtype=torch.float64)
+    want_d[0:2 * (nelem // 4):2] = (torch.arange(nelem, dtype=torch.float64) + 1000 * left)[0:3 * (nelem // 4):3]
+    assert torch.equal(ddst.cpu(), want_d)
+    assert gout.tolist() == [1000 + RANK, n, 1, 1], gout.tolist()
+    assert nv.error_bits() == 0
+    for t in (dst, srcsym, fdst, idst, ddst, hdst):
+        nv.free_tensor(t)
+    teardown(nv)
+
+
+@worker
+def device_signals_amo_barrier():
+    nv = setup()
+    dt = _devtest()
+    n = WORLD
+    right, left = (RANK + 1) % n, (RANK - 1) % n
+    words = 1 << 16
+    data = nv.tensor((words,), torch.int32, zero=True)
+    sig = nv.tensor((2,), torch.int64, zero=True)
+    out = torch.zeros(2, dtype=torch.int64, device="cuda")
+    side = torch.cuda.Stream()
+    for it, (scope, op) in enumerate([(0, 9), (1, 9), (2, 9), (2, 10)]):
+        payload = torch.randint(0, 1 << 20, (words,), dtype=torch.int32, device="cuda")
+        want_val = it + 1 if op == 9 else 4 + 3
+        # consumer first, on a side stream: it spins (bounded) until the producer's signal lands
+        with torch.cuda.stream(side):
+            assert dt.devtest_signal_wait_sum(C.c_void_p(data.data_ptr()), C.c_size_t(words), C.c_void_p(sig.data_ptr()), 5, C.c_uint64(want_val), C.c_void_p(out.data_ptr()),
+                                              C.c_void_p(side.cuda_stream)) == 0
+        assert dt.devtest_put_signal(C.c_void_p(data.data_ptr()), C.c_void_p(payload.data_ptr()), C.c_size_t(words * 4), C.c_void_p(sig.data_ptr()),
+                                     C.c_uint64(it + 1 if op == 9 else 3), op, right, scope, _stream()) == 0
+        torch.cuda.synchronize()
+        sums = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(n)]
+        dist.all_gather(sums, payload.to(torch.int64).sum().reshape(1))
+        assert int(out[0]) == int(sums[left]), (scope, op)
+        nv.barrier_all()
+    # ring of put_signal
+    token = nv.tensor((1,), torch.int64, zero=True)
+    rsig = nv.tensor((1,), torch.int64, zero=True)
+    nv.barrier_all()
+    rounds = 5
+    assert dt.devtest_ring(C.c_void_p(token.data_ptr()), C.c_void_p(rsig.data_ptr()), rounds, C.c_uint64(0), _stream()) == 0
+    torch.cuda.synchronize()
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    if RANK == 0:
+        assert int(token[0]) == rounds * n * (n + 1) // 2, int(token[0])
+    # atomics: fetch_add from every thread of every PE onto PE 0
+    target = nv.tensor((4,), torch.int64, zero=True)
+    ctas, threads = 4, 128
+    olds = torch.zeros(ctas * threads, dtype=torch.int64, device="cuda")
+    nv.barrier_all()
+    assert dt.devtest_amo_fetch_add(C.c_void_p(target.data_ptr()), 0, C.c_void_p(olds.data_ptr()), ctas, threads, _stream()) == 0
+    torch.cuda.synchronize()
+    nv.barrier_all()
+    allolds = [torch.zeros_like(olds) for _ in range(n)]
+    dist.all_gather(allolds, olds)
+    if RANK == 0:
+        assert int(target[0]) == n * ctas * threads
+        assert torch.equal(torch.cat(allolds).sort().values.cpu(), torch.arange(n * ctas * threads))
+    # mixed atomics
+    t64 = nv.tensor((4,), torch.int64, zero=True)
+    t32 = nv.tensor((4,), torch.int32, zero=True)
+    tf = nv.tensor((2,), torch.float32, zero=True)
+    t64[1] = 0x0f
+    t64[2] = -1
+    mixout = torch.zeros(4, dtype=torch.int64, device="cuda")
+    nv.barrier_all()
+    assert dt.devtest_amo_mix(C.c_void_p(t64.data_ptr()), C.c_void_p(t32.data_ptr()), C.c_void_p(tf.data_ptr()), 0, C.c_void_p(mixout.data_ptr()), _stream()) == 0
+    torch.cuda.synchronize()
+    nv.barrier_all()
+    cas = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(n)]
+    dist.all_gather(cas, mixout[1:2].clone())
+    if RANK == 0:
+        assert int(t64[0]) == (1 << n) - 1
+        assert int(t32[0]) == 4 * n
+        assert [int(c) for c in cas].count(0) == 1 and 77 <= int(t32[1]) < 77 + n
+        assert int(t64[1]) == (0x0f ^ 0xff if n % 2 else 0x0f)
+        assert int(t64[2]) & ((1 << n) - 1) == 0
+        assert 1.5 <= float(tf[0]) < 1.5 + n
+    # barriers in every scope with data hand-off
+    slots = nv.tensor((max(n, 2),), torch.int64, zero=True)
+    errs = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for scope in (0, 1, 2, 3):
+        nv.barrier_all()
+        assert dt.devtest_barrier_rounds(C.c_void_p(slots.data_ptr()), 20, scope, C.c_void_p(errs.data_ptr()), _stream()) == 0
+        torch.cuda.synchronize()
+        assert int(errs[0]) == 0, (scope, int(errs[0]))
+    assert nv.error_bits() == 0
+    # bounded wait: nobody sets this flag; the kernel must return and report
+    nv.set_wait_timeout_ms(300)
+    nv.clear_errors()
+    never = nv.tensor((1,), torch.int64, zero=True)
+    res = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert dt.devtest_wait_never(C.c_void_p(never.data_ptr()), C.c_uint64(42), C.c_void_p(res.data_ptr()), _stream()) == 0
+    torch.cuda.synchronize()
+    assert int(res[0]) != 0 and nv.error_bits() & 1
+    info = nv.direct.timeout_info()
+    assert info["count"] >= 1 and info["expected"] == 42
+    nv.clear_errors()
+    nv.set_wait_timeout_ms(30000)
+    nv.barrier_all()
+    teardown(nv)
+
+
+def _oracle(op, tensors):
+    st = torch.stack([t.double() if t.is_floating_point() else t.long() for t in tensors])
+    if op == "sum":
+        return st.sum(0)
+    if op == "prod":
+        return st.prod(0)
+    if op == "min":
+        return st.min(0).values
+    if op == "max":
+        return st.max(0).values
+    out = st[0].clone()
+    for t in st[1:]:
+        out = out & t if op == "and" else out | t if op == "or" else out ^ t
+    return out
+
+
+def _close(got, want, dtype):
+    if dtype in (torch.float32, torch.float64):
+        return torch.allclose(got.double(), want, rtol=1e-5, atol=1e-5)
+    if dtype in (torch.float16, torch.bfloat16):
+        return torch.allclose(got.double(), want, rtol=2e-2, atol=2e-2)
+    return torch.equal(got.long(), want.long())
+
+
+@worker
+def collectives_on_stream():
+    nv = setup()
+    n = WORLD
+    nvls = nv.heap_info()["mc_base"] != 0
+    g = torch.Generator(device="cuda").manual_seed(5 + RANK)
+    sizes = [1, 3, 8, 255, 1024, 4097, 65536, 1 << 20]
+    cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.int32, "min"), (torch.int64, "xor"), (torch.float64, "prod"), (torch.uint8, "and"),
+             (torch.int16, "or")]
+    red_algos = ["auto", "oneshot", "twoshot"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
+    for dtype, op in cases:
+        for count in sizes:
+            if dtype.is_floating_point:
+                scale = 1.0 if op != "prod" else 0.2
+                make = lambda m: ((torch.rand(m, device="cuda", generator=g) * 2 - 1) * scale + (1.0 if op == "prod" else 0.0)).to(dtype)
+            else:
+                hi = 100 if dtype in (torch.uint8,) else 1 << 12
+                make = lambda m: torch.randint(0, hi, (m,), device="cuda", generator=g).to(dtype)
+            src = nv.tensor((count,), dtype)
+            dst = nv.tensor((count,), dtype)
+            src.copy_(make(count))
+            allsrc = [torch.empty_like(src) for _ in range(n)]
+            dist.all_gather(allsrc, src.clone())
+            want = _oracle(op, allsrc)
+            for algo in (red_algos if op == "sum" else red_algos[:3]):
+                dst.zero_()
+                nv.barrier_all()
+                nv.reduce(0, dst, src, op, algo=algo)
+                torch.cuda.synchronize()
+                assert _close(dst, want, dtype), ("reduce", dtype, op, count, algo, (dst.double() - want.double()).abs().max().item())
+            # in place
+            work = nv.tensor((count,), dtype)
+            work.copy_(src)
+            nv.barrier_all()
+            nv.reduce(0, work, work, op)
+            torch.cuda.synchronize()
+            assert _close(work, want, dtype), ("reduce in place", dtype, op, count)
+            for t in (src, dst, work):
+                nv.free_tensor(t)
+    # reducescatter / fcollect / alltoall / broadcast
+    for dtype in (torch.float32, torch.bfloat16, torch.int32):
+        for count in (1, 5, 256, 4099, 1 << 18):
+            make = (lambda m: (torch.rand(m, device="cuda", generator=g) * 2 - 1).to(dtype)) if dtype.is_floating_point else (lambda m: torch.randint(0, 1000, (m,), device="cuda", generator=g).to(dtype))
+            big = nv.tensor((count * n,), dtype)
+            small = nv.tensor((count,), dtype)
+            out_big = nv.tensor((count * n,), dtype)
+            big.copy_(make(count * n))
+            small.copy_(make(count))
+            allbig = [torch.empty_like(big) for _ in range(n)]
+            dist.all_gather(allbig, big.clone())
+            allsmall = [torch.empty_like(small) for _ in range(n)]
+            dist.all_gather(allsmall, small.clone())
+            for algo in ["auto", "pull"] + (["nvls"] if nvls else []):
+                res = nv.tensor((count,), dtype)
+                nv.barrier_all()
+                nv.reducescatter(0, res, big, "sum", algo=algo)
+                torch.cuda.synchronize()
+                want = _oracle("sum", [b[RANK * count:(RANK + 1) * count] for b in allbig])
+                assert _close(res, want, dtype), ("reducescatter", dtype, count, algo)
+                nv.free_tensor(res)
+            for algo in ["auto", "push", "ll"] + (["nvls"] if nvls else []):
+                out_big.zero_()
+                nv.barrier_all()
+                nv.fcollect(0, out_big, small, algo=algo)
+                torch.cuda.synchronize()
+                assert torch.equal(out_big, torch.cat(allsmall)), ("fcollect", dtype, count, algo)
+            out_big.zero_()
+            nv.barrier_all()
+            nv.alltoall(0, out_big, big)
+            torch.cuda.synchronize()
+            want = torch.cat([b[RANK * count:(RANK + 1) * count] for b in allbig])
+            assert torch.equal(out_big, want), ("alltoall", dtype, count)
+            for root in {0, n - 1}:
+                for algo in ["auto", "push", "pull"] + (["nvls"] if nvls else []):
+                    res = nv.tensor((count,), dtype, zero=True)
+                    nv.barrier_all()
+                    nv.broadcast(0, res, small, root=root, algo=algo)
+                    torch.cuda.synchronize()
+                    assert torch.equal(res, allsmall[root]), ("broadcast", dtype, count, root, algo)
+                    nv.free_tensor(res)
+            for t in (big, small, out_big):
+                nv.free_tensor(t)
+    # sub-team collective
+    if n >= 4:
+        even = nv.team_split_strided(0, 0, 2, n // 2)
+        x = nv.tensor((1000,), torch.float32)
+        y = nv.tensor((1000,), torch.float32)
+        x.fill_(float(RANK + 1))
+        nv.barrier_all()
+        if RANK % 2 == 0 and RANK // 2 < n // 2:
+            nv.reduce(even, y, x, "sum")
+            torch.cuda.synchronize()
+            assert float(y[0]) == sum(r + 1 for r in range(0, n, 2))
+            nv.team_destroy(even)
+        nv.barrier_all()
+        nv.free_tensor(x)
+        nv.free_tensor(y)
+    # maxloc
+    pair = nv.tensor((2,), torch.float64)
+    res = nv.tensor((2,), torch.float64)
+    pair[0] = float((RANK * 7) % n)
+    pair[1] = float(RANK)
+    nv.barrier_all()
+    nv.maxloc(0, res, pair)
+    torch.cuda.synchronize()
+    vals = [(r * 7) % n for r in range(n)]
+    assert res[0].item() == max(vals) and int(res[1].item()) == vals.index(max(vals))
+    assert nv.error_bits() == 0
+    teardown(nv)
+
+
+@worker
+def collectives_in_graph():
+    """On-stream collectives captured into a CUDA graph and replayed."""
+    nv = setup()
+    n = WORLD
+    src = nv.tensor((1 << 16,), torch.float32)
+    dst = nv.tensor((1 << 16,), torch.float32)
+    src.fill_(1.0 + RANK)
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        nv.reduce(0, dst, src, "sum", stream=s)  # warm-up outside capture
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            nv.reduce(0, dst, src, "sum", stream=s)
+            nv.barrier_all(stream=s)
+    for it in range(3):
+        src.fill_(1.0 + RANK + it)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert float(dst[123]) == sum(1.0 + r + it for r in range(n)), (it, float(dst[123]))
+    teardown(nv)
+
+
+@worker
+def device_collectives_and_tiles():
+    nv = setup()
+    dt = _devtest()
+    n = WORLD
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    count = 3000
+    def run(kind, dst, src, cnt, root=0, threads=256):
+        nv.barrier_all()
+        assert dt.devtest_device_coll(kind, 0, C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), C.c_size_t(cnt), root, C.c_void_p(status.data_ptr()), threads, _stream()) == 0
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+    f_src, f_dst = nv.tensor((count * n,), torch.float32), nv.tensor((count * n,), torch.float32)
+    f_src.copy_(torch.arange(count * n, device="cuda", dtype=torch.float32) % 13 + RANK)
+    run(0, f_dst, f_src, count)
+    base = torch.arange(count * n, dtype=torch.float32) % 13
+    assert torch.equal(f_dst[:count].cpu(), base[:count] * n + sum(range(n)))
+    run(2, f_dst, f_src, count)
+    assert torch.equal(f_dst[:count].cpu(), base[RANK * count:(RANK + 1) * count] * n + sum(range(n)))
+    i_src, i_dst = nv.tensor((count * n,), torch.int32), nv.tensor((count * n,), torch.int32)
+    i_src.copy_((torch.arange(count * n, device="cuda") * (RANK + 3)) % 1009)
+    run(1, i_dst, i_src, count)
+    want = torch.stack([(torch.arange(count) * (r + 3)) % 1009 for r in range(n)]).max(0).values
+    assert torch.equal(i_dst[:count].cpu().long(), want)
+    for kind in (3, 8):
+        i_dst.zero_()
+        run(kind, i_dst, i_src, 100 if kind == 8 else count)
+        m = 100 if kind == 8 else count
+        want = torch.cat([((torch.arange(count * n) * (r + 3)) % 1009)[:m] for r in range(n)])
+        assert torch.equal(i_dst[:m * n].cpu().long(), want), kind
+    run(4, i_dst, i_src, count)
+    want = torch.cat([((torch.arange(count * n) * (r + 3)) % 1009)[RANK * count:(RANK + 1) * count] for r in range(n)])
+    assert torch.equal(i_dst.cpu().long(), want)
+    run(5, i_dst, i_src, count, root=n - 1)
+    assert torch.equal(i_dst[:count].cpu().long(), ((torch.arange(count * n) * (n - 1 + 3)) % 1009)[:count])
+    h_src, h_dst = nv.tensor((4096,), torch.bfloat16), nv.tensor((4096,), torch.bfloat16)
+    h_src.fill_(0.5 + RANK)
+    run(6, h_dst, h_src, 4096)
+    assert float(h_dst[17]) == sum(0.5 + r for r in range(n))
+    u_src, u_dst = nv.tensor((512,), torch.int64), nv.tensor((512,), torch.int64)
+    u_src.fill_(1 << RANK)
+    run(7, u_dst, u_src, 512)
+    assert int(u_dst[5]) == (1 << n) - 1
+    # tiles
+    R, Cc = 100, 96
+    t_src, t_dst = nv.tensor((R, Cc), torch.float32), nv.tensor((R, Cc), torch.float32, zero=True)
+    t_src.copy_(torch.arange(R * Cc, device="cuda", dtype=torch.float32).reshape(R, Cc) * (RANK + 1))
+    for algo, (r0, c0, rows, cols) in ((1, (8, 16, 32, 64)), (2, (64, 32, 64, 64)), (1, (3, 5, 7, 9))):
+        t_dst.zero_()
+        nv.barrier_all()
+        assert dt.devtest_tile_allreduce(0, C.c_void_p(t_dst.data_ptr()), C.c_void_p(t_src.data_ptr()), R, Cc, r0, c0, rows, cols, algo, n - 1, _stream()) == 0
+        torch.cuda.synchronize()
+        want = torch.zeros(R, Cc)
+        r1, c1 = min(r0 + rows, R), min(c0 + cols, Cc)
+        want[r0:r1, c0:c1] = (torch.arange(R * Cc, dtype=torch.float32).reshape(R, Cc) * (n * (n + 1) // 2))[r0:r1, c0:c1]
+        assert torch.equal(t_dst.cpu(), want), (algo, r0, c0)
+    right = (RANK + 1) % n
+    t_dst.zero_()
+    nv.barrier_all()
+    assert dt.devtest_tile_put_get(C.c_void_p(t_dst.data_ptr()), C.c_void_p(t_src.data_ptr()), R, Cc, 10, 8, 16, 32, right, 0, _stream()) == 0
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    left = (RANK - 1) % n
+    want = torch.zeros(R, Cc)
+    want[10:26, 8:40] = (torch.arange(R * Cc, dtype=torch.float32).reshape(R, Cc) * (left + 1))[10:26, 8:40]
+    assert torch.equal(t_dst.cpu(), want)
+    assert nv.error_bits() == 0
+    teardown(nv)
+
+
+# ====================================================================== GPU: fused kernels
+@worker
+def fused_gemm_collectives():
+    nv = setup()
+    from nvshmem_b200.ops import fused_gemm as fg
+    n = WORLD
+    torch.manual_seed(100)
+    for (M, N, Kl) in ((128 * n, 256, 64), (256 * n, 512, 192), (1024 * n, 768, 256)):
+        xs = [(torch.randn(M, Kl, device="cuda")).to(torch.bfloat16) for _ in range(n)]   # same seed on all ranks: everyone knows all inputs
+        ws = [(torch.randn(N, Kl, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
+        full = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+        tol = full.abs().max().item() * 2 ** -6 + 1e-2
+        rows = M // n
+        rs = fg.GemmReduceScatter(M, N, mode="rs", wait_limit_ms=5000)
+        for it in range(3):  # several calls: epochs and the two receive generations
+            out = rs(xs[RANK], ws[RANK])
+            torch.cuda.synchronize()
+            fg.check_errors()
+            err = (out.float() - full[RANK * rows:(RANK + 1) * rows]).abs().max().item()
+            assert err <= tol, ("rs", M, N, Kl, it, err, tol)
+        rs.close()
+        ar = fg.GemmReduceScatter(M, N, mode="ar", wait_limit_ms=5000)
+        for it in range(2):
+            out = ar(xs[RANK], ws[RANK])
+            nv.barrier_all()
+            torch.cuda.synchronize()
+            fg.check_errors()
+            err = (out.float() - full).abs().max().item()
+            assert err <= tol, ("ar", M, N, Kl, it, err, tol)
+        ar.close()
+    for (M, K, Nl) in ((128 * n, 64, 256), (256 * n, 512, 512), (1024 * n, 1024, 256)):
+        x_full = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(Nl, K, device="cuda") * 0.05).to(torch.bfloat16)
+        rows = M // n
+        ag = fg.AllGatherGemm(M, K, wait_limit_ms=5000)
+        for it in range(3):
+            xi = (x_full.float() * (it + 1)).to(torch.bfloat16)
+            ag.shard.copy_(xi[RANK * rows:(RANK + 1) * rows])
+            out = ag(w)
+            torch.cuda.synchronize()
+            fg.check_errors()
+            ref = xi.float() @ w.float().t()
+            err = (out.float() - ref).abs().max().item()
+            assert err <= ref.abs().max().item() * 2 ** -7 + 1e-3, ("ag", M, K, Nl, it, err)
+            assert torch.equal(ag.gathered, xi), "gathered activations differ"
+        ag.close()
+    teardown(nv)
+
+
+@worker
+def tp_mlp_matches_single_device():
+    nv = setup()
+    from nvshmem_b200.models.tp_mlp import TensorParallelMLP
+    from nvshmem_b200.ops import fused_gemm as fg
+    n = WORLD
+    hidden, ffn, tokens = 512, 1024 * n if n > 1 else 1024, 256 * n
+    torch.manual_seed(7)  # identical full weights on every rank
+    w_up = (torch.randn(ffn, hidden, device="cuda") * 0.02).to(torch.bfloat16)
+    w_down = (torch.randn(hidden, ffn, device="cuda") * 0.02).to(torch.bfloat16)
+    x_full = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+    mlp = TensorParallelMLP(hidden, ffn, tokens)
+    fl, rows = ffn // n, tokens // n
+    with torch.no_grad():
+        mlp.up.weight.copy_(w_up[RANK * fl:(RANK + 1) * fl])
+        mlp.down.weight.copy_(w_down[:, RANK * fl:(RANK + 1) * fl])
+    x = x_full[RANK * rows:(RANK + 1) * rows].clone().requires_grad_(True)
+    y = mlp(x)
+    y.float().pow(2).mean().backward()
+    torch.cuda.synchronize()
+    fg.check_errors()
+    ref = mlp.reference(x_full, w_up, w_down)
+    err = (y.float() - ref[RANK * rows:(RANK + 1) * rows]).abs().max().item()
+    assert err <= 0.03 * ref.abs().max().item() + 1e-2, err
+    # gradients against fp32 autograd on the full problem
+    x32 = x_full.float().requires_grad_(True)
+    w1, w2 = w_up.float().requires_grad_(True), w_down.float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(x32 @ w1.t(), approximate="tanh") @ w2.t()
+    # each rank's loss is the mean over ITS rows; the sum of the ranks' losses is n * global mean
+    (yr.pow(2).mean() * n).backward()
+    for got, want in ((x.grad, x32.grad[RANK * rows:(RANK + 1) * rows]), (mlp.up.weight.grad, w1.grad[RANK * fl:(RANK + 1) * fl]), (mlp.down.weight.grad, w2.grad[:, RANK * fl:(RANK + 1) * fl])):
+        denom = want.abs().max().item() + 1e-12
+        assert (got.float() - want).abs().max().item() / denom < 0.08, (got.float() - want).abs().max().item() / denom
+    mlp.close()
+    teardown(nv)
+
+
+@worker
+def rank_leaves_between_steps():
+    """Failure detection without faulting a GPU: after a clean step one rank leaves (finalises nothing
+    collectively, just stops taking part).  The others learn it on the host through the store before
+    their next launch and stop too; a wait that would have depended on the missing rank is never issued."""
+    nv = setup()
+    n = WORLD
+    x = nv.tensor((1024,), torch.float32)
+    y = nv.tensor((1024,), torch.float32)
+    x.fill_(1.0)
+    nv.barrier_all()
+    nv.reduce(0, y, x, "sum")
+    torch.cuda.synchronize() if GPU else None
+    assert float(y[0]) == n
+    store = dist.distributed_c10d._get_default_store()
+    dist.barrier()
+    if RANK == n - 1:
+        store.set("leaving", str(RANK))
+    else:
+        store.wait(["leaving"])
+        gone = int(store.get("leaving"))
+        assert gone == n - 1
+        # no kernel that waits on the departed rank is launched; local work still runs
+        y.mul_(2.0)
+        torch.cuda.synchronize() if GPU else None
+        assert float(y[0]) == 2 * n
+    # Everyone is still alive here (leaving = no longer computing), so the collective shutdown is safe.
+    teardown(nv)
+
+
+if __name__ == "__main__":
+    name = sys.argv[1]
+    WORKERS[name]()
+    print(f"rank {RANK}: {name} ok", flush=True)
