@@ -177,6 +177,17 @@ __global__ void k_tile_put_get(float* dst, float* src, int R, int C, int r0, int
 }
 
 extern "C" {
+// With lazy module loading the first launch of a kernel may have to wait for running kernels to
+// finish.  Tests that start a waiting kernel before the kernel that satisfies it call this first.
+int devtest_preload(void) {
+  cudaFuncAttributes a;
+  const void* fns[] = {(const void*)k_put, (const void*)k_get, (const void*)k_typed, (const void*)k_put_signal, (const void*)k_signal_wait_sum, (const void*)k_ring,
+                       (const void*)k_wait_never, (const void*)k_amo_fetch_add, (const void*)k_amo_mix, (const void*)k_barrier_rounds, (const void*)k_device_coll,
+                       (const void*)k_tile_allreduce, (const void*)k_tile_put_get};
+  int bad = 0;
+  for (const void* f : fns) bad |= cudaFuncGetAttributes(&a, f) != cudaSuccess;
+  return bad;
+}
 int devtest_put(void* dst, const void* src, size_t bytes, int pe, int scope, int nbi, cudaStream_t s) {
   k_put<<<1, 256, 0, s>>>((char*)dst, (const char*)src, bytes, pe, scope, nbi);
   return LAUNCH_OK();

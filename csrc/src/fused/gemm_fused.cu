@@ -62,6 +62,7 @@ struct alignas(64) FusedParams {
   uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
   int* error_flag;
   uint64_t epoch, wait_limit_ns, ag_unit_bytes;
+  uint32_t ag_piece_bytes;  // size of one bulk copy of the sender (16-byte multiple, at most COMM_PIECE)
   int M, N, K, rank, npes, mode, n_comm, ag_parts, ag_tiles_per_unit;
 };
 
@@ -114,7 +115,8 @@ __device__ void ag_sender(const FusedParams& p, uint8_t* smem, uint64_t* bars, v
   if (threadIdx.x != 0) return;
   const int unit = blockIdx.x;  // one unit of my shard per sender CTA
   const size_t unit_off = (size_t)unit * p.ag_unit_bytes;
-  const int pieces = (int)(p.ag_unit_bytes / COMM_PIECE);
+  const uint32_t PIECE = p.ag_piece_bytes;
+  const int pieces = (int)(p.ag_unit_bytes / PIECE);
   const int tmr = (p.M / p.npes) / BM;
   uint32_t phase_bits = 0;  // one parity bit per ring slot
   for (int o = 1; o < p.npes && !*abort_flag; ++o) {
@@ -123,21 +125,21 @@ __device__ void ag_sender(const FusedParams& p, uint8_t* smem, uint64_t* bars, v
     char* dst = p.ag_dst[peer] + unit_off;
     const int ahead = pieces < COMM_AHEAD ? pieces : COMM_AHEAD;
     for (int q = 0; q < ahead; ++q) {
-      mbar_expect_tx(&bars[q % COMM_BUFS], COMM_PIECE);
-      bulk_load(smem + (q % COMM_BUFS) * COMM_PIECE, src + (size_t)q * COMM_PIECE, COMM_PIECE, &bars[q % COMM_BUFS]);
+      mbar_expect_tx(&bars[q % COMM_BUFS], PIECE);
+      bulk_load(smem + (q % COMM_BUFS) * COMM_PIECE, src + (size_t)q * PIECE, PIECE, &bars[q % COMM_BUFS]);
     }
     for (int q = 0; q < pieces; ++q) {
       const int nxt = q + COMM_AHEAD;
       if (nxt < pieces) {
         // Ring slot of piece `nxt` was last used by piece nxt-COMM_BUFS, stored COMM_BUFS-COMM_AHEAD iterations ago.
         bulk_wait_read<COMM_BUFS - COMM_AHEAD - 1>();
-        mbar_expect_tx(&bars[nxt % COMM_BUFS], COMM_PIECE);
-        bulk_load(smem + (nxt % COMM_BUFS) * COMM_PIECE, src + (size_t)nxt * COMM_PIECE, COMM_PIECE, &bars[nxt % COMM_BUFS]);
+        mbar_expect_tx(&bars[nxt % COMM_BUFS], PIECE);
+        bulk_load(smem + (nxt % COMM_BUFS) * COMM_PIECE, src + (size_t)nxt * PIECE, PIECE, &bars[nxt % COMM_BUFS]);
       }
       const int slot = q % COMM_BUFS;
       if (!mbar_wait(&bars[slot], (phase_bits >> slot) & 1, p.wait_limit_ns, abort_flag)) break;
       phase_bits ^= 1u << slot;
-      bulk_store(dst + (size_t)q * COMM_PIECE, smem + slot * COMM_PIECE, COMM_PIECE);
+      bulk_store(dst + (size_t)q * PIECE, smem + slot * COMM_PIECE, PIECE);
       bulk_commit();
     }
     bulk_wait<0>();  // every byte of the unit has been written to the peer
@@ -458,7 +460,11 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
     const size_t shard_bytes = (size_t)rows_per_pe * a->K * 2;
     p.n_comm = n_comm;
     p.ag_unit_bytes = shard_bytes / n_comm;
-    if (p.ag_unit_bytes % COMM_PIECE) return BSHMEM_FUSED_ERR_SHAPE;
+    // Largest power-of-two piece (16 B .. COMM_PIECE) that divides a unit.
+    uint32_t piece = COMM_PIECE;
+    while (piece > 16 && p.ag_unit_bytes % piece) piece >>= 1;
+    if (p.ag_unit_bytes % piece) return BSHMEM_FUSED_ERR_SHAPE;
+    p.ag_piece_bytes = piece;
     p.ag_parts = n_comm >= tmr ? n_comm / tmr : 1;
     p.ag_tiles_per_unit = n_comm >= tmr ? 1 : tmr / n_comm;
     p.ag_src = (const char*)a->A + (size_t)a->rank * shard_bytes;

@@ -23,6 +23,7 @@ def run_workers(func: str, nprocs: int, gpu: bool = False, env: dict | None = No
         e = dict(os.environ)
         e.update({"RANK": str(rank), "WORLD_SIZE": str(nprocs), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port),
                   "BSHMEM_TEST_GPU": "1" if gpu else "0", "PYTHONPATH": ROOT + os.pathsep + e.get("PYTHONPATH", "")})
+        e.setdefault("NVSHMEM_WAIT_TIMEOUT_MS", "5000")  # a lost peer costs seconds, not minutes
         if not gpu:
             e["CUDA_VISIBLE_DEVICES"] = ""
             e.setdefault("NVSHMEM_SYMMETRIC_SIZE", "16M")
@@ -30,16 +31,28 @@ def run_workers(func: str, nprocs: int, gpu: bool = False, env: dict | None = No
             e.update(env)
         procs.append(subprocess.Popen([sys.executable, "-m", "tests.workers", func] + (args or []), cwd=ROOT, env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     deadline = time.time() + timeout
+    # Fail fast: once a rank has exited with an error the others can only time out, so give them a
+    # short grace period and stop exactly the children started here.
+    first_failure = None
+    while True:
+        codes = [p.poll() for p in procs]
+        if all(c is not None for c in codes):
+            break
+        now = time.time()
+        if first_failure is None and any(c not in (None, 0) for c in codes):
+            first_failure = now
+        if now > deadline or (first_failure is not None and now - first_failure > 15):
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+            break
+        time.sleep(0.2)
     outs, codes = [], []
     for p in procs:
-        try:
-            out, _ = p.communicate(timeout=max(1, deadline - time.time()))
-        except subprocess.TimeoutExpired:
-            p.kill()  # exactly the child we started
-            out, _ = p.communicate()
-            out += "\n[killed: timeout]"
+        out, _ = p.communicate()
         outs.append(out)
         codes.append(p.returncode)
     if not expect_fail:
-        assert all(c == 0 for c in codes), "worker failed:\n" + "\n".join(f"--- rank {i} rc={c}\n{o[-3000:]}" for i, (c, o) in enumerate(zip(codes, outs)))
+        order = sorted(range(nprocs), key=lambda i: (codes[i] in (0, -9), i))  # the rank that failed by itself first
+        assert all(c == 0 for c in codes), "worker failed:\n" + "\n".join(f"--- rank {i} rc={codes[i]}\n{outs[i][-2500:]}" for i in order)
     return codes, outs

@@ -35,7 +35,7 @@ def test_device_rma():
 
 @need2
 def test_device_signals_atomics_barriers():
-    run_workers("device_signals_amo_barrier", NG, gpu=True, env=NO_NVLS, timeout=600)
+    run_workers("device_signals_amo_barrier", NG, gpu=True, env=NO_NVLS, timeout=240)
 
 
 @need2

@@ -42,6 +42,11 @@ def teardown(nv):
     dist.destroy_process_group()
 
 
+def mark(msg):
+    """Progress line (the harness shows the tail of each rank's output when a worker fails)."""
+    print(f"[rank {RANK}] {msg}", flush=True)
+
+
 def gather_objects(obj):
     out = [None] * WORLD
     dist.all_gather_object(out, obj)
@@ -275,6 +280,7 @@ def _devtest():
     from nvshmem_b200.bindings import host as H
     H.load()
     lib = C.CDLL(str(H.lib_path("libbshmem_devtest.so")))
+    assert lib.devtest_preload() == 0
     return lib
 
 
@@ -366,7 +372,7 @@ def device_signals_amo_barrier():
     side = torch.cuda.Stream()
     for it, (scope, op) in enumerate([(0, 9), (1, 9), (2, 9), (2, 10)]):
         payload = torch.randint(0, 1 << 20, (words,), dtype=torch.int32, device="cuda")
-        want_val = it + 1 if op == 9 else 4 + 3
+        want_val = it + 1 if op == 9 else 3 + 3
         # consumer first, on a side stream: it spins (bounded) until the producer's signal lands
         with torch.cuda.stream(side):
             assert dt.devtest_signal_wait_sum(C.c_void_p(data.data_ptr()), C.c_size_t(words), C.c_void_p(sig.data_ptr()), 5, C.c_uint64(want_val), C.c_void_p(out.data_ptr()),
@@ -378,6 +384,7 @@ def device_signals_amo_barrier():
         dist.all_gather(sums, payload.to(torch.int64).sum().reshape(1))
         assert int(out[0]) == int(sums[left]), (scope, op)
         nv.barrier_all()
+    mark('signals ok')
     # ring of put_signal
     token = nv.tensor((1,), torch.int64, zero=True)
     rsig = nv.tensor((1,), torch.int64, zero=True)
@@ -389,6 +396,7 @@ def device_signals_amo_barrier():
     torch.cuda.synchronize()
     if RANK == 0:
         assert int(token[0]) == rounds * n * (n + 1) // 2, int(token[0])
+    mark('ring ok')
     # atomics: fetch_add from every thread of every PE onto PE 0
     target = nv.tensor((4,), torch.int64, zero=True)
     ctas, threads = 4, 128
@@ -402,6 +410,7 @@ def device_signals_amo_barrier():
     if RANK == 0:
         assert int(target[0]) == n * ctas * threads
         assert torch.equal(torch.cat(allolds).sort().values.cpu(), torch.arange(n * ctas * threads))
+    mark('fetch_add ok')
     # mixed atomics
     t64 = nv.tensor((4,), torch.int64, zero=True)
     t32 = nv.tensor((4,), torch.int32, zero=True)
@@ -422,6 +431,7 @@ def device_signals_amo_barrier():
         assert int(t64[1]) == (0x0f ^ 0xff if n % 2 else 0x0f)
         assert int(t64[2]) & ((1 << n) - 1) == 0
         assert 1.5 <= float(tf[0]) < 1.5 + n
+    mark('mixed atomics ok')
     # barriers in every scope with data hand-off
     slots = nv.tensor((max(n, 2),), torch.int64, zero=True)
     errs = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -430,6 +440,7 @@ def device_signals_amo_barrier():
         assert dt.devtest_barrier_rounds(C.c_void_p(slots.data_ptr()), 20, scope, C.c_void_p(errs.data_ptr()), _stream()) == 0
         torch.cuda.synchronize()
         assert int(errs[0]) == 0, (scope, int(errs[0]))
+        mark(f'barrier scope {scope} ok')
     assert nv.error_bits() == 0
     # bounded wait: nobody sets this flag; the kernel must return and report
     nv.set_wait_timeout_ms(300)
@@ -463,6 +474,14 @@ def _oracle(op, tensors):
     return out
 
 
+def _gather(t):
+    """all_gather through a byte view: NCCL has no 16-bit integer type."""
+    raw = t.clone().contiguous().view(torch.uint8)
+    outs = [torch.empty_like(raw) for _ in range(WORLD)]
+    dist.all_gather(outs, raw)
+    return [o.view(t.dtype).view(t.shape) for o in outs]
+
+
 def _close(got, want, dtype):
     if dtype in (torch.float32, torch.float64):
         return torch.allclose(got.double(), want, rtol=1e-5, atol=1e-5)
@@ -492,8 +511,7 @@ def collectives_on_stream():
             src = nv.tensor((count,), dtype)
             dst = nv.tensor((count,), dtype)
             src.copy_(make(count))
-            allsrc = [torch.empty_like(src) for _ in range(n)]
-            dist.all_gather(allsrc, src.clone())
+            allsrc = _gather(src)
             want = _oracle(op, allsrc)
             for algo in (red_algos if op == "sum" else red_algos[:3]):
                 dst.zero_()
@@ -519,10 +537,8 @@ def collectives_on_stream():
             out_big = nv.tensor((count * n,), dtype)
             big.copy_(make(count * n))
             small.copy_(make(count))
-            allbig = [torch.empty_like(big) for _ in range(n)]
-            dist.all_gather(allbig, big.clone())
-            allsmall = [torch.empty_like(small) for _ in range(n)]
-            dist.all_gather(allsmall, small.clone())
+            allbig = _gather(big)
+            allsmall = _gather(small)
             for algo in ["auto", "pull"] + (["nvls"] if nvls else []):
                 res = nv.tensor((count,), dtype)
                 nv.barrier_all()
