@@ -1,0 +1,373 @@
+// Expert-parallel MoE dispatch and combine for sm_100a over NVLink peer memory.
+//
+// dispatch (one cooperative kernel, persistent CTAs of 256 threads):
+//   A  histogram of the K expert ids of every token (shared-memory bins, then global atomics)
+//   B  CTA 0 stores this PE's E counts into row `rank` of every PE's count matrix and runs a
+//      cross-PE barrier; a grid barrier releases the other CTAs
+//   C  every CTA derives, from the complete [npes, E] matrix, the first row of each expert's
+//      segment that belongs to this PE as a source: rows of a receive buffer are ordered by
+//      local expert, then by source PE, so the expert GEMMs read contiguous groups
+//   D  one CTA per token: the row is staged in shared memory once (and quantised once to fp8 with
+//      1x128 fp32 scales when asked), each of its K slots takes the next row of its segment with an
+//      atomic cursor, and the row is pushed with 16-byte stores to the owning PE
+//   E  grid barrier, then a cross-PE barrier: when the kernel ends on one PE, every PE's rows have landed
+// combine (one cooperative kernel): cross-PE barrier on entry (expert outputs are final), then one CTA
+// per token pulls its K rows with 16-byte loads from the owners, multiplies by the routing weights in
+// fp32, rounds once to bf16; a cross-PE barrier on exit lets the owners reuse their buffers.
+// All waits are bounded and report through `error_flag`; nothing traps.
+// (reference for the capability: examples/moe_shuffle.cu, an fp32 dispatch-only all-to-all-v)
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/bshmem/moe.h"
+
+namespace bshmem {
+namespace moe {
+
+constexpr int THREADS = 256;
+
+struct Scratch {                 // local device memory, zeroed by the host before each dispatch
+  unsigned int grid_bar;         // arrivals at grid barriers (monotonic within a launch)
+  unsigned int pad[63];
+  int send_count[BSHMEM_MOE_MAX_EXPERTS];   // pairs this PE sends to each expert
+  int cursor[BSHMEM_MOE_MAX_EXPERTS];       // next free position inside my segment of each expert
+};
+
+struct DispatchParams {
+  bshmem_moe_dispatch_args_t a;
+  uint64_t wait_limit_ns;
+};
+struct CombineParams {
+  bshmem_moe_combine_args_t a;
+  uint64_t wait_limit_ns;
+};
+
+__device__ __forceinline__ uint64_t timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Grid barrier over co-resident CTAs (cooperative launch).  `phase` counts barriers of this launch; the
+// counter starts at zero.  Returns false after the wait bound.
+__device__ bool grid_barrier(unsigned* counter, unsigned& phase, uint64_t limit_ns, int* error_flag) {
+  __shared__ int ok_s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ++phase;
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const unsigned target = phase * gridDim.x;
+    const uint64_t start = timer_ns();
+    int ok = 1;
+    unsigned spins = 0;
+    while (ld_acquire_gpu_u32(counter) < target) {
+      if ((++spins & 63) == 0 && timer_ns() - start > limit_ns) {
+        atomicOr(error_flag, BSHMEM_MOE_ERRBIT_TIMEOUT);
+        ok = 0;
+        break;
+      }
+    }
+    ok_s = ok;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+// Cross-PE barrier run by the first `npes` threads of one CTA: store `value` into slot `rank` of row
+// `row` of every PE's flag block, wait until every slot of my row holds at least `value`.
+__device__ bool pe_barrier(uint64_t* const* flags, int row, int rank, int npes, uint64_t value, uint64_t limit_ns, int* error_flag) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < npes) {
+    const int q = threadIdx.x;
+    __threadfence_system();
+    if (q != rank) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flags[q] + row * npes + rank), "l"(value) : "memory");
+    if (q != rank) {
+      const uint64_t* mine = flags[rank] + row * npes + q;
+      const uint64_t start = timer_ns();
+      unsigned spins = 0;
+      while (ld_acquire_sys_u64(mine) < value) {
+        if ((++spins & 31) == 0) {
+          if (timer_ns() - start > limit_ns) {
+            atomicOr(error_flag, BSHMEM_MOE_ERRBIT_TIMEOUT);
+            ok_s = 0;
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant__ DispatchParams P) {
+  const bshmem_moe_dispatch_args_t& a = P.a;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int T = a.T, H = a.H, K = a.K, E = a.E, npes = a.npes, rank = a.rank;
+  const int EL = E / npes;
+  Scratch* sc = (Scratch*)a.scratch;
+  unsigned phase = 0;
+  int* s_bins = (int*)smem;                     // [E] histogram bins, later my segment starts
+  __shared__ int s_row[BSHMEM_MOE_MAX_TOPK], s_dest[BSHMEM_MOE_MAX_TOPK];
+
+  // ---- A: histogram
+  for (int e = threadIdx.x; e < E; e += THREADS) s_bins[e] = 0;
+  __syncthreads();
+  for (long i = (long)blockIdx.x * THREADS + threadIdx.x; i < (long)T * K; i += (long)gridDim.x * THREADS) {
+    const int e = a.topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&s_bins[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += THREADS)
+    if (s_bins[e]) atomicAdd(&sc->send_count[e], s_bins[e]);
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+
+  // ---- B: publish my counts to every PE, cross-PE barrier
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < E * npes; i += THREADS) {
+      const int q = i / E, e = i % E;
+      a.counts[q][rank * E + e] = sc->send_count[e];
+    }
+    __syncthreads();
+    pe_barrier(a.flags, 0, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
+  }
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+
+  // ---- C: where my rows start on each owner.  Rows of PE d's buffer: for le in [0, EL): for s in [0, npes): count[s][d*EL+le] rows.
+  const int* cm = a.counts[rank];
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += THREADS) {
+    const int d = e / EL, le = e % EL;
+    int start = 0;
+    for (int l2 = 0; l2 < le; ++l2)
+      for (int s = 0; s < npes; ++s) start += __ldcg(&cm[s * E + d * EL + l2]);
+    for (int s = 0; s < rank; ++s) start += __ldcg(&cm[s * E + e]);
+    s_bins[e] = start;
+  }
+  if (blockIdx.x == 0) {  // receiver-side description of my own buffer
+    for (int le = threadIdx.x; le <= EL; le += THREADS) {
+      int start = 0;
+      for (int l2 = 0; l2 < le; ++l2)
+        for (int s = 0; s < npes; ++s) start += __ldcg(&cm[s * E + rank * EL + l2]);
+      a.expert_offsets[le] = start;
+      if (le < EL && a.src_offsets) {
+        int run = start;
+        for (int s = 0; s < npes; ++s) {
+          a.src_offsets[le * npes + s] = run;
+          run += __ldcg(&cm[s * E + rank * EL + le]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- D: push rows
+  const int row_bytes = a.payload == BSHMEM_MOE_FP8_E4M3 ? H : H * 2;
+  const int nscale = H / BSHMEM_MOE_QUANT_BLOCK;
+  uint8_t* s_x = smem + ((E * 4 + 15) & ~15);          // bf16 row
+  uint8_t* s_q = s_x + H * 2;                          // fp8 row
+  float* s_scale = (float*)(s_q + H);                  // scales
+  const uint4* xg = (const uint4*)a.x;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int c = threadIdx.x; c < H / 8; c += THREADS) ((uint4*)s_x)[c] = xg[(size_t)t * (H / 8) + c];
+    if ((int)threadIdx.x < K) {
+      const int e = a.topk_idx[(size_t)t * K + threadIdx.x];
+      int row = -1, dest = 0;
+      if (e >= 0 && e < E) {
+        const int pos = atomicAdd(&sc->cursor[e], 1);
+        row = s_bins[e] + pos;
+        dest = e / EL;
+        if (row >= a.cap_rows) {
+          atomicOr(a.error_flag, BSHMEM_MOE_ERRBIT_OVERFLOW);
+          row = -1;
+        }
+      }
+      s_row[threadIdx.x] = row;
+      s_dest[threadIdx.x] = dest;
+      a.slot_map[(size_t)t * K + threadIdx.x] = row;
+    }
+    __syncthreads();
+    const uint8_t* payload = s_x;
+    if (a.payload == BSHMEM_MOE_FP8_E4M3) {
+      // one warp per 128-value block: 4 values per lane, absmax by shuffles, scale = amax / 448
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      for (int g = warp; g < nscale; g += THREADS / 32) {
+        const uint2 raw = ((const uint2*)s_x)[g * 32 + lane];
+        const float2 v01 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+        const float2 v23 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+        float amax = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float scale = fmaxf(amax, 1e-10f) / 448.0f;
+        const float inv = 1.0f / scale;
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v01.x * inv, v01.y * inv), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v23.x * inv, v23.y * inv), __NV_SATFINITE, __NV_E4M3);
+        ((uint32_t*)s_q)[g * 32 + lane] = (uint32_t)lo | ((uint32_t)hi << 16);
+        if (lane == 0) s_scale[g] = scale;
+      }
+      __syncthreads();
+      payload = s_q;
+    }
+    for (int j = 0; j < K; ++j) {
+      const int row = s_row[j];
+      if (row < 0) continue;
+      uint4* dst = (uint4*)((uint8_t*)a.recv_x[s_dest[j]] + (size_t)row * row_bytes);
+      for (int c = threadIdx.x; c < row_bytes / 16; c += THREADS) dst[c] = ((const uint4*)payload)[c];
+      if (a.payload == BSHMEM_MOE_FP8_E4M3) {
+        float* sd = a.recv_scale[s_dest[j]] + (size_t)row * nscale;
+        for (int c = threadIdx.x; c < nscale; c += THREADS) sd[c] = s_scale[c];
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- E: all my rows are out; meet every PE
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+  if (blockIdx.x == 0) pe_barrier(a.flags, 1, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
+}
+
+__global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant__ CombineParams P) {
+  const bshmem_moe_combine_args_t& a = P.a;
+  const int T = a.T, H = a.H, K = a.K, E = a.E, npes = a.npes, rank = a.rank;
+  const int EL = E / npes;
+  Scratch* sc = (Scratch*)a.scratch;
+  unsigned phase = 0;
+  __shared__ const uint8_t* s_src[BSHMEM_MOE_MAX_TOPK];
+  __shared__ float s_w[BSHMEM_MOE_MAX_TOPK];
+  if (blockIdx.x == 0) pe_barrier(a.flags, 2, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    if ((int)threadIdx.x < K) {
+      const int e = a.topk_idx[(size_t)t * K + threadIdx.x];
+      const int row = a.slot_map[(size_t)t * K + threadIdx.x];
+      const bool ok = e >= 0 && e < E && row >= 0;
+      s_src[threadIdx.x] = ok ? (const uint8_t*)a.y[e / EL] + (size_t)row * H * 2 : nullptr;
+      s_w[threadIdx.x] = ok ? a.topk_weight[(size_t)t * K + threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < H / 8; c += THREADS) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 v[BSHMEM_MOE_MAX_TOPK];
+#pragma unroll
+      for (int j = 0; j < BSHMEM_MOE_MAX_TOPK; ++j)  // all K loads of this 16-byte column block are in flight together
+        if (j < K && s_src[j]) v[j] = ((const uint4*)s_src[j])[c];
+#pragma unroll
+      for (int j = 0; j < BSHMEM_MOE_MAX_TOPK; ++j) {
+        if (j < K && s_src[j]) {
+          const float w = s_w[j];
+          const __nv_bfloat162* h = (const __nv_bfloat162*)&v[j];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(h[q]);
+            acc[2 * q] += w * f.x;
+            acc[2 * q + 1] += w * f.y;
+          }
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* oh = (__nv_bfloat162*)&o;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) oh[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      ((uint4*)a.out)[(size_t)t * (H / 8) + c] = o;
+    }
+    __syncthreads();
+  }
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+  if (blockIdx.x == 0) pe_barrier(a.flags, 3, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
+}
+
+static size_t dispatch_smem(int E, int H) { return ((size_t)E * 4 + 15 & ~(size_t)15) + (size_t)H * 2 + H + (H / BSHMEM_MOE_QUANT_BLOCK) * 4 + 16; }
+
+// Cooperative grid: as many CTAs as are co-resident, at most one per token.
+template <class Kernel>
+static int coop_grid(Kernel k, size_t smem, int want, int max_ctas, int* grid_out) {
+  int dev = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, THREADS, smem) != cudaSuccess || per_sm < 1) return BSHMEM_MOE_ERR_DRIVER;
+  int grid = per_sm * sms;
+  if (grid > want) grid = want;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grid < 1) grid = 1;
+  *grid_out = grid;
+  return 0;
+}
+
+}  // namespace moe
+}  // namespace bshmem
+
+using namespace bshmem::moe;
+
+extern "C" size_t bshmem_moe_scratch_bytes(int) { return sizeof(Scratch); }
+
+static int check_common(int T, int H, int K, int E, int rank, int npes) {
+  if (npes < 1 || npes > BSHMEM_MOE_MAX_PES || rank < 0 || rank >= npes) return BSHMEM_MOE_ERR_ARGS;
+  if (T <= 0 || K < 1 || K > BSHMEM_MOE_MAX_TOPK || E < npes || E > BSHMEM_MOE_MAX_EXPERTS || E % npes) return BSHMEM_MOE_ERR_SHAPE;
+  if (H <= 0 || H % BSHMEM_MOE_QUANT_BLOCK) return BSHMEM_MOE_ERR_SHAPE;  // rows are moved in 16-byte pieces and quantised in blocks of 128
+  return 0;
+}
+
+extern "C" int bshmem_moe_dispatch(const bshmem_moe_dispatch_args_t* a, cudaStream_t stream) {
+  if (!a || !a->x || !a->topk_idx || !a->slot_map || !a->expert_offsets || !a->scratch || !a->error_flag) return BSHMEM_MOE_ERR_ARGS;
+  int st = check_common(a->T, a->H, a->K, a->E, a->rank, a->npes);
+  if (st) return st;
+  for (int q = 0; q < a->npes; ++q)
+    if (!a->recv_x[q] || !a->counts[q] || !a->flags[q] || (a->payload == BSHMEM_MOE_FP8_E4M3 && !a->recv_scale[q])) return BSHMEM_MOE_ERR_ARGS;
+  DispatchParams P;
+  P.a = *a;
+  P.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
+  const size_t smem = dispatch_smem(a->E, a->H);
+  int grid = 0;
+  st = coop_grid(dispatch_kernel, smem, a->T, a->max_ctas, &grid);
+  if (st) return st;
+  if (cudaMemsetAsync(a->scratch, 0, sizeof(Scratch), stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;
+  void* params[] = {(void*)&P};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)dispatch_kernel, dim3(grid), dim3(THREADS), params, smem, stream);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "bshmem_moe_dispatch: launch failed: %s\n", cudaGetErrorString(e));
+    return BSHMEM_MOE_ERR_DRIVER;
+  }
+  return 0;
+}
+
+extern "C" int bshmem_moe_combine(const bshmem_moe_combine_args_t* a, cudaStream_t stream) {
+  if (!a || !a->topk_idx || !a->topk_weight || !a->slot_map || !a->out || !a->scratch || !a->error_flag) return BSHMEM_MOE_ERR_ARGS;
+  int st = check_common(a->T, a->H, a->K, a->E, a->rank, a->npes);
+  if (st) return st;
+  for (int q = 0; q < a->npes; ++q)
+    if (!a->y[q] || !a->flags[q]) return BSHMEM_MOE_ERR_ARGS;
+  CombineParams P;
+  P.a = *a;
+  P.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
+  int grid = 0;
+  st = coop_grid(combine_kernel, 0, a->T, a->max_ctas, &grid);
+  if (st) return st;
+  if (cudaMemsetAsync(a->scratch, 0, 256, stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;  // the grid-barrier counter
+  void* params[] = {(void*)&P};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)combine_kernel, dim3(grid), dim3(THREADS), params, 0, stream);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "bshmem_moe_combine: launch failed: %s\n", cudaGetErrorString(e));
+    return BSHMEM_MOE_ERR_DRIVER;
+  }
+  return 0;
+}

@@ -64,6 +64,11 @@ def test_fused_gemm_collectives():
 
 
 @need2
+def test_moe_dispatch_combine():
+    run_workers("moe_dispatch_combine", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
 def test_tp_mlp_matches_single_device():
     run_workers("tp_mlp_matches_single_device", NG, gpu=True, env=NO_NVLS, timeout=600)
 

@@ -126,3 +126,10 @@ def test_tp_mlp_forward_backward_single_pe(nv):
     for got, want in ((x.grad, x32.grad), (mlp.up.weight.grad, w1.grad), (mlp.down.weight.grad, w2.grad)):
         denom = want.abs().max().item() + 1e-12
         assert (got.float() - want).abs().max().item() / denom < 0.06
+
+
+def test_moe_dispatch_combine_single_pe(nv):
+    """All experts local: dispatch is a permutation by expert, combine its weighted inverse."""
+    import tests.workers as W
+    W._moe_check(nv, "bf16", T=200, H=512, K=4, E=16, seed=11)
+    W._moe_check(nv, "fp8", T=128, H=1024, K=8, E=32, seed=12)

@@ -476,6 +476,8 @@ def _oracle(op, tensors):
 
 def _gather(t):
     """all_gather through a byte view: NCCL has no 16-bit integer type."""
+    if not dist.is_initialized():
+        return [t.clone()]
     raw = t.clone().contiguous().view(torch.uint8)
     outs = [torch.empty_like(raw) for _ in range(WORLD)]
     dist.all_gather(outs, raw)
@@ -693,6 +695,79 @@ def device_collectives_and_tiles():
     want[10:26, 8:40] = (torch.arange(R * Cc, dtype=torch.float32).reshape(R, Cc) * (left + 1))[10:26, 8:40]
     assert torch.equal(t_dst.cpu(), want)
     assert nv.error_bits() == 0
+    teardown(nv)
+
+
+def _moe_check(nv, payload, T, H, K, E, seed):
+    """Dispatch + combine against a gather-based oracle; returns nothing, asserts."""
+    from nvshmem_b200.ops.moe import MoeDispatchCombine
+    from nvshmem_b200.ops import fused_gemm as fg
+    n = WORLD
+    EL = E // n
+    g = torch.Generator(device="cuda").manual_seed(seed + RANK)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    probs = logits.softmax(-1)
+    w, idx = probs.topk(K, dim=-1)
+    idx = idx.to(torch.int32).contiguous()
+    idx[0, 0] = -1  # a dropped slot must be skipped everywhere
+    w = w.float().contiguous()
+    moe = MoeDispatchCombine(T, H, K, E, payload=payload, wait_limit_ms=5000)
+    for it in range(2):
+        recv, offs = moe.dispatch(x, idx)
+        torch.cuda.synchronize()
+        fg.check_errors()
+        allx, allidx, allmap = _gather(x), _gather(idx), _gather(moe.slot_map)
+        offs_h = offs.cpu().tolist()
+        # segment sizes: expert_offsets must equal the number of pairs routed to each local expert
+        for le in range(EL):
+            want = sum(int((ai == RANK * EL + le).sum()) for ai in allidx)
+            assert offs_h[le + 1] - offs_h[le] == want, (le, offs_h[le + 1] - offs_h[le], want)
+        rows = offs_h[EL]
+        got = moe.dequantized(rows) if payload == "fp8" else recv[:rows].float()
+        seen = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        for s in range(n):
+            mine = (allidx[s] >= RANK * EL) & (allidx[s] < (RANK + 1) * EL)
+            tt, jj = mine.nonzero(as_tuple=True)
+            r = allmap[s][tt, jj].long()
+            assert int(r.min()) >= 0 and int(r.max()) < rows
+            e_of_row = allidx[s][tt, jj].long() - RANK * EL
+            lo = torch.tensor(offs_h, device="cuda")[e_of_row]
+            hi = torch.tensor(offs_h, device="cuda")[e_of_row + 1]
+            assert bool(((r >= lo) & (r < hi)).all()), "row outside its expert's segment"
+            seen.index_add_(0, r, torch.ones_like(r, dtype=torch.int32))
+            src_rows = allx[s][tt].float()
+            if payload == "fp8":
+                amax = src_rows.view(-1, H // 128, 128).abs().amax(-1, keepdim=True).expand(-1, -1, 128).reshape(-1, H)
+                assert bool(((got[r] - src_rows).abs() <= 0.0625 * src_rows.abs() + amax / 448 + 1e-6).all()), "fp8 payload outside quantisation error"
+            else:
+                assert torch.equal(got[r], src_rows), ("payload mismatch", s)
+        assert bool((seen == 1).all()), "a receive row was written twice or never"
+        assert int(moe.slot_map[0, 0]) == -1
+        # expert "MLP": scale by (local expert + 1)
+        le_of_row = torch.bucketize(torch.arange(rows, device="cuda"), torch.tensor(offs_h[1:], device="cuda"), right=True)
+        src_for_y = got if payload == "fp8" else recv[:rows].float()
+        moe.expert_out[:rows] = (src_for_y * (le_of_row + 1).unsqueeze(1)).to(torch.bfloat16)
+        out = moe.combine(idx, w)
+        torch.cuda.synchronize()
+        fg.check_errors()
+        valid = (idx >= 0).float()
+        factor = ((idx % EL + 1).float() * w * valid).sum(1, keepdim=True)
+        want = x.float() * factor
+        tol = 0.09 if payload == "fp8" else 0.02
+        assert bool(((out.float() - want).abs() <= tol * want.abs() + tol * want.abs().max()).all()), (payload, (out.float() - want).abs().max().item())
+        x = (x.float() * 0.5 + 0.25).to(torch.bfloat16)  # next iteration: other data, same object (epochs)
+    moe.close()
+
+
+@worker
+def moe_dispatch_combine():
+    nv = setup()
+    n = WORLD
+    _moe_check(nv, "bf16", T=64, H=256, K=2, E=4 * n, seed=1)
+    _moe_check(nv, "bf16", T=512, H=1024, K=8, E=32 * n if n <= 4 else 256, seed=2)
+    _moe_check(nv, "fp8", T=256, H=512, K=4, E=8 * n, seed=3)
+    _moe_check(nv, "fp8", T=384, H=7168, K=8, E=16 * n, seed=4)
     teardown(nv)
 
 
