@@ -371,3 +371,81 @@ extern "C" int bshmem_moe_combine(const bshmem_moe_combine_args_t* a, cudaStream
   }
   return 0;
 }
+
+// ------------------------------------------------------------------ dispatch without any allocation
+// Single-PE dispatch whose scratch is a fixed array inside this library (see bshmem/moe_noalloc.h
+// for who needs that and the rules of use).  In host code the array's name is only a handle; the
+// address a kernel can use comes from cudaGetSymbolAddress, looked up once per GPU.
+#include "../../include/bshmem/moe_noalloc.h"
+
+namespace {
+
+struct NoAllocBlock {
+  bshmem::moe::Scratch scratch;                    // counters + grid-barrier word (cleared every call)
+  int counts[BSHMEM_MOE_NOALLOC_MAX_EXPERTS];      // the 1 x E count matrix
+  uint64_t flags[4];                               // cross-PE barrier rows (unused with one PE, must exist)
+  int error_flag;                                  // used when the caller passes none
+  int pad[7];
+};
+static_assert(sizeof(NoAllocBlock) <= BSHMEM_MOE_NOALLOC_SCRATCH_BYTES, "documented scratch size is too small");
+
+static __device__ __align__(256) unsigned char g_noalloc_block[BSHMEM_MOE_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static NoAllocBlock* g_noalloc_addr[kMaxDevices];  // device address of the array, per GPU ordinal
+
+}  // namespace
+
+extern "C" int bshmem_moe_dispatch_local_noalloc(const void* x, const int* topk_idx, int T, int H, int K, int E, void* recv_x, int* slot_map, int* expert_offsets,
+                                                 int* error_flag, cudaStream_t stream) {
+  if (!x || !topk_idx || !recv_x || !slot_map || !expert_offsets) return BSHMEM_MOE_ERR_ARGS;
+  if (E > BSHMEM_MOE_NOALLOC_MAX_EXPERTS || E < 1 || K < 1 || K > BSHMEM_MOE_MAX_TOPK || T < 1 || H < 1 || H % BSHMEM_MOE_QUANT_BLOCK) {
+    fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: unsupported size (T=%d H=%d K=%d E=%d): at most %d experts and top-%d, H a multiple of %d\n", T, H, K, E,
+            BSHMEM_MOE_NOALLOC_MAX_EXPERTS, BSHMEM_MOE_MAX_TOPK, BSHMEM_MOE_QUANT_BLOCK);
+    return BSHMEM_MOE_ERR_SHAPE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return BSHMEM_MOE_ERR_DRIVER;
+  if (!g_noalloc_addr[dev]) {  // first call on this GPU (it is the current device): resolve the array's device address
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_block);
+    if (e != cudaSuccess || !p) {
+      fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return BSHMEM_MOE_ERR_DRIVER;
+    }
+    g_noalloc_addr[dev] = (NoAllocBlock*)p;
+  }
+  NoAllocBlock* blk = g_noalloc_addr[dev];
+  // The block keeps what the previous call left: clear the counters, the barrier word, the flags and the built-in error word.
+  if (cudaMemsetAsync(blk, 0, sizeof(NoAllocBlock), stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;
+
+  DispatchParams P;
+  memset(&P, 0, sizeof(P));
+  bshmem_moe_dispatch_args_t& a = P.a;
+  a.T = T; a.H = H; a.K = K; a.E = E; a.rank = 0; a.npes = 1;
+  a.payload = BSHMEM_MOE_BF16;
+  a.cap_rows = T * K;
+  a.epoch = 1;
+  a.error_flag = error_flag ? error_flag : &blk->error_flag;
+  a.x = x;
+  a.topk_idx = topk_idx;
+  a.recv_x[0] = recv_x;
+  a.slot_map = slot_map;
+  a.expert_offsets = expert_offsets;
+  a.src_offsets = nullptr;
+  a.counts[0] = blk->counts;
+  a.flags[0] = blk->flags;
+  a.scratch = &blk->scratch;
+  P.wait_limit_ns = 10000000000ull;
+  const size_t smem = dispatch_smem(E, H);
+  int grid = 0;
+  int st = coop_grid(dispatch_kernel, smem, T, 0, &grid);
+  if (st) return st;
+  void* params[] = {(void*)&P};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)dispatch_kernel, dim3(grid), dim3(THREADS), params, smem, stream);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: launch failed: %s\n", cudaGetErrorString(e));
+    return BSHMEM_MOE_ERR_DRIVER;
+  }
+  return BSHMEM_MOE_OK;
+}
