@@ -96,6 +96,110 @@ def reference_arm(args):
     return reference_bench.run(args, M, N, K_LOCAL)
 
 
+def timed_runs(step, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step):
+    """Times `step(x, w) -> out` (a) on device-resident inputs and (b) end to end from pinned host
+    memory with a checksum read back every step.  Returns the JSON line (without `impl`)."""
+    import torch
+    import torch.distributed as dist
+
+    dev = torch.device("cuda", local_rank)
+    torch.manual_seed(1234 + rank)
+    sets = max(1, args.sets)
+    xs = [torch.randn(M, K_LOCAL, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(sets)]
+    ws = [torch.randn(N, K_LOCAL, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16) for _ in range(sets)]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(3, args.warmup)
+    for i in range(warm):
+        step(xs[i % sets], ws[i % sets])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(args.steps):
+        step(xs[i % sets], ws[i % sets])
+    end.record()
+    barrier()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop()
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    flops_per_rank = 2.0 * M * N * K_LOCAL
+    value = world * flops_per_rank / (ms_per_step * 1e-3) / 1e12
+
+    # ---------------- end to end: pinned host input every step, checksum read back every step
+    host_x = [torch.randn(M, K_LOCAL, dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty(M, K_LOCAL, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    main_stream = torch.cuda.current_stream()
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_steps(n):
+        # Step i+1's input is copied on the copy stream while step i computes.
+        with torch.cuda.stream(copy_stream):
+            dev_x[0].copy_(host_x[0], non_blocking=True)
+            copied[0].record(copy_stream)
+        for i in range(n):
+            cur, nxt = i & 1, (i + 1) & 1
+            if i + 1 < n:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(consumed[nxt])
+                    dev_x[nxt].copy_(host_x[nxt], non_blocking=True)
+                    copied[nxt].record(copy_stream)
+            main_stream.wait_event(copied[cur])
+            out = step(dev_x[cur], ws[i % sets])
+            consumed[cur].record(main_stream)
+            host_out.copy_(out.float().sum().reshape(1), non_blocking=True)
+            main_stream.synchronize()  # the result of every step reaches the host
+        return float(host_out.item())
+
+    e2e_steps(3)
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_steps(args.steps)
+    t1.record()
+    barrier()
+    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms_per_step = float(e2e_ms.item()) / args.steps
+    e2e_value = world * flops_per_rank / (e2e_ms_per_step * 1e-3) / 1e12
+    return {
+        "metric": "fused_gemm_reduce_scatter_tflops",
+        "value": round(value, 2),
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": warm,
+        "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None,
+        "dtype": "bf16",
+        "data": "synthetic (seeded randn activations, N(0,0.02) weights, random init)",
+        "config": {"model": "tp_row_parallel_gemm_reduce_scatter", "M": M, "N": N, "K_per_rank": K_LOCAL, "global_batch": M, "seq_len": 1,
+                   "parallelism": f"tp{world}", "l2": f"inputs rotate over {sets} buffer sets ({sets * (M + N) * K_LOCAL * 2 >> 20} MiB > 126 MiB L2)"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms_per_step, 5), "h2d_bytes_per_step": M * K_LOCAL * 2,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": args.steps * launches_per_step,
+    }
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -113,8 +217,6 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus and world > 1:
-        args.gpus = world
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -128,110 +230,11 @@ def main():
         nv.init(device=local_rank, initializer_method="torch")
     else:
         nv.init(device=local_rank, uid=nv.get_unique_id(), rank=0, nranks=1)
-
-    torch.manual_seed(1234 + rank)
-    sets = max(1, args.sets)
-    xs = [torch.randn(M, K_LOCAL, device=dev, dtype=torch.float32).mul_(1.0).to(torch.bfloat16) for _ in range(sets)]
-    ws = [torch.randn(N, K_LOCAL, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16) for _ in range(sets)]
     op = fg.GemmReduceScatter(M, N, mode="rs")
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---------------- device-timed kernel path
-    for i in range(max(3, args.warmup)):
-        op(xs[i % sets], ws[i % sets])
-    barrier()
+    # one fused tcgen05 kernel per step (libbshmem_fused.so): GEMM, peer pushes and the reduction
+    line = timed_runs(lambda x, w: op(x, w), args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=1)
+    line["impl"] = "ours"
     fg.check_errors(dev)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    time.sleep(0.25)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(args.steps):
-        op(xs[i % sets], ws[i % sets])
-    end.record()
-    barrier()
-    ms = start.elapsed_time(end)
-    clocks = sampler.stop()
-    fg.check_errors(dev)
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
-    flops_per_rank = 2.0 * M * N * K_LOCAL
-    value = world * flops_per_rank / (ms_per_step * 1e-3) / 1e12
-
-    # ---------------- end to end: pinned host input every step, checksum read back every step
-    host_x = [torch.randn(M, K_LOCAL, dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(2)]
-    dev_x = [torch.empty(M, K_LOCAL, device=dev, dtype=torch.bfloat16) for _ in range(2)]
-    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
-    copy_stream = torch.cuda.Stream()
-    main_stream = torch.cuda.current_stream()
-    copied = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-
-    def e2e_steps(n):
-        # Step i's input is copied on the copy stream while step i-1 computes.
-        with torch.cuda.stream(copy_stream):
-            dev_x[0].copy_(host_x[0], non_blocking=True)
-            copied[0].record(copy_stream)
-        for i in range(n):
-            cur, nxt = i & 1, (i + 1) & 1
-            if i + 1 < n:
-                with torch.cuda.stream(copy_stream):
-                    if i >= 1:
-                        copy_stream.wait_event(consumed[nxt])
-                    dev_x[nxt].copy_(host_x[nxt], non_blocking=True)
-                    copied[nxt].record(copy_stream)
-            main_stream.wait_event(copied[cur])
-            out = op(dev_x[cur], ws[i % sets])
-            consumed[cur].record(main_stream)
-            host_out.copy_(out.float().sum().reshape(1), non_blocking=True)
-            main_stream.synchronize()  # the result of every step reaches the host
-        return float(host_out.item())
-
-    e2e_steps(3)
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    e2e_steps(args.steps)
-    t1.record()
-    barrier()
-    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_ms_per_step = float(e2e_ms.item()) / args.steps
-    e2e_value = world * flops_per_rank / (e2e_ms_per_step * 1e-3) / 1e12
-    fg.check_errors(dev)
-
-    line = {
-        "metric": "fused_gemm_reduce_scatter_tflops",
-        "value": round(value, 2),
-        "unit": "TFLOP/s",
-        "n_gpus": world,
-        "steps": args.steps,
-        "warmup": max(3, args.warmup),
-        "ms_per_step": round(ms_per_step, 5),
-        "higher_is_better": True,
-        "scaling": "weak",
-        "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None,
-        "dtype": "bf16",
-        "data": "synthetic (seeded randn activations, N(0,0.02) weights, random init)",
-        "impl": "ours",
-        "config": {"model": "tp_row_parallel_gemm_reduce_scatter", "M": M, "N": N, "K_per_rank": K_LOCAL, "global_batch": M, "seq_len": 1,
-                   "parallelism": f"tp{world}", "l2": f"inputs rotate over {sets} buffer sets ({sets * (M + N) * K_LOCAL * 2 >> 20} MiB > 126 MiB L2)"},
-        "clocks": clocks,
-        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms_per_step, 5), "h2d_bytes_per_step": M * K_LOCAL * 2,
-                "d2h_bytes_per_step": 4},
-        "gpu_launches": args.steps,  # one fused tcgen05 kernel per step (libbshmem_fused.so)
-    }
     op.close()
     nv.finalize()
     if world > 1:
