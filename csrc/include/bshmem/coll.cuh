@@ -60,7 +60,26 @@ __device__ __forceinline__ int team_translate_pe(int src_team, int src_pe, int d
 }
 
 // ------------------------------------------------------------------ sync / barrier
-// One-round sync.  Returns 0, or 1 if a member did not arrive within the wait bound.
+// Polls a flag with relaxed loads until it reaches `want` (no fence: the caller fences once after all its polls).
+__device__ __forceinline__ int poll_ge_relaxed(const uint64_t* flag, uint64_t want) {
+  if (ld_relaxed_sys(flag) >= want) return 0;
+  const uint64_t start = global_timer_ns(), limit = bshmemi_state_d.wait_timeout_ns;
+  uint32_t spins = 0;
+  for (;;) {
+    const uint64_t v = ld_relaxed_sys(flag);
+    if (v >= want) return 0;
+    if ((++spins & 0xff) == 0 && global_timer_ns() - start > limit) {
+      record_timeout(flag, want, v, BSHMEM_WHERE_BARRIER);
+      return 1;
+    }
+  }
+}
+
+// Sync over the team.  One release fence for the whole group, relaxed flag stores to every member,
+// relaxed polls of the members' flags, one acquire fence per polling thread: two fences on the critical
+// path however many members there are.  On a flat NVSwitch fabric one all-to-all round is used (every
+// member one hop away); thread and warp scope on teams beyond 32 members fall back to radix-k
+// dissemination.  Returns 0, or 1 if a member did not arrive within the wait bound.
 template <int SCOPE>
 __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) {
   const int size = t->size, me = t->my_pe;
@@ -71,12 +90,14 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
   const uint64_t epoch = epochs[slot] + 1;
   uint64_t* flags = (uint64_t*)t->sync_base + (size_t)slot * size;
   int err = 0;
+  if (rank == 0) fence_sys();  // release: the group's earlier stores (ordered before this by the group barrier)
+  group_sync<SCOPE>();
   const int k = SCOPE == SCOPE_BLOCK || SCOPE == SCOPE_WARPGROUP || size <= 32 ? size : bshmemi_state_d.barrier_dissem_kval;
   if (k >= size) {
     for (int i = rank; i < size; i += G)
-      if (i != me) st_release_sys(translate(flags + me, team_world_pe(t, i)), epoch);
+      if (i != me) st_relaxed_sys(translate(flags + me, team_world_pe(t, i)), epoch);
     for (int i = rank; i < size; i += G)
-      if (i != me) err |= wait_ge_u64(flags + i, epoch, BSHMEM_WHERE_BARRIER);
+      if (i != me) err |= poll_ge_relaxed(flags + i, epoch);
   } else {
     // Radix-k dissemination: in round r talk to the PEs at distance j*k^r, j = 1..k-1.
     // Flag index r*(k-1)+(j-1) never exceeds `size` for k >= 2.
@@ -85,24 +106,25 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
       for (int j = 1 + rank; j < k; j += G) {
         if ((long)j * dist >= size) continue;
         const int to = (me + j * dist) % size;
-        st_release_sys(translate(flags + round * (k - 1) + (j - 1), team_world_pe(t, to)), epoch);
+        st_relaxed_sys(translate(flags + round * (k - 1) + (j - 1), team_world_pe(t, to)), epoch);
       }
       for (int j = 1 + rank; j < k; j += G) {
         if ((long)j * dist >= size) continue;
-        err |= wait_ge_u64(flags + round * (k - 1) + (j - 1), epoch, BSHMEM_WHERE_BARRIER);
+        err |= poll_ge_relaxed(flags + round * (k - 1) + (j - 1), epoch);
       }
+      // A round's arrivals must be ordered before the next round's announcements.
+      fence_sys();
       group_sync<SCOPE>();
     }
   }
+  fence_sys();  // acquire: data published by the members before their flags
   group_sync<SCOPE>();
   if (rank == 0) epochs[slot] = epoch;
   return err;
 }
-// Barrier = completion of this group's earlier puts (quiet) + sync.
+// Barrier = completion of this group's earlier puts (quiet) + sync; the sync's release fence is that quiet.
 template <int SCOPE>
 __device__ __forceinline__ int team_barrier(const bshmemi_team_t* t, int slot = 0) {
-  group_sync<SCOPE>();
-  if (group_rank<SCOPE>() == 0) fence_sys();
   return team_sync<SCOPE>(t, slot);
 }
 

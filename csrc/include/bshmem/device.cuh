@@ -262,7 +262,14 @@ __device__ __forceinline__ void iget(T* dest, const T* src, ptrdiff_t dst, ptrdi
 }
 
 // ------------------------------------------------------------------ signals
+// Bare signal update: an atomic store or add with no ordering of its own.  Code that publishes
+// data with it orders the data first (fence / quiet); putmem_signal below does so itself.
 __device__ __forceinline__ void signal_op(uint64_t* sig_addr, uint64_t value, int op, int pe) {
+  uint64_t* remote = translate(sig_addr, pe);
+  if (op == SIGNAL_ADD) asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(remote), "l"(value) : "memory");
+  else st_relaxed_sys(remote, value);
+}
+__device__ __forceinline__ void signal_op_release(uint64_t* sig_addr, uint64_t value, int op, int pe) {
   uint64_t* remote = translate(sig_addr, pe);
   if (op == SIGNAL_ADD) red_add_release_sys(remote, value);
   else st_release_sys(remote, value);
@@ -274,10 +281,7 @@ __device__ __forceinline__ void putmem_signal(void* dest, const void* src, size_
   if (!check_target(dest, pe)) return;
   memcpy_group<SCOPE>(translate((char*)dest, pe), src, bytes);
   group_sync<SCOPE>();
-  if (group_rank<SCOPE>() == 0) {
-    if (SCOPE != SCOPE_THREAD) fence_sys();  // the other threads' stores, ordered here by the barrier
-    signal_op(sig_addr, value, op, pe);
-  }
+  if (group_rank<SCOPE>() == 0) signal_op_release(sig_addr, value, op, pe);  // release: cumulative over the group's stores (ordered here by the barrier)
 }
 __device__ __forceinline__ uint64_t signal_fetch(const uint64_t* sig_addr) { return ld_acquire_sys(sig_addr); }
 

@@ -260,6 +260,10 @@ int nvshmemx_collective_launch(const void* func, dim3 grid_dims, dim3 block_dims
 int nvshmemx_collective_launch_query_gridsize(const void* func, dim3 block_dims, void** args, size_t shared_mem, int* gridsize);
 
 /* ---------------------------------------------------------------- extensions of this library (no NVSHMEM counterpart) */
+/* Fills the device-state copy of every library with device code loaded so far.  Initialisation and
+ * every later API call do this on their own; call it after loading such a library at run time when
+ * its kernels are launched before any other call into this library. */
+void nvshmemx_b200_module_sync(void);
 /* Error bits recorded by device code since the last clear (BSHMEM_ERR_*): bounded waits
  * report a time-out here instead of hanging the GPU. */
 uint32_t nvshmemx_b200_error_bits(void);

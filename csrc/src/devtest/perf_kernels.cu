@@ -1,0 +1,227 @@
+// Timing kernels of the perftest drivers (put/get bandwidth, ping-pong latency, atomics, barrier and
+// device-collective latency), written against the public device API.  Each kernel performs `iters`
+// operations so that one launch amortises launch overhead; the host times the launch with CUDA events
+// (reference method: perftest/device/pt-to-pt/shmem_put_bw.cu, shmem_put_signal_ping_pong_latency.cu,
+//  perftest/common/atomic_bw_common.h, perftest/device/coll/*_latency.cu).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "nvshmem.h"
+#include "nvshmemx.h"
+
+// Inter-CTA barrier inside one launch (all CTAs co-resident: grids here never exceed the SM count).
+__device__ __forceinline__ void cta_rendezvous(unsigned* counter, unsigned target) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const unsigned long long start = bshmem::global_timer_ns();
+    while (*(volatile unsigned*)counter < target) {
+      if (bshmem::global_timer_ns() - start > 5000000000ull) break;  // bounded
+    }
+  }
+  __syncthreads();
+}
+
+// scope: 0 thread (each thread moves its own piece), 1 warp, 2 block.  `dir` 0 = put, 1 = get.
+__global__ void __launch_bounds__(1024) k_bw(char* sym, char* local, size_t bytes, int pe, int iters, int scope, int dir, unsigned* counter) {
+  const size_t per_cta = (bytes / gridDim.x) & ~(size_t)15;
+  char* s = sym + (size_t)blockIdx.x * per_cta;
+  char* l = local + (size_t)blockIdx.x * per_cta;
+  for (int it = 0; it < iters; ++it) {
+    if (scope == 2) {
+      if (dir == 0) nvshmemx_putmem_nbi_block(s, l, per_cta, pe);
+      else nvshmemx_getmem_nbi_block(l, s, per_cta, pe);
+    } else if (scope == 1) {
+      const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+      const size_t per_w = (per_cta / nw) & ~(size_t)15;
+      if (dir == 0) nvshmemx_putmem_nbi_warp(s + w * per_w, l + w * per_w, per_w, pe);
+      else nvshmemx_getmem_nbi_warp(l + w * per_w, s + w * per_w, per_w, pe);
+    } else {
+      const size_t per_t = (per_cta / blockDim.x) & ~(size_t)15;
+      if (per_t) {
+        if (dir == 0) nvshmem_putmem_nbi(s + threadIdx.x * per_t, l + threadIdx.x * per_t, per_t, pe);
+        else nvshmem_getmem_nbi(l + threadIdx.x * per_t, s + threadIdx.x * per_t, per_t, pe);
+      }
+    }
+    cta_rendezvous(counter, (unsigned)(it + 1) * gridDim.x);
+  }
+  nvshmemx_quiet_block();
+}
+
+// Small-message rate: every thread issues `iters` single-element puts (p) or gets (g).
+__global__ void __launch_bounds__(1024) k_pg_rate(unsigned long long* sym, int pe, int iters, int dir, unsigned long long* sink) {
+  unsigned long long acc = 0;
+  unsigned long long* slot = sym + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int it = 0; it < iters; ++it) {
+    if (dir == 0) nvshmem_ulonglong_p(slot, (unsigned long long)it, pe);
+    else acc += nvshmem_ulonglong_g(slot, pe);
+  }
+  nvshmem_quiet();
+  if (acc == 0xdeadbeefULL) *sink = acc;
+}
+
+// Blocking latency of one operation issued by a single thread / warp / block: `iters` put + quiet round trips.
+__global__ void __launch_bounds__(1024) k_put_latency(char* sym, char* local, size_t bytes, int pe, int iters, int scope) {
+  for (int it = 0; it < iters; ++it) {
+    if (scope == 2) { nvshmemx_putmem_block(sym, local, bytes, pe); nvshmemx_quiet_block(); }
+    else if (scope == 1) { if (threadIdx.x < 32) { nvshmemx_putmem_warp(sym, local, bytes, pe); nvshmemx_quiet_warp(); } }
+    else if (threadIdx.x == 0) { nvshmem_putmem(sym, local, bytes, pe); nvshmem_quiet(); }
+  }
+}
+__global__ void __launch_bounds__(1024) k_get_latency(char* sym, char* local, size_t bytes, int pe, int iters, int scope) {
+  for (int it = 0; it < iters; ++it) {
+    if (scope == 2) nvshmemx_getmem_block(local, sym, bytes, pe);
+    else if (scope == 1) { if (threadIdx.x < 32) nvshmemx_getmem_warp(local, sym, bytes, pe); }
+    else if (threadIdx.x == 0) nvshmem_getmem(local, sym, bytes, pe);
+    __syncthreads();
+  }
+}
+
+// Ping-pong between PE 0 and PE 1 with put_signal: half the round trip is the one-way latency.
+__global__ void __launch_bounds__(1024) k_pingpong(char* data, char* local, size_t bytes, uint64_t* sig, int iters, uint64_t base, int scope) {
+  const int me = nvshmem_my_pe(), peer = 1 - me;
+  if (me > 1) return;
+  for (int it = 1; it <= iters; ++it) {
+    const uint64_t v = base + (uint64_t)it;
+    if (me == 0) {
+      if (scope == 2) nvshmemx_putmem_signal_block(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer);
+      else if (scope == 1) { if (threadIdx.x < 32) nvshmemx_putmem_signal_warp(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer); }
+      else if (threadIdx.x == 0) nvshmem_putmem_signal(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer);
+      if (threadIdx.x == 0) nvshmem_signal_wait_until(sig, NVSHMEM_CMP_GE, v);
+      __syncthreads();
+    } else {
+      if (threadIdx.x == 0) nvshmem_signal_wait_until(sig, NVSHMEM_CMP_GE, v);
+      __syncthreads();
+      if (scope == 2) nvshmemx_putmem_signal_block(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer);
+      else if (scope == 1) { if (threadIdx.x < 32) nvshmemx_putmem_signal_warp(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer); }
+      else if (threadIdx.x == 0) nvshmem_putmem_signal(data, local, bytes, sig, v, NVSHMEM_SIGNAL_SET, peer);
+    }
+  }
+}
+// Signal-only ping-pong (no payload).
+__global__ void __launch_bounds__(1024) k_signal_pingpong(uint64_t* sig, int iters, uint64_t base) {
+  const int me = nvshmem_my_pe(), peer = 1 - me;
+  if (me > 1 || threadIdx.x) return;
+  for (int it = 1; it <= iters; ++it) {
+    const uint64_t v = base + (uint64_t)it;
+    if (me == 0) {
+      nvshmemx_signal_op(sig, v, NVSHMEM_SIGNAL_SET, peer);
+      nvshmem_signal_wait_until(sig, NVSHMEM_CMP_GE, v);
+    } else {
+      nvshmem_signal_wait_until(sig, NVSHMEM_CMP_GE, v);
+      nvshmemx_signal_op(sig, v, NVSHMEM_SIGNAL_SET, peer);
+    }
+  }
+}
+
+// Atomic throughput: every thread performs `iters` operations on its own 64-bit word of PE `pe`
+// (kind 0 fetch_add, 1 add, 2 compare_swap, 3 swap, 4 fetch_or), or all on one word when `contend`.
+__global__ void __launch_bounds__(1024) k_atomic_rate(long long* sym, int pe, int iters, int kind, int contend, long long* sink) {
+  long long* t = contend ? sym : sym + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  long long acc = 0;
+  for (int it = 0; it < iters; ++it) {
+    switch (kind) {
+      case 0: acc += nvshmem_longlong_atomic_fetch_add(t, 1LL, pe); break;
+      case 1: nvshmem_longlong_atomic_add(t, 1LL, pe); break;
+      case 2: acc += nvshmem_longlong_atomic_compare_swap(t, (long long)it, (long long)it + 1, pe); break;
+      case 3: acc += nvshmem_longlong_atomic_swap(t, (long long)it, pe); break;
+      default: acc += (long long)nvshmem_uint64_atomic_fetch_or((uint64_t*)t, 1ULL, pe); break;
+    }
+  }
+  nvshmem_quiet();
+  if (acc == 0x7fffffffffffffffLL) *sink = acc;
+}
+// Latency of a dependent chain of fetching atomics by one thread.
+__global__ void __launch_bounds__(1024) k_atomic_latency(long long* sym, int pe, int iters, long long* sink) {
+  if (threadIdx.x || blockIdx.x) return;
+  long long v = 0;
+  for (int it = 0; it < iters; ++it) v = nvshmem_longlong_atomic_fetch_add(sym, v & 1, pe);
+  *sink = v;
+}
+
+// Barrier / sync latency at each scope.
+__global__ void __launch_bounds__(1024) k_barrier_latency(int iters, int scope, int sync_only) {
+  for (int it = 0; it < iters; ++it) {
+    if (scope == 2) { if (sync_only) nvshmemx_sync_all_block(); else nvshmemx_barrier_all_block(); }
+    else if (scope == 1) { if (threadIdx.x < 32) { if (sync_only) nvshmemx_sync_all_warp(); else nvshmemx_barrier_all_warp(); } }
+    else if (threadIdx.x == 0) { if (sync_only) nvshmem_sync_all(); else nvshmem_barrier_all(); }
+  }
+}
+
+// Device-initiated collectives, `iters` back to back (block scope).  kind as in the test kernels:
+// 0 float sum allreduce, 2 float sum reducescatter, 3 int fcollect, 4 int alltoall, 5 int broadcast, 6 bf16 sum allreduce.
+__global__ void __launch_bounds__(1024) k_coll_latency(int kind, void* dst, const void* src, size_t n, int iters) {
+  for (int it = 0; it < iters; ++it) {
+    switch (kind) {
+      case 0: nvshmemx_float_sum_reduce_block(NVSHMEM_TEAM_WORLD, (float*)dst, (const float*)src, n); break;
+      case 2: nvshmemx_float_sum_reducescatter_block(NVSHMEM_TEAM_WORLD, (float*)dst, (const float*)src, n); break;
+      case 3: nvshmemx_int_fcollect_block(NVSHMEM_TEAM_WORLD, (int*)dst, (const int*)src, n); break;
+      case 4: nvshmemx_int_alltoall_block(NVSHMEM_TEAM_WORLD, (int*)dst, (const int*)src, n); break;
+      case 5: nvshmemx_int_broadcast_block(NVSHMEM_TEAM_WORLD, (int*)dst, (const int*)src, n, 0); break;
+      default: nvshmemx_bfloat16_sum_reduce_block(NVSHMEM_TEAM_WORLD, (__nv_bfloat16*)dst, (const __nv_bfloat16*)src, n); break;
+    }
+  }
+}
+
+#define OK() (cudaGetLastError() == cudaSuccess ? 0 : 1)
+extern "C" {
+int perf_preload(void) {
+  cudaFuncAttributes a;
+  const void* fns[] = {(const void*)k_bw, (const void*)k_pg_rate, (const void*)k_put_latency, (const void*)k_get_latency, (const void*)k_pingpong,
+                       (const void*)k_signal_pingpong, (const void*)k_atomic_rate, (const void*)k_atomic_latency, (const void*)k_barrier_latency,
+                       (const void*)k_coll_latency};
+  int bad = 0, i = 0;
+  for (const void* f : fns) {
+    cudaError_t e = cudaFuncGetAttributes(&a, f);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "perf_preload: kernel %d: %s\n", i, cudaGetErrorString(e));
+      bad = 1;
+    }
+    ++i;
+  }
+  return bad;
+}
+int perf_bw(void* sym, void* local, size_t bytes, int pe, int iters, int scope, int dir, int ctas, int threads, unsigned* counter, cudaStream_t s) {
+  cudaMemsetAsync(counter, 0, sizeof(unsigned), s);
+  k_bw<<<ctas, threads, 0, s>>>((char*)sym, (char*)local, bytes, pe, iters, scope, dir, counter);
+  return OK();
+}
+int perf_pg_rate(void* sym, int pe, int iters, int dir, int ctas, int threads, void* sink, cudaStream_t s) {
+  k_pg_rate<<<ctas, threads, 0, s>>>((unsigned long long*)sym, pe, iters, dir, (unsigned long long*)sink);
+  return OK();
+}
+int perf_put_latency(void* sym, void* local, size_t bytes, int pe, int iters, int scope, int threads, cudaStream_t s) {
+  k_put_latency<<<1, threads, 0, s>>>((char*)sym, (char*)local, bytes, pe, iters, scope);
+  return OK();
+}
+int perf_get_latency(void* sym, void* local, size_t bytes, int pe, int iters, int scope, int threads, cudaStream_t s) {
+  k_get_latency<<<1, threads, 0, s>>>((char*)sym, (char*)local, bytes, pe, iters, scope);
+  return OK();
+}
+int perf_pingpong(void* data, void* local, size_t bytes, uint64_t* sig, int iters, uint64_t base, int scope, int threads, cudaStream_t s) {
+  k_pingpong<<<1, threads, 0, s>>>((char*)data, (char*)local, bytes, sig, iters, base, scope);
+  return OK();
+}
+int perf_signal_pingpong(uint64_t* sig, int iters, uint64_t base, cudaStream_t s) {
+  k_signal_pingpong<<<1, 32, 0, s>>>(sig, iters, base);
+  return OK();
+}
+int perf_atomic_rate(void* sym, int pe, int iters, int kind, int contend, int ctas, int threads, void* sink, cudaStream_t s) {
+  k_atomic_rate<<<ctas, threads, 0, s>>>((long long*)sym, pe, iters, kind, contend, (long long*)sink);
+  return OK();
+}
+int perf_atomic_latency(void* sym, int pe, int iters, void* sink, cudaStream_t s) {
+  k_atomic_latency<<<1, 32, 0, s>>>((long long*)sym, pe, iters, (long long*)sink);
+  return OK();
+}
+int perf_barrier_latency(int iters, int scope, int sync_only, int threads, cudaStream_t s) {
+  k_barrier_latency<<<1, threads, 0, s>>>(iters, scope, sync_only);
+  return OK();
+}
+int perf_coll_latency(int kind, void* dst, const void* src, size_t n, int iters, int threads, cudaStream_t s) {
+  k_coll_latency<<<1, threads, 0, s>>>(kind, dst, src, n, iters);
+  return OK();
+}
+}

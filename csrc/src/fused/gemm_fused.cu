@@ -274,10 +274,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
     const bool reduce_mode = (p.mode == BSHMEM_FUSED_RS || p.mode == BSHMEM_FUSED_AR) && p.npes > 1;
     int acc = 0;
     uint32_t acc_phase = 0, chunk_counter = 0;
+    uint64_t* pending_flag = nullptr;  // flag of the previous remote tile, published once its stores have completed
     for (int t = first; t < total_tiles; t += step) {
       const TileInfo ti = tile_info(p, t);
       const bool own = !reduce_mode || ti.peer == p.rank;
       uint32_t ok = mbar_wait(&acc_full[acc], acc_phase, p.wait_limit_ns, abort_flag) ? 1u : 0u;
+      if (issuer && pending_flag) {
+        // The previous tile's stores were issued a whole main loop ago: this wait does not stall.
+        bulk_wait<0>();
+        fence_proxy_async_all();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pending_flag), "l"(p.epoch) : "memory");
+        pending_flag = nullptr;
+      }
       if (reduce_mode && own && issuer && ok) {
         // Partials of this tile from every other PE must have landed in my receive slots.
         for (int s = 0; s < p.npes && ok; ++s)
@@ -348,17 +356,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         }
         ++chunk_counter;
       }
-      if (!own && issuer) {
-        // The four stores of the tile are complete at the destination; publish the tile.
-        bulk_wait<0>();
-        fence_proxy_async_all();
-        asm volatile("fence.acq_rel.sys;" ::: "memory");
-        uint64_t* f = p.flags_peer[ti.peer] + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
-        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(p.epoch) : "memory");
-      }
+      // Waiting here for the remote writes would idle the epilogue for a link round trip per tile;
+      // the flag goes out at the start of the next tile's epilogue instead (or after the loop).
+      if (!own && issuer) pending_flag = p.flags_peer[ti.peer] + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (issuer) bulk_wait<0>();
+    if (issuer) {
+      bulk_wait<0>();
+      if (pending_flag) {
+        fence_proxy_async_all();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pending_flag), "l"(p.epoch) : "memory");
+      }
+    }
   }
 
   // ---------------- teardown

@@ -29,7 +29,10 @@ namespace {
 enum CopyMode { COPY_BLOCKING, COPY_NBI, COPY_STREAM };
 
 bool ready(const char* fn) {
-  if (is_initialized()) return true;
+  if (is_initialized()) {
+    push_pending_modules();  // libraries with device code that were loaded since the last call
+    return true;
+  }
   ERROR_PRINT("%s called before nvshmem_init (or after finalize)", fn);
   return false;
 }
@@ -655,6 +658,9 @@ int nvshmemx_collective_launch(const void* func, dim3 grid, dim3 block, void** a
 }
 
 // ------------------------------------------------------------------ library extensions
+void nvshmemx_b200_module_sync(void) {
+  if (is_initialized()) push_device_state();
+}
 uint32_t nvshmemx_b200_error_bits(void) {
   Runtime& r = rt();
   return r.status_host ? r.status_host->error_bits : 0;

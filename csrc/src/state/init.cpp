@@ -95,8 +95,15 @@ static int build_reach_map(Runtime& r) {
   return ST_SUCCESS;
 }
 
+void push_pending_modules() {
+  Runtime& r = rt();
+  if (!r.modules_pending.load() || r.init_status < INIT_IS_INITIALIZED) return;
+  push_device_state();
+}
+
 int push_device_state() {
   Runtime& r = rt();
+  r.modules_pending.store(false);
   if (!r.have_gpu) return ST_SUCCESS;
   for (auto& m : r.modules) {
     void* addr = m.first();
@@ -367,12 +374,13 @@ int runtime_finalize() {
 }  // namespace bshmem
 
 extern "C" void bshmemi_register_module(void* (*getter)(), const char* name) {
+  // Runs inside static initialisers of the registering library, possibly while that library's
+  // device code is still being registered with the CUDA runtime: make no CUDA call here.  The
+  // state reaches the module at initialisation, or at the next API call if the library was
+  // loaded later (push_pending_modules).
   bshmem::Runtime& r = bshmem::rt();
   for (auto& m : r.modules)
     if (m.first == getter) return;
   r.modules.emplace_back(getter, name ? name : "?");
-  if (r.init_status >= bshmem::INIT_IS_INITIALIZED && r.have_gpu) {
-    void* addr = getter();
-    if (addr) cudaMemcpy(addr, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice);
-  }
+  r.modules_pending.store(true);
 }

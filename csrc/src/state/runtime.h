@@ -94,6 +94,7 @@ struct Runtime {
   std::vector<uint64_t> team_bitmap;         // 1 = free
   int max_teams = 128;
   std::vector<std::pair<StateAddrGetter, std::string>> modules;
+  std::atomic<bool> modules_pending{false};  // a module registered after the last state push
   cudaStream_t stream = nullptr;             // internal stream of blocking calls
   std::vector<cudaStream_t> peer_streams;    // non-blocking host RMA, indexed by distance % size
   std::vector<bool> peer_stream_used;
@@ -114,6 +115,7 @@ Runtime& rt();
 int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_hint, bool hostlib_only, int boot_mode);
 int runtime_finalize();
 int push_device_state();   // copies dstate into every registered module
+void push_pending_modules(); // the same, only if a module registered since the last push
 bool is_initialized();
 int probe_topology(Runtime& r);
 void watchdog_start(Runtime& r);

@@ -144,6 +144,7 @@ def load() -> C.CDLL:
     sig("nvshmemx_b200_fcollect_on_stream", i32, i32, vp, vp, sz, i32, stream)
     sig("nvshmemx_b200_broadcast_on_stream", i32, i32, vp, vp, sz, i32, i32, stream)
     sig("nvshmemx_double2_maxloc_reduce_on_stream", i32, i32, vp, vp, sz, stream)
+    sig("nvshmemx_b200_module_sync", None)
     sig("nvshmemx_b200_error_bits", C.c_uint32)
     sig("nvshmemx_b200_clear_errors", None)
     sig("nvshmemx_b200_timeout_info", C.c_uint32, C.POINTER(StatusBlock))

@@ -1,0 +1,124 @@
+"""Fused tensor-parallel GEMM + collective against cuBLAS + NCCL on the same GPUs.
+
+  row parallel   : x[M, K/n] @ w[N, K/n]^T -> reduce-scatter      ours: one fused kernel; baseline: matmul + reduce_scatter_tensor
+  column parallel: all-gather(x[M/n, K]) @ w[N/n, K]^T            ours: one fused kernel; baseline: all_gather_into_tensor + matmul
+Default shapes are the TP=8 configuration (M=8192, hidden 8192, ffn 28672).  Also reports the fraction of the
+roofline: max(FLOPs / measured cuBLAS peak, bytes over NVLink / 770 GB/s).
+
+  torchrun --nproc-per-node 8 -m perftest.fused
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .common import Env
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--ffn", type=int, default=28672)
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    env = Env()
+    nv, n = env.nv, env.world
+    from nvshmem_b200.ops import fused_gemm as fg
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak_tflops = peaks.get("bf16_tflops", 1590.0)
+    link_gbs = 770.0
+    M, H = args.M, args.hidden
+    ffn_local = args.ffn // 8  # per-GPU work stays that of TP=8 whatever n is (weak scaling)
+    sets = 3
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=env.dev)
+    flush = lambda: flush_buf.zero_()
+
+    def report(name, ms, flops, link_bytes, **extra):
+        t_compute = flops / (peak_tflops * 1e12) * 1e3
+        t_link = link_bytes / (link_gbs * 1e9) * 1e3
+        roof = max(t_compute, t_link)
+        env.record(test=name, ms=round(ms, 4), TFLOPs_per_gpu=round(flops / (ms * 1e-3) / 1e12, 1), roofline_ms=round(roof, 4), fraction_of_roofline=round(roof / ms, 3),
+                   bound="compute" if t_compute >= t_link else "nvlink", npes=n, **extra)
+
+    # ---- row parallel: GEMM -> reduce-scatter
+    K = ffn_local
+    x = [torch.randn(M, K, device=env.dev).to(torch.bfloat16) for _ in range(sets)]
+    w = [(torch.randn(H, K, device=env.dev) * 0.02).to(torch.bfloat16) for _ in range(sets)]
+    flops = 2.0 * M * H * K
+    link = (n - 1) / n * M * H * 2
+    i = [0]
+    for mode in ("rs", "ar"):
+        op = fg.GemmReduceScatter(M, H, mode=mode)
+        def step():
+            i[0] += 1
+            op(x[i[0] % sets], w[i[0] % sets])
+        ms = env.time_ms(step, iters=args.iters, warmup=5)
+        fg.check_errors()
+        report(f"gemm_{mode}_fused", ms, flops, link * (2 if mode == "ar" else 1), M=M, N=H, K=K)
+        op.close()
+    if n > 1:
+        partial = torch.empty(M, H, dtype=torch.bfloat16, device=env.dev)
+        outp = torch.empty(M // n, H, dtype=torch.bfloat16, device=env.dev)
+        def base():
+            i[0] += 1
+            torch.matmul(x[i[0] % sets], w[i[0] % sets].t(), out=partial)
+            dist.reduce_scatter_tensor(outp, partial)
+        ms = env.time_ms(base, iters=args.iters, warmup=5)
+        report("gemm_rs_cublas_nccl", ms, flops, link, M=M, N=H, K=K)
+        def base_ar():
+            i[0] += 1
+            torch.matmul(x[i[0] % sets], w[i[0] % sets].t(), out=partial)
+            dist.all_reduce(partial)
+        ms = env.time_ms(base_ar, iters=args.iters, warmup=5)
+        report("gemm_ar_cublas_nccl", ms, flops, 2 * link, M=M, N=H, K=K)
+    out = torch.empty(M, H, dtype=torch.bfloat16, device=env.dev)
+    def mm():
+        i[0] += 1
+        torch.matmul(x[i[0] % sets], w[i[0] % sets].t(), out=out)
+    ms = env.time_ms(mm, iters=args.iters, warmup=5)
+    report("gemm_only_cublas", ms, flops, 0, M=M, N=H, K=K)
+    def mine():
+        i[0] += 1
+        fg.gemm(x[i[0] % sets], w[i[0] % sets], out)
+    ms = env.time_ms(mine, iters=args.iters, warmup=5)
+    report("gemm_only_tcgen05", ms, flops, 0, M=M, N=H, K=K)
+    del x, w
+
+    # ---- column parallel: all-gather -> GEMM
+    Nl = ffn_local
+    ws = [(torch.randn(Nl, H, device=env.dev) * 0.02).to(torch.bfloat16) for _ in range(sets)]
+    shard = torch.randn(M // n, H, device=env.dev).to(torch.bfloat16)
+    flops = 2.0 * M * Nl * H
+    link = (n - 1) / n * M * H * 2
+    ag = fg.AllGatherGemm(M, H)
+    ag.shard.copy_(shard)
+    def step_ag():
+        i[0] += 1
+        ag(ws[i[0] % sets])
+    ms = env.time_ms(step_ag, iters=args.iters, warmup=5)
+    fg.check_errors()
+    report("ag_gemm_fused", ms, flops, link, M=M, N=Nl, K=H)
+    if n > 1:
+        gathered = torch.empty(M, H, dtype=torch.bfloat16, device=env.dev)
+        out2 = torch.empty(M, Nl, dtype=torch.bfloat16, device=env.dev)
+        def base_ag():
+            i[0] += 1
+            dist.all_gather_into_tensor(gathered, shard)
+            torch.matmul(gathered, ws[i[0] % sets].t(), out=out2)
+        ms = env.time_ms(base_ag, iters=args.iters, warmup=5)
+        report("ag_gemm_cublas_nccl", ms, flops, link, M=M, N=Nl, K=H)
+    ag.close()
+    env.finish()
+
+
+if __name__ == "__main__":
+    main()

@@ -280,6 +280,7 @@ def _devtest():
     from nvshmem_b200.bindings import host as H
     H.load()
     lib = C.CDLL(str(H.lib_path("libbshmem_devtest.so")))
+    H.load().nvshmemx_b200_module_sync()  # the library was loaded after init: hand it the device state
     assert lib.devtest_preload() == 0
     return lib
 
