@@ -309,28 +309,47 @@ __device__ __forceinline__ void record_timeout(const void* addr, uint64_t expect
   __threadfence_system();
   atomicOr_system((unsigned int*)&s->error_bits, BSHMEM_ERR_WAIT_TIMEOUT);
 }
-// Polls with acquire loads until cmp(*ivar, value) holds.  Returns 0 on success,
-// 1 after `wait_timeout_ns` (the time-out is recorded; the caller carries on).
+// One polling read with acquire semantics at system scope: 32- and 64-bit words use ld.acquire.sys
+// (no separate fence is then needed once the comparison holds); narrower types use a volatile load
+// and the caller fences.
+template <class T>
+__device__ __forceinline__ T poll_load(const T* p, bool* needs_fence) {
+  if (sizeof(T) == 8) {
+    uint64_t v = ld_acquire_sys((const uint64_t*)p);
+    T out;
+    memcpy(&out, &v, 8);
+    return out;
+  } else if (sizeof(T) == 4) {
+    uint32_t v = ld_acquire_sys((const uint32_t*)p);
+    T out;
+    memcpy(&out, &v, 4);
+    return out;
+  }
+  *needs_fence = true;
+  return *(const volatile T*)p;
+}
+// Polls until cmp(*ivar, value) holds.  Returns 0 on success, 1 after `wait_timeout_ns`
+// (the time-out is recorded; the caller carries on).  Data published before the flag is
+// visible to the caller on return.
 template <class T>
 __device__ __forceinline__ int wait_until(const T* ivar, int cmp, T value, uint32_t where = BSHMEM_WHERE_WAIT_UNTIL) {
-  const volatile T* v = (const volatile T*)ivar;
-  T found = *v;
+  bool needs_fence = false;
+  T found = poll_load(ivar, &needs_fence);
   if (!compare(found, cmp, value)) {
     const uint64_t start = global_timer_ns(), limit = bshmemi_state_d.wait_timeout_ns;
     uint32_t spins = 0;
     for (;;) {
-      found = *v;
+      found = poll_load(ivar, &needs_fence);
       if (compare(found, cmp, value)) break;
-      if ((++spins & 0xff) == 0) {
+      if ((++spins & 0x3ff) == 0) {
         if (global_timer_ns() - start > limit) {
           record_timeout((const void*)ivar, (uint64_t)value, (uint64_t)found, where);
           return 1;
         }
-        __nanosleep(20);
       }
     }
   }
-  fence_sys();  // acquire: data published before the flag is visible after this
+  if (needs_fence) fence_sys();
   return 0;
 }
 __device__ __forceinline__ int wait_ge_u64(const uint64_t* ivar, uint64_t value, uint32_t where) {
@@ -338,9 +357,10 @@ __device__ __forceinline__ int wait_ge_u64(const uint64_t* ivar, uint64_t value,
 }
 template <class T>
 __device__ __forceinline__ int test(const T* ivar, int cmp, T value) {
-  T found = *(const volatile T*)ivar;
+  bool needs_fence = false;
+  T found = poll_load(ivar, &needs_fence);
   if (!compare(found, cmp, value)) return 0;
-  fence_sys();
+  if (needs_fence) fence_sys();
   return 1;
 }
 // wait_until_all / any / some and their _vector forms.  `status[i] != 0` excludes entry i.

@@ -70,11 +70,18 @@ __global__ void __launch_bounds__(1024) k_put_latency(char* sym, char* local, si
     else if (threadIdx.x == 0) { nvshmem_putmem(sym, local, bytes, pe); nvshmem_quiet(); }
   }
 }
+// Each get starts where the previous one's data says (the driver zeroes the source buffer, so always offset 0):
+// the chain makes consecutive gets dependent, so the time per iteration is a latency, not a rate.
 __global__ void __launch_bounds__(1024) k_get_latency(char* sym, char* local, size_t bytes, int pe, int iters, int scope) {
+  __shared__ size_t off;
+  if (threadIdx.x == 0) off = 0;
+  __syncthreads();
   for (int it = 0; it < iters; ++it) {
-    if (scope == 2) nvshmemx_getmem_block(local, sym, bytes, pe);
-    else if (scope == 1) { if (threadIdx.x < 32) nvshmemx_getmem_warp(local, sym, bytes, pe); }
-    else if (threadIdx.x == 0) nvshmem_getmem(local, sym, bytes, pe);
+    if (scope == 2) nvshmemx_getmem_block(local, sym + off, bytes, pe);
+    else if (scope == 1) { if (threadIdx.x < 32) nvshmemx_getmem_warp(local, sym + off, bytes, pe); }
+    else if (threadIdx.x == 0) nvshmem_getmem(local, sym + off, bytes, pe);
+    __syncthreads();
+    if (threadIdx.x == 0) off = (size_t)(*(volatile unsigned char*)local);  // data-dependent; the data is zero
     __syncthreads();
   }
 }

@@ -51,7 +51,10 @@ def main():
                 ms = env.time_ms(fn, iters=5, warmup=2)
                 moved = (size // ctas // 16 * 16) * ctas
                 env.record(test=f"{dname}_bw", scope=scope_name[scope], bytes=size, ctas=ctas, us=round(ms * 1e3 / iters, 3), GBps=round(moved * iters / (ms * 1e-3) / 1e9, 2), npes=n)
-    # ---- blocking latency (one group, put + quiet / get)
+    # ---- blocking latency (one group, put + quiet / get); the get chain reads its next offset from the data, which is zero
+    sym.zero_()
+    local.zero_()
+    env.barrier()
     for dname, call in (("put_latency", lib.perf_put_latency), ("get_latency", lib.perf_get_latency)):
         for scope in (0, 1, 2):
             for size in sizes_pow2(min_bytes, min(max_bytes, 1 << 20)):
