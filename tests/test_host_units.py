@@ -1,0 +1,188 @@
+"""Unit tests of the host library's pure-CPU pieces through its C test hooks: option parsing, log and
+NVTX masks, the allocator (against an interval model), and the nvshmem-info tool."""
+import ctypes as C
+import os
+import random
+import subprocess
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def lib(hostlib):
+    hostlib.bshmem_test_alloc_new.restype = C.c_void_p
+    hostlib.bshmem_test_alloc_malloc.restype = C.c_longlong
+    hostlib.bshmem_test_alloc_digest.restype = C.c_ulonglong
+    hostlib.bshmem_test_alloc_in_use.restype = C.c_ulonglong
+    hostlib.bshmem_test_alloc_largest_free.restype = C.c_ulonglong
+    hostlib.bshmem_test_log_subsys.restype = C.c_uint
+    hostlib.bshmem_test_nvtx_groups.restype = C.c_uint
+    return hostlib
+
+
+@pytest.mark.parametrize("text,want", [("1024", 1024), ("20m", 20 << 20), ("20M", 20 << 20), ("3.1M", 3250586), (".5m", 524288), ("0.5g", 1 << 29),
+                                       ("2t", 2 << 40), ("7k", 7168), ("20kk", 20 << 10)])
+def test_size_parser_accepts_suffixes(lib, text, want):
+    out = C.c_ulonglong()
+    assert lib.bshmem_test_parse_size(text.encode(), C.byref(out)) == 0
+    assert out.value == want
+
+
+@pytest.mark.parametrize("text", ["", "abc", "-5", "12q", "m"])
+def test_size_parser_rejects_junk(lib, text):
+    out = C.c_ulonglong()
+    assert lib.bshmem_test_parse_size(text.encode(), C.byref(out)) != 0
+
+
+@pytest.mark.parametrize("text,want", [("1", 1), ("true", 1), ("YES", 1), ("on", 1), ("", 1), ("0", 0), ("False", 0), ("no", 0), ("off", 0)])
+def test_bool_parser(lib, text, want):
+    out = C.c_int(-1)
+    assert lib.bshmem_test_parse_bool(text.encode(), C.byref(out)) == 0 and out.value == want
+
+
+def test_bool_parser_rejects_junk(lib):
+    out = C.c_int()
+    assert lib.bshmem_test_parse_bool(b"maybe", C.byref(out)) != 0
+
+
+def test_log_subsystem_masks(lib):
+    INIT, COLL, MEM = 1, 2, 32
+    assert lib.bshmem_test_log_subsys(b"") == 0xFFFFFFFF
+    assert lib.bshmem_test_log_subsys(b"INIT,COLL") == INIT | COLL
+    assert lib.bshmem_test_log_subsys(b"mem") == MEM
+    assert lib.bshmem_test_log_subsys(b"^MEM") == (~MEM) & 0xFFFFFFFF
+    assert lib.bshmem_test_log_subsys(b"ALL") == 0xFFFFFFFF
+
+
+def test_nvtx_groups(lib):
+    assert lib.bshmem_test_nvtx_groups(b"off") == 0
+    assert lib.bshmem_test_nvtx_groups(b"init,coll") == (1 | 8)
+    assert lib.bshmem_test_nvtx_groups(b"all") == 0xFFFFFFFF
+    common = lib.bshmem_test_nvtx_groups(b"common")
+    assert common & 1 and common & 2 and common & 8 and not common & (1 << 11)
+
+
+def test_invalid_environment_value_is_counted(lib):
+    os.environ["NVSHMEM_SYMMETRIC_SIZE"] = "lots"
+    try:
+        assert lib.bshmem_test_options_count_bad() == 1
+    finally:
+        del os.environ["NVSHMEM_SYMMETRIC_SIZE"]
+    assert lib.bshmem_test_options_count_bad() == 0
+
+
+def test_options_dump_reflects_environment(lib):
+    os.environ["NVSHMEM_MAX_TEAMS"] = "77"
+    try:
+        buf = C.create_string_buffer(32768)
+        lib.bshmem_test_options_dump(buf, len(buf))
+        text = buf.value.decode()
+        assert "NVSHMEM_MAX_TEAMS=77 (set)" in text and "NVSHMEM_SYMMETRIC_SIZE=1073741824" in text
+    finally:
+        del os.environ["NVSHMEM_MAX_TEAMS"]
+
+
+class IntervalModel:
+    """Reference allocator: first fit over a sorted free list, 512-byte granule, same alignment rule."""
+
+    def __init__(self, cap):
+        self.free = [(0, cap)]
+        self.used = {}
+
+    def malloc(self, size, align):
+        size = (size + 511) // 512 * 512
+        align = max(align, 512)
+        for i, (s, l) in enumerate(self.free):
+            a = (s + align - 1) // align * align
+            if a + size <= s + l:
+                parts = []
+                if a > s:
+                    parts.append((s, a - s))
+                if s + l > a + size:
+                    parts.append((a + size, s + l - a - size))
+                self.free[i:i + 1] = parts
+                self.used[a] = size
+                return a
+        return -1
+
+    def release(self, off):
+        size = self.used.pop(off)
+        self.free.append((off, size))
+        self.free.sort()
+        merged = []
+        for s, l in self.free:
+            if merged and merged[-1][0] + merged[-1][1] == s:
+                merged[-1] = (merged[-1][0], merged[-1][1] + l)
+            else:
+                merged.append((s, l))
+        self.free = merged
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_allocator_matches_interval_model(lib, seed):
+    cap = 64 << 20
+    h = C.c_void_p(lib.bshmem_test_alloc_new(cap))
+    model = IntervalModel(cap)
+    rng = random.Random(seed)
+    live = []
+    for step in range(600):
+        if live and rng.random() < 0.45:
+            off = live.pop(rng.randrange(len(live)))
+            assert lib.bshmem_test_alloc_free(h, off) == 0
+            model.release(off)
+        else:
+            size = int(2 ** rng.uniform(3, 21))
+            align = rng.choice([0, 64, 256, 4096, 1 << 16])
+            got = lib.bshmem_test_alloc_malloc(h, size, align)
+            want = model.malloc(size, align)
+            assert got == want, (step, size, align, got, want)
+            if got >= 0:
+                assert got % max(align, 512) == 0
+                live.append(got)
+        assert lib.bshmem_test_alloc_check(h) == 0
+    assert lib.bshmem_test_alloc_in_use(h) == sum(model.used.values())
+    assert lib.bshmem_test_alloc_free(h, 12345) != 0  # unknown offset is refused
+    for off in live:
+        lib.bshmem_test_alloc_free(h, off)
+    assert lib.bshmem_test_alloc_largest_free(h) == cap  # everything coalesced again
+    lib.bshmem_test_alloc_delete(h)
+
+
+def test_allocator_history_digest_is_order_sensitive(lib):
+    a, b = C.c_void_p(lib.bshmem_test_alloc_new(1 << 20)), C.c_void_p(lib.bshmem_test_alloc_new(1 << 20))
+    x = lib.bshmem_test_alloc_malloc(a, 1000, 0)
+    y = lib.bshmem_test_alloc_malloc(a, 2000, 0)
+    y2 = lib.bshmem_test_alloc_malloc(b, 2000, 0)
+    x2 = lib.bshmem_test_alloc_malloc(b, 1000, 0)
+    assert (x, y) != (x2, y2)
+    assert lib.bshmem_test_alloc_digest(a) != lib.bshmem_test_alloc_digest(b)
+    lib.bshmem_test_alloc_delete(a)
+    lib.bshmem_test_alloc_delete(b)
+
+
+def test_allocator_growth_adds_adjacent_chunk(lib):
+    h = C.c_void_p(lib.bshmem_test_alloc_new(1 << 20))
+    assert lib.bshmem_test_alloc_malloc(h, 2 << 20, 0) == -1
+    lib.bshmem_test_alloc_grow(h, 1 << 20, 3 << 20)
+    assert lib.bshmem_test_alloc_malloc(h, 2 << 20, 0) == 0  # the old and the new chunk coalesced
+    assert lib.bshmem_test_alloc_check(h) == 0
+    lib.bshmem_test_alloc_delete(h)
+
+
+def test_nvshmem_info_tool():
+    from nvshmem_b200.bindings import host as H
+    exe = H.lib_path("nvshmem-info")
+    if not exe.exists():
+        from nvshmem_b200.utils.build import build_all
+        build_all(only="info")
+    out = subprocess.run([str(exe), "-a"], capture_output=True, text=True, env=dict(os.environ, NVSHMEM_SYMMETRIC_SIZE="2g"))
+    assert out.returncode == 0
+    assert "NVSHMEM_SYMMETRIC_SIZE" in out.stdout and "2147483648" in out.stdout and "sm_100a" in out.stdout
+    rst = subprocess.run([str(exe), "-e", "-r"], capture_output=True, text=True)
+    assert ".. c:var:: NVSHMEM_DEBUG" in rst.stdout
+
+
+def test_python_layer_imports_and_reports_version():
+    import nvshmem_b200.core as nv
+    v = nv.get_version()
+    assert v["openshmem_spec_version"] == (1, 3) and v["libnvshmem_version"][0] == 3
