@@ -28,136 +28,32 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <map>
 #include <mutex>
 #include <tuple>
 
-#include "../../include/bshmem/fused.h"
-#include "../../include/bshmem/tcgen05.cuh"
+
+#include "gemm_fused_common.cuh"
 
 namespace bshmem {
 using namespace sm100;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2;
-constexpr int EPI_COLS = 64, EPI_BUF = BM * EPI_COLS * 2, EPI_BUFS = 2;
-constexpr int TMEM_COLS = 512, ACC_COLS = BN;
-constexpr int NTHREADS = 256, EPI_THREADS = 128, EPI_WARP0 = 4;
-constexpr int COMM_PIECE = 16384, COMM_BUFS = 8, COMM_AHEAD = 4;
-constexpr int SMEM_TILES = STAGES * (A_STAGE + B_STAGE) + EPI_BUFS * EPI_BUF;
-constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-static_assert(COMM_PIECE * COMM_BUFS <= SMEM_TILES, "the sender's ring must fit in the GEMM's shared memory");
-
-struct alignas(64) FusedParams {
-  CUtensorMap tmA, tmB;
-  CUtensorMap tmOut[BSHMEM_FUSED_MAX_PES];   // PLAIN/RS/AG: [0] is the local output; AR: output of each PE
-  CUtensorMap tmRecv[BSHMEM_FUSED_MAX_PES];  // RS/AR: my slot in the receive buffer of each PE
-  const __nv_bfloat16* recv_local;           // [npes][M/npes][N] partials received from each PE
-  uint64_t* flags_local;                     // [npes][tiles per PE]
-  uint64_t* flags_peer[BSHMEM_FUSED_MAX_PES];
-  const char* ag_src;                        // my shard inside my gathered buffer
-  char* ag_dst[BSHMEM_FUSED_MAX_PES];        // the same shard inside each PE's gathered buffer
-  uint64_t* ag_flags_local;                  // [npes][m-tiles per shard]
-  uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
-  int* error_flag;
-  uint64_t epoch, wait_limit_ns, ag_unit_bytes;
-  uint32_t ag_piece_bytes;  // size of one bulk copy of the sender (16-byte multiple, at most COMM_PIECE)
-  int M, N, K, rank, npes, mode, n_comm, ag_parts, ag_tiles_per_unit;
-};
-
-struct TileInfo {
-  int m_tile, n_tile;   // position in the full output
-  int peer;             // RS/AR: PE that owns the rows; AG: PE whose shard holds the rows
-  int m_local;          // m-tile index inside that PE's block of rows
-  int idx_in_peer;      // tile number inside the block (flag index)
-};
-
-// Tile order.  Blocks of rows are visited peer by peer (RS/AR: rank+1, rank+2, …, own last; AG: own, rank-1, …);
-// inside a block m runs fastest so that concurrently running CTAs share B tiles through L2.
-__device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
-  const int tiles_n = p.N / BN;
-  const int tmr = (p.M / p.npes) / BM;
-  const int per_peer = tmr * tiles_n;
-  const int o = t / per_peer, within = t % per_peer;
-  TileInfo ti;
-  if (p.mode == BSHMEM_FUSED_AG) ti.peer = (p.rank - o + p.npes) % p.npes;
-  else ti.peer = (p.rank + 1 + o) % p.npes;
-  ti.m_local = within % tmr;
-  ti.n_tile = within / tmr;
-  ti.m_tile = ti.peer * tmr + ti.m_local;
-  ti.idx_in_peer = within;
-  return ti;
-}
-
-__device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t want, uint64_t limit_ns, volatile int* abort_flag) {
-  uint64_t v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
-  if (v >= want) return true;
-  const uint64_t start = timer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
-    if (v >= want) return true;
-    if ((++spins & 31) == 0) {
-      if (*abort_flag) return false;
-      if (timer_ns() - start > limit_ns) {
-        *abort_flag = 1;
-        return false;
-      }
-      __nanosleep(64);
-    }
-  }
-}
-
-// ------------------------------------------------------------------ all-gather sender (MODE_AG, extra CTAs)
-__device__ void ag_sender(const FusedParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
-  if (threadIdx.x != 0) return;
-  const int unit = blockIdx.x;  // one unit of my shard per sender CTA
-  const size_t unit_off = (size_t)unit * p.ag_unit_bytes;
-  const uint32_t PIECE = p.ag_piece_bytes;
-  const int pieces = (int)(p.ag_unit_bytes / PIECE);
-  const int tmr = (p.M / p.npes) / BM;
-  uint32_t phase_bits = 0;  // one parity bit per ring slot
-  for (int o = 1; o < p.npes && !*abort_flag; ++o) {
-    const int peer = (p.rank + o) % p.npes;
-    const char* src = p.ag_src + unit_off;
-    char* dst = p.ag_dst[peer] + unit_off;
-    const int ahead = pieces < COMM_AHEAD ? pieces : COMM_AHEAD;
-    for (int q = 0; q < ahead; ++q) {
-      mbar_expect_tx(&bars[q % COMM_BUFS], PIECE);
-      bulk_load(smem + (q % COMM_BUFS) * COMM_PIECE, src + (size_t)q * PIECE, PIECE, &bars[q % COMM_BUFS]);
-    }
-    for (int q = 0; q < pieces; ++q) {
-      const int nxt = q + COMM_AHEAD;
-      if (nxt < pieces) {
-        // Ring slot of piece `nxt` was last used by piece nxt-COMM_BUFS, stored COMM_BUFS-COMM_AHEAD iterations ago.
-        bulk_wait_read<COMM_BUFS - COMM_AHEAD - 1>();
-        mbar_expect_tx(&bars[nxt % COMM_BUFS], PIECE);
-        bulk_load(smem + (nxt % COMM_BUFS) * COMM_PIECE, src + (size_t)nxt * PIECE, PIECE, &bars[nxt % COMM_BUFS]);
-      }
-      const int slot = q % COMM_BUFS;
-      if (!mbar_wait(&bars[slot], (phase_bits >> slot) & 1, p.wait_limit_ns, abort_flag)) break;
-      phase_bits ^= 1u << slot;
-      bulk_store(dst + (size_t)q * PIECE, smem + slot * COMM_PIECE, PIECE);
-      bulk_commit();
-    }
-    bulk_wait<0>();  // every byte of the unit has been written to the peer
-    fence_proxy_async_all();
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
-    // Tell the peer which 128-row blocks are (partly) complete.
-    const int first_tile = p.ag_parts > 1 ? unit / p.ag_parts : unit * p.ag_tiles_per_unit;
-    const int ntiles = p.ag_parts > 1 ? 1 : p.ag_tiles_per_unit;
-    for (int j = 0; j < ntiles; ++j) {
-      uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + first_tile + j;
-      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)1) : "memory");
-    }
-  }
-  bulk_wait<0>();
-}
-
 // ------------------------------------------------------------------ the kernel
+// PAIR = false: every CTA owns 128 x 256 output tiles (4 stages of A 16 KB + B 32 KB).
+// PAIR = true:  clusters of two CTAs; CTA r of a pair owns tile 2u + r of the same tile order, so the
+// two tiles share their 256 columns.  Each CTA loads its own 128 rows of A and HALF of the B tile
+// (6 stages of 16 KB + 16 KB), the even CTA issues one 256 x 256 x 16 MMA per K step for both, and each
+// CTA's tensor memory receives its own 128 x 256 accumulator: per SM, half the B traffic from L2 and
+// half the shared-memory reads per FLOP.  Everything after the accumulator (epilogue, flags, stores)
+// is per CTA and identical in both variants.
+template <bool PAIR>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_constant__ FusedParams p) {
+  constexpr int STAGES = PAIR ? 6 : 4;
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;
+  constexpr int B_STAGE = B_ROWS * BK * 2;
+  static_assert(STAGES * (A_STAGE + B_STAGE) + EPI_BUFS * EPI_BUF == SMEM_TILES, "both variants use the same shared-memory budget");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -172,6 +68,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0;  // sender CTAs come in whole pairs: n_comm is even
   const bool is_sender = p.mode == BSHMEM_FUSED_AG && (int)blockIdx.x < p.n_comm;
 
   if (threadIdx.x == 0) {
@@ -180,12 +77,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
       for (int i = 0; i < COMM_BUFS; ++i) mbar_init(&bars[i], 1);
     } else {
       for (int i = 0; i < STAGES; ++i) {
-        mbar_init(&full[i], 1);
+        mbar_init(&full[i], PAIR ? 2 : 1);  // pair: one arrival (with its byte count) from each CTA's producer
         mbar_init(&empty[i], 1);
       }
       for (int i = 0; i < 2; ++i) {
         mbar_init(&acc_full[i], 1);
-        mbar_init(&acc_empty[i], EPI_THREADS);
+        mbar_init(&acc_empty[i], (PAIR ? 2 : 1) * (EPI_THREADS / 32));  // one arrival per epilogue warp
       }
     }
     mbar_fence_init();
@@ -204,14 +101,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_n = p.N / BN;
   const int total_tiles = (p.M / BM) * tiles_n;
   const int kblocks = p.K / BK;
-  const int first = (int)blockIdx.x - (p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0);
-  const int step = (int)gridDim.x - (p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0);
+  const int n_send = p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0;
+  // Pair: worker u = pair index takes tiles 2u + r, 2(u + workers) + r, …
+  const int first = PAIR ? (((int)blockIdx.x - n_send) & ~1) + (int)cta_rank : (int)blockIdx.x - n_send;
+  const int step = (int)gridDim.x - n_send;
   const int tmr = (p.M / p.npes) / BM;
 
   if (warp == 0) {
@@ -230,17 +130,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, p.wait_limit_ns, abort_flag)) break;
-          mbar_expect_tx(&full[stage], A_STAGE + B_STAGE);
-          tma_load_2d(sA + stage * A_STAGE, &p.tmA, &full[stage], kb * BK, ti.m_tile * BM);
-          tma_load_2d(sB + stage * B_STAGE, &p.tmB, &full[stage], kb * BK, ti.n_tile * BN);
+          if (PAIR) {
+            const uint32_t lead = mapa_u32(smem_u32(&full[stage]), 0);
+            mbar_expect_tx_cluster(lead, A_STAGE + B_STAGE);
+            tma_load_2d_pair(sA + stage * A_STAGE, &p.tmA, lead, kb * BK, ti.m_tile * BM);
+            tma_load_2d_pair(sB + stage * B_STAGE, &p.tmB, lead, kb * BK, ti.n_tile * BN + (int)cta_rank * B_ROWS);
+          } else {
+            mbar_expect_tx(&full[stage], A_STAGE + B_STAGE);
+            tma_load_2d(sA + stage * A_STAGE, &p.tmA, &full[stage], kb * BK, ti.m_tile * BM);
+            tma_load_2d(sB + stage * B_STAGE, &p.tmB, &full[stage], kb * BK, ti.n_tile * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+      }
+      // The MMA side still arrives on the empty barriers of the last fills: wait for those arrivals,
+      // so that none of them (in a pair they come from the other SM) finds this CTA gone.
+      for (int i = 0; i < STAGES && !*abort_flag; ++i) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, p.wait_limit_ns, abort_flag)) break;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+    if ((!PAIR || cta_rank == 0) && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR ? 2 * BM : BM, BN);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int t = first; t < total_tiles && !*abort_flag; t += step) {
@@ -256,13 +169,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // Advancing K inside the 128-byte swizzle atom: +32 bytes = +2 in descriptor address units.
-            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            if (PAIR) umma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            else umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
           }
-          umma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          // The stage is free (in both CTAs of a pair) once these MMAs have read it.
+          if (PAIR) umma_commit_pair(&empty[stage]);
+          else umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(&acc_full[acc]);
+        if (PAIR) umma_commit_pair(&acc_full[acc]);
+        else umma_commit(&acc_full[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -304,7 +221,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         if (c == BN / EPI_COLS - 1) {
           // All of this accumulator is in registers: hand the TMEM buffer back to the MMA warp.
           tc_fence_before_sync();
-          mbar_arrive(&acc_empty[acc]);
+          __syncwarp();
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[acc]), 0));
+            else mbar_arrive(&acc_empty[acc]);
+          }
         }
         if (reduce_mode && own) {
           const size_t rows_per_pe = (size_t)p.M / p.npes;
@@ -378,40 +299,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   }
   tc_fence_before_sync();
   __syncthreads();
+  // Pair: neither CTA leaves (or frees tensor memory the leader's MMAs write) before both are done.
+  if (PAIR) cluster_sync_all();
   if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 1);
 }
 
-// ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)sym;
-  });
-  return fn;
-}
-
-// Row-major bf16 matrix [rows, cols], box [box_rows, 64 columns], 128-byte swizzle.
-static int make_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return BSHMEM_FUSED_ERR_DRIVER;
-  if (((uintptr_t)base & 15) || (cols * 2) % 16) return BSHMEM_FUSED_ERR_ALIGNMENT;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : BSHMEM_FUSED_ERR_DRIVER;
-}
-
 static int g_attr_set_for_device = -1;
+
+// CTA pairs are the default where the shape allows them; BSHMEM_FUSED_2CTA=0 selects one CTA per tile.
+static bool pair_wanted() {
+  static const bool on = [] {
+    const char* e = getenv("BSHMEM_FUSED_2CTA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 }  // namespace bshmem
 
@@ -430,8 +333,14 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   p.error_flag = a->error_flag;
   const int rows_per_pe = a->M / npes;
   const int tmr = rows_per_pe / BM;
+  int device = 0, sms = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  int grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
+  // A pair takes two consecutive 128-row tiles of one PE's block of rows.
+  bool pair = pair_wanted() && rows_per_pe % (2 * BM) == 0 && grid >= 2;
+  if (pair) grid &= ~1;
   int st = make_map(&p.tmA, a->A, a->M, a->K, BM);
-  if (!st) st = make_map(&p.tmB, a->B, a->N, a->K, BN);
   if (st) return st;
   const bool reduce_mode = (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1;
   if (mode == BSHMEM_FUSED_AR && npes > 1) {
@@ -457,15 +366,24 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
     }
     if (st) return st;
   }
-  int device = 0, sms = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  int grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
   if (mode == BSHMEM_FUSED_AG && npes > 1) {
     if (!a->ag_flags_local) return BSHMEM_FUSED_ERR_ARGS;
-    int n_comm = a->n_comm > 0 ? a->n_comm : 16;
-    // One unit of the shard per sender CTA; units and 128-row blocks must nest.
-    while (n_comm > 1 && !((n_comm % tmr == 0 && BM % (rows_per_pe / n_comm) == 0 && rows_per_pe % n_comm == 0) || tmr % n_comm == 0)) --n_comm;
+    // One unit of the shard per sender CTA; units and 128-row blocks must nest.  Pairs need an even count.
+    auto pick_n_comm = [&](bool even) {
+      int n = a->n_comm > 0 ? a->n_comm : 16;
+      auto fits = [&](int c) {
+        const bool nests = (c % tmr == 0 && rows_per_pe % c == 0 && BM % (rows_per_pe / c) == 0) || tmr % c == 0;
+        return nests && !(even && (c & 1));
+      };
+      while (n > 1 && !fits(n)) --n;
+      return n;
+    };
+    int n_comm = pick_n_comm(pair);
+    if (pair && (n_comm & 1)) {
+      pair = false;
+      grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
+      n_comm = pick_n_comm(false);
+    }
     const size_t shard_bytes = (size_t)rows_per_pe * a->K * 2;
     p.n_comm = n_comm;
     p.ag_unit_bytes = shard_bytes / n_comm;
@@ -484,18 +402,38 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
       p.ag_dst[q] = (char*)a->ag_peer[q] + (size_t)a->rank * shard_bytes;
       p.ag_flags_peer[q] = a->ag_flags_peer[q];
     }
-    if (grid - n_comm < 1) return BSHMEM_FUSED_ERR_ARGS;
+    if (grid - n_comm < (pair ? 2 : 1)) return BSHMEM_FUSED_ERR_ARGS;
   }
+  st = make_map(&p.tmB, a->B, a->N, a->K, pair ? BN / 2 : BN);
+  if (st) return st;
   if (g_attr_set_for_device != device) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) {
       fprintf(stderr, "bshmem_fused_gemm: cannot reserve %d bytes of shared memory: %s\n", SMEM_BYTES, cudaGetErrorString(e));
       return BSHMEM_FUSED_ERR_DRIVER;
     }
     g_attr_set_for_device = device;
   }
-  gemm_fused_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemm_fused_kernel<true>, p);
+  } else {
+    gemm_fused_kernel<false><<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     fprintf(stderr, "bshmem_fused_gemm: launch failed: %s\n", cudaGetErrorString(e));
     return BSHMEM_FUSED_ERR_DRIVER;
