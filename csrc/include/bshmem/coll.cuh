@@ -60,13 +60,15 @@ __device__ __forceinline__ int team_translate_pe(int src_team, int src_pe, int d
 }
 
 // ------------------------------------------------------------------ sync / barrier
-// Polls a flag with relaxed loads until it reaches `want` (no fence: the caller fences once after all its polls).
-__device__ __forceinline__ int poll_ge_relaxed(const uint64_t* flag, uint64_t want) {
-  if (ld_relaxed_sys(flag) >= want) return 0;
+// Polls a flag until it reaches `want`.  ACQUIRE = true polls with acquire loads, so the data published
+// before the flag is visible to this thread on return; false leaves that to a fence of the caller.
+template <bool ACQUIRE>
+__device__ __forceinline__ int poll_ge(const uint64_t* flag, uint64_t want) {
+  if ((ACQUIRE ? ld_acquire_sys(flag) : ld_relaxed_sys(flag)) >= want) return 0;
   const uint64_t start = global_timer_ns(), limit = bshmemi_state_d.wait_timeout_ns;
   uint32_t spins = 0;
   for (;;) {
-    const uint64_t v = ld_relaxed_sys(flag);
+    const uint64_t v = ACQUIRE ? ld_acquire_sys(flag) : ld_relaxed_sys(flag);
     if (v >= want) return 0;
     if ((++spins & 0xff) == 0 && global_timer_ns() - start > limit) {
       record_timeout(flag, want, v, BSHMEM_WHERE_BARRIER);
@@ -76,11 +78,18 @@ __device__ __forceinline__ int poll_ge_relaxed(const uint64_t* flag, uint64_t wa
 }
 
 // Sync over the team.  One release fence for the whole group, relaxed flag stores to every member,
-// relaxed polls of the members' flags, one acquire fence per polling thread: two fences on the critical
-// path however many members there are.  On a flat NVSwitch fabric one all-to-all round is used (every
+// acquire polls of the members' flags by the threads that own them, then a group barrier that hands
+// what those threads acquired to the rest of the group: one fence on the critical path however many
+// members there are.  On a flat NVSwitch fabric one all-to-all round is used (every
 // member one hop away); thread and warp scope on teams beyond 32 members fall back to radix-k
 // dissemination.  Returns 0, or 1 if a member did not arrive within the wait bound.
-template <int SCOPE>
+//
+// QUIET = false (sync): the release fence has GPU scope.  It orders this group's earlier stores to its
+// own memory (which peers read through this GPU's L2) before the flags, and does not wait for stores
+// still in flight to other GPUs, as the sync contract allows.  QUIET = true (barrier): system scope,
+// which also completes the group's earlier stores to peers; it costs a link round trip when such
+// stores are outstanding.
+template <int SCOPE, bool QUIET = false>
 __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) {
   const int size = t->size, me = t->my_pe;
   const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
@@ -90,14 +99,17 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
   const uint64_t epoch = epochs[slot] + 1;
   uint64_t* flags = (uint64_t*)t->sync_base + (size_t)slot * size;
   int err = 0;
-  if (rank == 0) fence_sys();  // release: the group's earlier stores (ordered before this by the group barrier)
+  if (rank == 0) {  // release: the group's earlier stores (ordered before this by the group barrier)
+    if (QUIET) fence_sys();
+    else asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  }
   group_sync<SCOPE>();
   const int k = SCOPE == SCOPE_BLOCK || SCOPE == SCOPE_WARPGROUP || size <= 32 ? size : bshmemi_state_d.barrier_dissem_kval;
   if (k >= size) {
     for (int i = rank; i < size; i += G)
       if (i != me) st_relaxed_sys(translate(flags + me, team_world_pe(t, i)), epoch);
     for (int i = rank; i < size; i += G)
-      if (i != me) err |= poll_ge_relaxed(flags + i, epoch);
+      if (i != me) err |= poll_ge<true>(flags + i, epoch);
   } else {
     // Radix-k dissemination: in round r talk to the PEs at distance j*k^r, j = 1..k-1.
     // Flag index r*(k-1)+(j-1) never exceeds `size` for k >= 2.
@@ -110,14 +122,13 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
       }
       for (int j = 1 + rank; j < k; j += G) {
         if ((long)j * dist >= size) continue;
-        err |= poll_ge_relaxed(flags + round * (k - 1) + (j - 1), epoch);
+        err |= poll_ge<false>(flags + round * (k - 1) + (j - 1), epoch);
       }
       // A round's arrivals must be ordered before the next round's announcements.
       fence_sys();
       group_sync<SCOPE>();
     }
   }
-  fence_sys();  // acquire: data published by the members before their flags
   group_sync<SCOPE>();
   if (rank == 0) epochs[slot] = epoch;
   return err;
@@ -125,7 +136,7 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
 // Barrier = completion of this group's earlier puts (quiet) + sync; the sync's release fence is that quiet.
 template <int SCOPE>
 __device__ __forceinline__ int team_barrier(const bshmemi_team_t* t, int slot = 0) {
-  return team_sync<SCOPE>(t, slot);
+  return team_sync<SCOPE, true>(t, slot);
 }
 
 // ------------------------------------------------------------------ element arithmetic
@@ -266,7 +277,17 @@ __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, 
   } else if (algo == RED_NVLS_ONESHOT) {
     const char* mc_src = (const char*)t->mc_base + ((uint64_t)(src + lo) - bshmemi_state_d.heap_base);
     const size_t nvec = (hi - lo) / N;
-    for (size_t v = rank; v < nvec; v += G) ((uint4*)(dst + lo))[v] = MultimemSum<T>::ld(mc_src + v * 16);
+    uint4* out = (uint4*)(dst + lo);
+    size_t v = rank;
+    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {  // four reductions in flight per thread
+      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
+      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
+      out[v] = r0;
+      out[v + G] = r1;
+      out[v + 2 * (size_t)G] = r2;
+      out[v + 3 * (size_t)G] = r3;
+    }
+    for (; v < nvec; v += G) out[v] = MultimemSum<T>::ld(mc_src + v * 16);
     err |= team_sync<SCOPE>(t, slot);
   } else {  // NVLS two-shot: reduce my chunk in the switch, multicast the result
     size_t a, b;

@@ -135,10 +135,13 @@ static int clamp_ctas(long want) {
   if (v > BSHMEM_SYNC_SLOTS - 2) v = BSHMEM_SYNC_SLOTS - 2;
   return (int)(v < 1 ? 1 : v);
 }
+// Every CTA runs its own team sync on its own flag slot, so extra CTAs cost no grid-wide step: the
+// count only has to cover the latency of the loads and stores in flight.
 static int ctas_for(size_t bytes, size_t threshold) {
   if (bytes < threshold) return 1;
-  if (bytes < (size_t)4 << 20) return clamp_ctas(8);
-  if (bytes < (size_t)64 << 20) return clamp_ctas(16);
+  if (bytes < (size_t)256 << 10) return clamp_ctas(4);
+  if (bytes < (size_t)1 << 20) return clamp_ctas(8);
+  if (bytes < (size_t)4 << 20) return clamp_ctas(16);
   return clamp_ctas(32);
 }
 
@@ -177,7 +180,7 @@ int coll_reduce_on_stream(int team, void* dst, const void* src, size_t n, int dt
   if (n == 0) return ST_SUCCESS;
   const size_t bytes = n * dtype_size(dtype);
   const int threads = (int)std::min<long>(1024, std::max<long>(32, options().REDUCE_NTHREADS));
-  f(ctas_for(bytes, (size_t)256 << 10), threads, stream, team, dst, src, n, algo);
+  f(ctas_for(bytes, (size_t)64 << 10), threads, stream, team, dst, src, n, algo);
   rt().n_coll++;
   return launch_status("reduce");
 }
@@ -191,7 +194,7 @@ int coll_reducescatter_on_stream(int team, void* dst, const void* src, size_t nr
   if (nreduce == 0) return ST_SUCCESS;
   const size_t bytes = nreduce * dtype_size(dtype) * team_get(team)->size;
   const int threads = (int)std::min<long>(1024, std::max<long>(32, options().REDUCESCATTER_NTHREADS));
-  f(ctas_for(bytes, (size_t)1 << 20), threads, stream, team, dst, src, nreduce, algo);
+  f(ctas_for(bytes, (size_t)64 << 10), threads, stream, team, dst, src, nreduce, algo);
   rt().n_coll++;
   return launch_status("reducescatter");
 }
@@ -203,7 +206,7 @@ int coll_fcollect_on_stream(int team, void* dst, const void* src, size_t block_b
   if (block_bytes == 0) return ST_SUCCESS;
   const size_t total = block_bytes * team_get(team)->size;
   const int threads = (int)std::min<long>(1024, std::max<long>(32, options().FCOLLECT_NTHREADS));
-  fcollect_kernel<<<ctas_for(total, (size_t)1 << 20), threads, 0, stream>>>(team, dst, src, block_bytes, algo);
+  fcollect_kernel<<<ctas_for(total, (size_t)64 << 10), threads, 0, stream>>>(team, dst, src, block_bytes, algo);
   rt().n_coll++;
   return launch_status("fcollect");
 }
@@ -214,7 +217,7 @@ int coll_alltoall_on_stream(int team, void* dst, const void* src, size_t block_b
   if (st) return st;
   if (block_bytes == 0) return ST_SUCCESS;
   const size_t total = block_bytes * team_get(team)->size;
-  alltoall_kernel<<<ctas_for(total, (size_t)1 << 20), 512, 0, stream>>>(team, dst, src, block_bytes);
+  alltoall_kernel<<<ctas_for(total, (size_t)64 << 10), 512, 0, stream>>>(team, dst, src, block_bytes);
   rt().n_coll++;
   return launch_status("alltoall");
 }
@@ -225,7 +228,7 @@ int coll_broadcast_on_stream(int team, void* dst, const void* src, size_t bytes,
   if (st) return st;
   if (root < 0 || root >= team_get(team)->size) return ST_INVALID_VALUE;
   if (bytes == 0) return ST_SUCCESS;
-  broadcast_kernel<<<ctas_for(bytes, (size_t)1 << 20), 512, 0, stream>>>(team, dst, src, bytes, root, algo);
+  broadcast_kernel<<<ctas_for(bytes, (size_t)64 << 10), 512, 0, stream>>>(team, dst, src, bytes, root, algo);
   rt().n_coll++;
   return launch_status("broadcast");
 }

@@ -24,6 +24,8 @@ def main():
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--graph", action="store_true", help="also time the collectives replayed from a CUDA graph")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--cold", action="store_true", help="also time single calls with the L2 flushed before each (8 MB and up)")
+    ap.add_argument("--algos", default="all", help="'all' or 'best': only the automatic choice of each collective")
     args = ap.parse_args()
     env = Env()
     nv = env.nv
@@ -38,12 +40,23 @@ def main():
     flush = lambda: flush_buf.zero_()
 
     def run(name, algo, dtype_name, size, fn, factor_name, per_pe_bytes):
-        iters = 20 if size <= (16 << 20) else 5
-        # small messages: back-to-back launches (latency); large: L2 flushed between launches
-        ms = env.time_ms(fn, iters=iters, warmup=3, flush=flush if size >= (8 << 20) else None)
+        # `us`: calls issued back to back, as the reference's perftest loops do.  The library's own calls are
+        # replayed from a CUDA graph so that no Python time sits between launches; NCCL goes through torch eagerly.
+        # `cold_us` (8 MB and up): one call at a time with the L2 flushed before it; includes the ranks' skew.
+        iters = 20 if size <= (16 << 20) else 8
+        if algo == "nccl":
+            ms, how = env.time_ms(lambda: fn(None), iters=iters, warmup=3), "eager"
+        else:
+            ms, how = env.time_graph_ms(fn, iters=iters), "graph"
+        extra = {}
+        if size >= (8 << 20) and args.cold:
+            extra["cold_us"] = round(env.time_ms(lambda: fn(None), iters=5, warmup=1, flush=flush) * 1e3, 2)
         bw = per_pe_bytes / (ms * 1e-3) / 1e9
         env.record(test=name, algo=algo, dtype=dtype_name, bytes_per_pe=size, us=round(ms * 1e3, 2), algbw_GBps=round(bw, 2),
-                   busbw_GBps=round(bw * busbw_factor(factor_name, n), 2), npes=n, nvls=nvls)
+                   busbw_GBps=round(bw * busbw_factor(factor_name, n), 2), npes=n, nvls=nvls, issue=how, **extra)
+
+    def pick(lst):
+        return ["auto"] if args.algos == "best" else lst + ["auto"]
 
     for dname in args.dtypes.split(","):
         dt = dts[dname]
@@ -52,36 +65,38 @@ def main():
             cnt = size // es
             s, d = src[:size].view(dt), dst[:size].view(dt)
             # allreduce: `size` bytes per PE
-            for algo in ["oneshot", "twoshot"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else []) + ["auto"]:
+            for algo in pick(["oneshot", "twoshot"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])):
                 if algo in ("oneshot", "nvls_oneshot") and size > (4 << 20):
                     continue
-                run("allreduce_on_stream", algo, dname, size, lambda: nv.reduce(0, d, s, "sum", algo=algo), "allreduce", size)
+                run("allreduce_on_stream", algo, dname, size, lambda st: nv.reduce(0, d, s, "sum", algo=algo, stream=st), "allreduce", size)
             if not args.no_nccl and n > 1:
                 t = torch.empty(cnt, dtype=dt, device=env.dev)
-                run("allreduce_nccl", "nccl", dname, size, lambda: dist.all_reduce(t), "allreduce", size)
+                run("allreduce_nccl", "nccl", dname, size, lambda st: dist.all_reduce(t), "allreduce", size)
             # reducescatter / fcollect / alltoall: `size` bytes is the full buffer, size/n per block
             if cnt % n == 0 and cnt >= n:
                 blk = cnt // n
-                for algo in ["pull"] + (["nvls"] if nvls else []):
-                    run("reducescatter_on_stream", algo, dname, size, lambda: nv.reducescatter(0, d[:blk], s, "sum", algo=algo), "reducescatter", size)
-                for algo in ["push"] + (["ll"] if size // n <= 2048 else []) + (["nvls"] if nvls else []):
-                    run("fcollect_on_stream", algo, dname, size, lambda: nv.fcollect(0, d, s[:blk], algo=algo), "fcollect", size)
-                run("alltoall_on_stream", "push", dname, size, lambda: nv.alltoall(0, d, s), "alltoall", size)
+                for algo in pick(["pull"] + (["nvls"] if nvls else [])):
+                    run("reducescatter_on_stream", algo, dname, size, lambda st: nv.reducescatter(0, d[:blk], s, "sum", algo=algo, stream=st), "reducescatter", size)
+                for algo in pick(["push"] + (["ll"] if size // n <= 2048 else []) + (["nvls"] if nvls else [])):
+                    run("fcollect_on_stream", algo, dname, size, lambda st: nv.fcollect(0, d, s[:blk], algo=algo, stream=st), "fcollect", size)
+                run("alltoall_on_stream", "push", dname, size, lambda st: nv.alltoall(0, d, s, stream=st), "alltoall", size)
                 if not args.no_nccl and n > 1:
                     full, part = torch.empty(cnt, dtype=dt, device=env.dev), torch.empty(blk, dtype=dt, device=env.dev)
-                    run("reducescatter_nccl", "nccl", dname, size, lambda: dist.reduce_scatter_tensor(part, full), "reducescatter", size)
-                    run("allgather_nccl", "nccl", dname, size, lambda: dist.all_gather_into_tensor(full, part), "fcollect", size)
+                    run("reducescatter_nccl", "nccl", dname, size, lambda st: dist.reduce_scatter_tensor(part, full), "reducescatter", size)
+                    run("allgather_nccl", "nccl", dname, size, lambda st: dist.all_gather_into_tensor(full, part), "fcollect", size)
                     full2 = torch.empty(cnt, dtype=dt, device=env.dev)
-                    run("alltoall_nccl", "nccl", dname, size, lambda: dist.all_to_all_single(full2, full), "alltoall", size)
-            for algo in ["push", "pull"] + (["nvls"] if nvls else []):
-                run("broadcast_on_stream", algo, dname, size, lambda: nv.broadcast(0, d, s, root=0, algo=algo), "broadcast", size)
+                    run("alltoall_nccl", "nccl", dname, size, lambda st: dist.all_to_all_single(full2, full), "alltoall", size)
+            for algo in pick(["push", "pull"] + (["nvls"] if nvls else [])):
+                run("broadcast_on_stream", algo, dname, size, lambda st: nv.broadcast(0, d, s, root=0, algo=algo, stream=st), "broadcast", size)
         break_after_first = False
     # barrier / sync latency: on-stream and device-initiated
     lib = env.devlib()
+    ms = env.time_graph_ms(lambda st: nv.barrier_all(stream=st), iters=50)
+    env.record(test="barrier_all_on_stream", us=round(ms * 1e3, 2), npes=n, issue="graph")
+    ms = env.time_graph_ms(lambda st: nv.sync_all(stream=st), iters=50)
+    env.record(test="sync_all_on_stream", us=round(ms * 1e3, 2), npes=n, issue="graph")
     ms = env.time_ms(lambda: nv.barrier_all(), iters=50, warmup=5)
-    env.record(test="barrier_all_on_stream", us=round(ms * 1e3, 2), npes=n)
-    ms = env.time_ms(lambda: nv.sync_all(), iters=50, warmup=5)
-    env.record(test="sync_all_on_stream", us=round(ms * 1e3, 2), npes=n)
+    env.record(test="barrier_all_on_stream", us=round(ms * 1e3, 2), npes=n, issue="eager")
     for scope, sname in ((0, "thread"), (1, "warp"), (2, "block")):
         for sync_only in (0, 1):
             iters = 200

@@ -75,6 +75,30 @@ class Env:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def time_graph_ms(self, fn, iters=20):
+        """Mean device time of one fn(stream) call in ms when `iters` calls are captured into a CUDA graph and
+        replayed back to back: no host time between launches (the way the reference's C loops issue them)."""
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            fn(stream)  # warm-up outside the capture (module loading, lazy state)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for _ in range(iters):
+                    fn(stream)
+        g.replay()
+        self.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        g.replay()
+        end.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(end) / iters], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del g
+        return float(t.item())
+
     def record(self, **row):
         self.rows.append(row)
         if self.rank == 0:
