@@ -126,8 +126,8 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
   const int EL = E / npes;
   Scratch* sc = (Scratch*)a.scratch;
   unsigned phase = 0;
-  int* s_bins = (int*)smem;                     // [E] histogram bins, later my segment starts
-  __shared__ int s_row[BSHMEM_MOE_MAX_TOPK], s_dest[BSHMEM_MOE_MAX_TOPK];
+  int* s_bins = (int*)smem;                     // [E] histogram bins, later my segment starts; [E] more for totals
+  __shared__ int s_row[THREADS], s_dest[THREADS];  // slots of one chunk of tokens: [token in chunk][choice]
 
   // ---- A: histogram
   for (int e = threadIdx.x; e < E; e += THREADS) s_bins[e] = 0;
@@ -153,21 +153,32 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
   if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
 
   // ---- C: where my rows start on each owner.  Rows of PE d's buffer: for le in [0, EL): for s in [0, npes): count[s][d*EL+le] rows.
+  // Per expert: rows from all PEs (s_tot) and rows from the PEs before me (s_bins); then a prefix over
+  // the experts of one owner, from shared memory.
   const int* cm = a.counts[rank];
+  int* s_tot = s_bins + E;
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += THREADS) {
-    const int d = e / EL, le = e % EL;
-    int start = 0;
-    for (int l2 = 0; l2 < le; ++l2)
-      for (int s = 0; s < npes; ++s) start += __ldcg(&cm[s * E + d * EL + l2]);
-    for (int s = 0; s < rank; ++s) start += __ldcg(&cm[s * E + e]);
-    s_bins[e] = start;
+    int tot = 0, pre = 0;
+    for (int s = 0; s < npes; ++s) {
+      const int c = __ldcg(&cm[s * E + e]);
+      tot += c;
+      if (s < rank) pre += c;
+    }
+    s_tot[e] = tot;
+    s_bins[e] = pre;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += THREADS) {
+    const int first = (e / EL) * EL;
+    int start = s_bins[e];
+    for (int l2 = first; l2 < e; ++l2) start += s_tot[l2];
+    s_bins[e] = start;  // only this thread reads or writes s_bins[e] in this loop
   }
   if (blockIdx.x == 0) {  // receiver-side description of my own buffer
     for (int le = threadIdx.x; le <= EL; le += THREADS) {
       int start = 0;
-      for (int l2 = 0; l2 < le; ++l2)
-        for (int s = 0; s < npes; ++s) start += __ldcg(&cm[s * E + rank * EL + l2]);
+      for (int l2 = 0; l2 < le; ++l2) start += s_tot[rank * EL + l2];
       a.expert_offsets[le] = start;
       if (le < EL && a.src_offsets) {
         int run = start;
@@ -178,66 +189,94 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
       }
     }
   }
-  __syncthreads();
 
-  // ---- D: push rows
+  // ---- D: push rows.  The slots of a whole chunk of this CTA's tokens are claimed first (one atomic per
+  // (token, choice) pair, all in flight together); after that each token moves from global memory through
+  // registers to its K destinations with no CTA-wide synchronisation, so that the loads of one token
+  // overlap the stores of the one before.
   const int row_bytes = a.payload == BSHMEM_MOE_FP8_E4M3 ? H : H * 2;
   const int nscale = H / BSHMEM_MOE_QUANT_BLOCK;
-  uint8_t* s_x = smem + ((E * 4 + 15) & ~15);          // bf16 row
-  uint8_t* s_q = s_x + H * 2;                          // fp8 row
-  float* s_scale = (float*)(s_q + H);                  // scales
-  const uint4* xg = (const uint4*)a.x;
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    for (int c = threadIdx.x; c < H / 8; c += THREADS) ((uint4*)s_x)[c] = xg[(size_t)t * (H / 8) + c];
-    if ((int)threadIdx.x < K) {
-      const int e = a.topk_idx[(size_t)t * K + threadIdx.x];
-      int row = -1, dest = 0;
-      if (e >= 0 && e < E) {
-        const int pos = atomicAdd(&sc->cursor[e], 1);
-        row = s_bins[e] + pos;
-        dest = e / EL;
-        if (row >= a.cap_rows) {
-          atomicOr(a.error_flag, BSHMEM_MOE_ERRBIT_OVERFLOW);
-          row = -1;
+  const int per_chunk = THREADS / K;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int base = 0; (long)blockIdx.x + (long)base * gridDim.x < T; base += per_chunk) {
+    __syncthreads();  // the previous chunk's slots are no longer read (and s_bins is final on the first pass)
+    {
+      const int i = threadIdx.x / K, k = threadIdx.x % K;
+      const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
+      if (i < per_chunk && t < T) {
+        const int e = a.topk_idx[(size_t)t * K + k];
+        int row = -1, dest = 0;
+        if (e >= 0 && e < E) {
+          const int pos = atomicAdd(&sc->cursor[e], 1);
+          row = s_bins[e] + pos;
+          dest = e / EL;
+          if (row >= a.cap_rows) {
+            atomicOr(a.error_flag, BSHMEM_MOE_ERRBIT_OVERFLOW);
+            row = -1;
+          }
+        }
+        s_row[i * K + k] = row;
+        s_dest[i * K + k] = dest;
+        a.slot_map[(size_t)t * K + k] = row;
+      }
+    }
+    __syncthreads();
+    for (int i = 0; i < per_chunk; ++i) {
+      const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
+      if (t >= T) break;
+      const int* rows = s_row + i * K;
+      const int* dests = s_dest + i * K;
+      if (a.payload == BSHMEM_MOE_FP8_E4M3) {
+        // One warp per 128-value block: 4 values per lane, absmax by shuffles, scale = amax / 448.
+        // Up to four blocks are loaded before the first one is stored.
+        const uint2* xrow = (const uint2*)a.x + (size_t)t * (H / 4);
+        constexpr int WARPS = THREADS / 32;
+        for (int g0 = warp; g0 < nscale; g0 += 4 * WARPS) {
+          uint2 raw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (g0 + u * WARPS < nscale) raw[u] = xrow[(g0 + u * WARPS) * 32 + lane];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int g = g0 + u * WARPS;
+            if (g >= nscale) break;
+            const float2 v01 = __bfloat1622float2(*(const __nv_bfloat162*)&raw[u].x);
+            const float2 v23 = __bfloat1622float2(*(const __nv_bfloat162*)&raw[u].y);
+            float amax = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float scale = fmaxf(amax, 1e-10f) / 448.0f;
+            const float inv = 1.0f / scale;
+            const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v01.x * inv, v01.y * inv), __NV_SATFINITE, __NV_E4M3);
+            const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v23.x * inv, v23.y * inv), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t q4 = (uint32_t)lo | ((uint32_t)hi << 16);
+            for (int j = 0; j < K; ++j) {
+              const int row = rows[j];
+              if (row < 0) continue;
+              ((uint32_t*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes))[g * 32 + lane] = q4;
+              if (lane == 0) a.recv_scale[dests[j]][(size_t)row * nscale + g] = scale;
+            }
+          }
+        }
+      } else {
+        const uint4* xrow = (const uint4*)a.x + (size_t)t * (H / 8);
+        const int nvec = H / 8;
+        for (int c0 = threadIdx.x; c0 < nvec; c0 += 4 * THREADS) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + u * THREADS < nvec) v[u] = xrow[c0 + u * THREADS];
+          for (int j = 0; j < K; ++j) {
+            const int row = rows[j];
+            if (row < 0) continue;
+            uint4* dst = (uint4*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (c0 + u * THREADS < nvec) dst[c0 + u * THREADS] = v[u];
+          }
         }
       }
-      s_row[threadIdx.x] = row;
-      s_dest[threadIdx.x] = dest;
-      a.slot_map[(size_t)t * K + threadIdx.x] = row;
     }
-    __syncthreads();
-    const uint8_t* payload = s_x;
-    if (a.payload == BSHMEM_MOE_FP8_E4M3) {
-      // one warp per 128-value block: 4 values per lane, absmax by shuffles, scale = amax / 448
-      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-      for (int g = warp; g < nscale; g += THREADS / 32) {
-        const uint2 raw = ((const uint2*)s_x)[g * 32 + lane];
-        const float2 v01 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
-        const float2 v23 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
-        float amax = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float scale = fmaxf(amax, 1e-10f) / 448.0f;
-        const float inv = 1.0f / scale;
-        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v01.x * inv, v01.y * inv), __NV_SATFINITE, __NV_E4M3);
-        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v23.x * inv, v23.y * inv), __NV_SATFINITE, __NV_E4M3);
-        ((uint32_t*)s_q)[g * 32 + lane] = (uint32_t)lo | ((uint32_t)hi << 16);
-        if (lane == 0) s_scale[g] = scale;
-      }
-      __syncthreads();
-      payload = s_q;
-    }
-    for (int j = 0; j < K; ++j) {
-      const int row = s_row[j];
-      if (row < 0) continue;
-      uint4* dst = (uint4*)((uint8_t*)a.recv_x[s_dest[j]] + (size_t)row * row_bytes);
-      for (int c = threadIdx.x; c < row_bytes / 16; c += THREADS) dst[c] = ((const uint4*)payload)[c];
-      if (a.payload == BSHMEM_MOE_FP8_E4M3) {
-        float* sd = a.recv_scale[s_dest[j]] + (size_t)row * nscale;
-        for (int c = threadIdx.x; c < nscale; c += THREADS) sd[c] = s_scale[c];
-      }
-    }
-    __syncthreads();
   }
 
   // ---- E: all my rows are out; meet every PE
@@ -245,57 +284,81 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
   if (blockIdx.x == 0) pe_barrier(a.flags, 1, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
 }
 
-__global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant__ CombineParams P) {
+// Weighted sum of up to KT expert rows into one output row.  Row pointers and weights sit in registers;
+// for every 16-byte column block the KT loads are issued before the first is consumed.
+template <int KT>
+__device__ __forceinline__ void combine_token(const uint8_t* const* src, const float* wt, int K, uint4* out_row, int nvec) {
+  const uint4* p[KT];
+  float w[KT];
+#pragma unroll
+  for (int j = 0; j < KT; ++j) {
+    const bool on = j < K && src[j] != nullptr;
+    p[j] = on ? (const uint4*)src[j] : nullptr;
+    w[j] = on ? wt[j] : 0.f;
+  }
+  for (int c = threadIdx.x; c < nvec; c += THREADS) {
+    uint4 v[KT];
+#pragma unroll
+    for (int j = 0; j < KT; ++j) v[j] = p[j] ? p[j][c] : make_uint4(0u, 0u, 0u, 0u);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
+      const __nv_bfloat162* h = (const __nv_bfloat162*)&v[j];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        acc[2 * q] += w[j] * f.x;
+        acc[2 * q + 1] += w[j] * f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = (__nv_bfloat162*)&o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) oh[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    out_row[c] = o;
+  }
+}
+
+template <int KT>
+__global__ void __launch_bounds__(THREADS, KT <= 8 ? 3 : 2) combine_kernel(const __grid_constant__ CombineParams P) {
   const bshmem_moe_combine_args_t& a = P.a;
   const int T = a.T, H = a.H, K = a.K, E = a.E, npes = a.npes, rank = a.rank;
   const int EL = E / npes;
   Scratch* sc = (Scratch*)a.scratch;
   unsigned phase = 0;
-  __shared__ const uint8_t* s_src[BSHMEM_MOE_MAX_TOPK];
-  __shared__ float s_w[BSHMEM_MOE_MAX_TOPK];
+  __shared__ const uint8_t* s_src[THREADS];  // one chunk of this CTA's tokens: [token in chunk][choice]
+  __shared__ float s_w[THREADS];
   if (blockIdx.x == 0) pe_barrier(a.flags, 2, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
   if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    if ((int)threadIdx.x < K) {
-      const int e = a.topk_idx[(size_t)t * K + threadIdx.x];
-      const int row = a.slot_map[(size_t)t * K + threadIdx.x];
-      const bool ok = e >= 0 && e < E && row >= 0;
-      s_src[threadIdx.x] = ok ? (const uint8_t*)a.y[e / EL] + (size_t)row * H * 2 : nullptr;
-      s_w[threadIdx.x] = ok ? a.topk_weight[(size_t)t * K + threadIdx.x] : 0.f;
-    }
+  const int per_chunk = THREADS / K;
+  for (int base = 0; (long)blockIdx.x + (long)base * gridDim.x < T; base += per_chunk) {
     __syncthreads();
-    for (int c = threadIdx.x; c < H / 8; c += THREADS) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      uint4 v[BSHMEM_MOE_MAX_TOPK];
-#pragma unroll
-      for (int j = 0; j < BSHMEM_MOE_MAX_TOPK; ++j)  // all K loads of this 16-byte column block are in flight together
-        if (j < K && s_src[j]) v[j] = ((const uint4*)s_src[j])[c];
-#pragma unroll
-      for (int j = 0; j < BSHMEM_MOE_MAX_TOPK; ++j) {
-        if (j < K && s_src[j]) {
-          const float w = s_w[j];
-          const __nv_bfloat162* h = (const __nv_bfloat162*)&v[j];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = __bfloat1622float2(h[q]);
-            acc[2 * q] += w * f.x;
-            acc[2 * q + 1] += w * f.y;
-          }
-        }
+    {
+      // Sources and weights of a whole chunk of tokens are looked up at once, so that the token loop
+      // below runs without CTA-wide synchronisation.
+      const int i = threadIdx.x / K, k = threadIdx.x % K;
+      const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
+      if (i < per_chunk && t < T) {
+        const int e = a.topk_idx[(size_t)t * K + k];
+        const int row = a.slot_map[(size_t)t * K + k];
+        const bool ok = e >= 0 && e < E && row >= 0;
+        s_src[i * K + k] = ok ? (const uint8_t*)a.y[e / EL] + (size_t)row * H * 2 : nullptr;
+        s_w[i * K + k] = ok ? a.topk_weight[(size_t)t * K + k] : 0.f;
       }
-      uint4 o;
-      __nv_bfloat162* oh = (__nv_bfloat162*)&o;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) oh[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-      ((uint4*)a.out)[(size_t)t * (H / 8) + c] = o;
     }
     __syncthreads();
+    for (int i = 0; i < per_chunk; ++i) {
+      const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
+      if (t >= T) break;
+      uint4* out_row = (uint4*)a.out + (size_t)t * (H / 8);
+      combine_token<KT>(s_src + i * K, s_w + i * K, K, out_row, H / 8);
+    }
   }
   if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
   if (blockIdx.x == 0) pe_barrier(a.flags, 3, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
 }
 
-static size_t dispatch_smem(int E, int H) { return ((size_t)E * 4 + 15 & ~(size_t)15) + (size_t)H * 2 + H + (H / BSHMEM_MOE_QUANT_BLOCK) * 4 + 16; }
+static size_t dispatch_smem(int E, int) { return (size_t)E * 8 + 16; }  // two int arrays of E entries; rows go through registers
 
 // Cooperative grid: as many CTAs as are co-resident, at most one per token.
 template <class Kernel>
@@ -360,11 +423,13 @@ extern "C" int bshmem_moe_combine(const bshmem_moe_combine_args_t* a, cudaStream
   P.a = *a;
   P.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
   int grid = 0;
-  st = coop_grid(combine_kernel, 0, a->T, a->max_ctas, &grid);
+  // Two builds of the kernel: up to 8 choices per token (fewer registers, three CTAs per SM) and up to 16.
+  const void* kernel = a->K <= 8 ? (const void*)combine_kernel<8> : (const void*)combine_kernel<BSHMEM_MOE_MAX_TOPK>;
+  st = a->K <= 8 ? coop_grid(combine_kernel<8>, 0, a->T, a->max_ctas, &grid) : coop_grid(combine_kernel<BSHMEM_MOE_MAX_TOPK>, 0, a->T, a->max_ctas, &grid);
   if (st) return st;
   if (cudaMemsetAsync(a->scratch, 0, 256, stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;  // the grid-barrier counter
   void* params[] = {(void*)&P};
-  cudaError_t e = cudaLaunchCooperativeKernel((const void*)combine_kernel, dim3(grid), dim3(THREADS), params, 0, stream);
+  cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(THREADS), params, 0, stream);
   if (e != cudaSuccess) {
     fprintf(stderr, "bshmem_moe_combine: launch failed: %s\n", cudaGetErrorString(e));
     return BSHMEM_MOE_ERR_DRIVER;
