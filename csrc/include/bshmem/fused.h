@@ -48,6 +48,9 @@ typedef struct {
   void* ag_peer[BSHMEM_FUSED_MAX_PES];
   uint64_t* ag_flags_local;                   /* [npes][M/npes/128] arrival counters */
   uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
+  /* AR, optional: NVLink-multicast alias of `out` (nvshmemx_mc_ptr).  When set, a reduced tile leaves this GPU
+   * once and the switch delivers it to every PE; when null it is stored to each PE's out in turn. */
+  void* out_mc;
 } bshmem_fused_args_t;
 
 /* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */

@@ -231,13 +231,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
           const size_t rows_per_pe = (size_t)p.M / p.npes;
           const size_t grow = (size_t)ti.m_local * BM + row;
           const size_t col0 = (size_t)ti.n_tile * BN + (size_t)c * EPI_COLS;
-          for (int s = 0; s < p.npes; ++s) {
-            if (s == p.rank) continue;
-            const uint4* src = (const uint4*)(p.recv_local + ((size_t)s * rows_per_pe + grow) * p.N + col0);
+          // Partials of two senders are loaded (16 x 16 bytes per thread in flight) before either is added:
+          // the epilogue of an own tile reads (npes - 1) x 64 KB and must not outlast the next tile's main loop.
+          auto add8 = [&](const uint4* v) {
 #pragma unroll
             for (int j = 0; j < EPI_COLS / 8; ++j) {
-              const uint4 v = src[j];
-              const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+              const __nv_bfloat162* h = (const __nv_bfloat162*)&v[j];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float2 x = __bfloat1622float2(h[e]);
@@ -245,6 +244,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
                 f[j * 8 + 2 * e + 1] += x.y;
               }
             }
+          };
+          for (int q = 0; q < p.npes - 1; q += 2) {
+            const bool two = q + 1 < p.npes - 1;
+            const int s0 = (p.rank + 1 + q) % p.npes, s1 = (p.rank + 2 + q) % p.npes;
+            const uint4* a0 = (const uint4*)(p.recv_local + ((size_t)s0 * rows_per_pe + grow) * p.N + col0);
+            const uint4* a1 = (const uint4*)(p.recv_local + ((size_t)s1 * rows_per_pe + grow) * p.N + col0);
+            uint4 v0[EPI_COLS / 8], v1[EPI_COLS / 8];
+#pragma unroll
+            for (int j = 0; j < EPI_COLS / 8; ++j) v0[j] = a0[j];
+            if (two) {
+#pragma unroll
+              for (int j = 0; j < EPI_COLS / 8; ++j) v1[j] = a1[j];
+            }
+            add8(v0);
+            if (two) add8(v1);
           }
         }
         // Staging buffer (chunk_counter & 1) must have been drained by the TMA store issued two chunks ago.
@@ -262,7 +276,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         }
         fence_proxy_async_smem();
         named_bar_sync(1, EPI_THREADS);
-        if (issuer) {
+        if (own && p.mode == BSHMEM_FUSED_AR && p.npes > 1 && p.out_mc) {
+          // Reduced tile of an all-reduce: every thread takes 16-byte pieces of the staged chunk, a warp
+          // covering four whole 128-byte rows per store, and writes them through the multicast alias:
+          // one copy leaves this GPU and the switch delivers it to all PEs (this one included).
+          char* base = p.out_mc + ((size_t)ti.m_tile * BM * p.N + (size_t)ti.n_tile * BN + (size_t)c * EPI_COLS) * 2;
+#pragma unroll
+          for (int i = 0; i < EPI_COLS * 2 * BM / 16 / EPI_THREADS; ++i) {
+            const int idx = i * EPI_THREADS + (int)threadIdx.x - EPI_WARP0 * 32;
+            const int r = idx >> 3, j = idx & 7;
+            const uint4 v = *(const uint4*)(buf + r * 128 + ((j ^ (r & 7)) << 4));
+            multimem_st_v4(base + (size_t)r * p.N * 2 + j * 16, v);
+          }
+        } else if (issuer) {
           const int x = ti.n_tile * BN + c * EPI_COLS;
           if (!own) {
             tma_store_2d(&p.tmRecv[ti.peer], buf, x, ti.m_local * BM);
@@ -344,6 +370,7 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   if (st) return st;
   const bool reduce_mode = (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1;
   if (mode == BSHMEM_FUSED_AR && npes > 1) {
+    p.out_mc = (char*)a->out_mc;
     for (int q = 0; q < npes && !st; ++q) {
       if (!a->out_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
       st = make_map(&p.tmOut[q], a->out_peer[q], a->M, a->N, BM);

@@ -13,6 +13,7 @@
 
 #include "../../include/bshmem/fused.h"
 #include "../../include/bshmem/tcgen05.cuh"
+#include "../../include/bshmem/nvls.cuh"
 
 namespace bshmem {
 using namespace sm100;
@@ -38,6 +39,7 @@ struct alignas(64) FusedParams {
   char* ag_dst[BSHMEM_FUSED_MAX_PES];        // the same shard inside each PE's gathered buffer
   uint64_t* ag_flags_local;                  // [npes][m-tiles per shard]
   uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
+  char* out_mc;                              // AR: multicast alias of the output (null: per-PE stores)
   int* error_flag;
   uint64_t epoch, wait_limit_ns, ag_unit_bytes;
   uint32_t ag_piece_bytes;  // size of one bulk copy of the sender (16-byte multiple, at most COMM_PIECE)

@@ -227,34 +227,58 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
       const int* rows = s_row + i * K;
       const int* dests = s_dest + i * K;
       if (a.payload == BSHMEM_MOE_FP8_E4M3) {
-        // One warp per 128-value block: 4 values per lane, absmax by shuffles, scale = amax / 448.
-        // Up to four blocks are loaded before the first one is stored.
-        const uint2* xrow = (const uint2*)a.x + (size_t)t * (H / 4);
+        // Eight lanes per 128-value block, 16 values per lane: a warp quantises four blocks at a time and
+        // stores 16 bytes per lane (512 contiguous bytes per warp and destination).  absmax over the eight
+        // lanes by shuffles, scale = amax / 448.  Two rounds of loads are in flight before the first store.
+        const uint4* xrow = (const uint4*)a.x + (size_t)t * (H / 8);
         constexpr int WARPS = THREADS / 32;
-        for (int g0 = warp; g0 < nscale; g0 += 4 * WARPS) {
-          uint2 raw[4];
+        const int sub = lane >> 3, part = lane & 7;  // block within the warp's four, 16-value piece within the block
+        const int ngroups = (nscale + 3) / 4;
+        for (int q0 = warp; q0 < ngroups; q0 += 2 * WARPS) {
+          uint4 raw[2][2];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (g0 + u * WARPS < nscale) raw[u] = xrow[(g0 + u * WARPS) * 32 + lane];
+          for (int u = 0; u < 2; ++u) {
+            const int g = (q0 + u * WARPS) * 4 + sub;
+            if (q0 + u * WARPS < ngroups && g < nscale) {
+              raw[u][0] = xrow[g * 16 + part * 2];
+              raw[u][1] = xrow[g * 16 + part * 2 + 1];
+            } else {
+              raw[u][0] = raw[u][1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int g = g0 + u * WARPS;
-            if (g >= nscale) break;
-            const float2 v01 = __bfloat1622float2(*(const __nv_bfloat162*)&raw[u].x);
-            const float2 v23 = __bfloat1622float2(*(const __nv_bfloat162*)&raw[u].y);
-            float amax = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
+          for (int u = 0; u < 2; ++u) {
+            if (q0 + u * WARPS >= ngroups) break;  // uniform over the warp
+            const int g = (q0 + u * WARPS) * 4 + sub;
+            float f[16];
+            const __nv_bfloat162* h = (const __nv_bfloat162*)raw[u];
+            float amax = 0.f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            for (int e = 0; e < 8; ++e) {
+              const float2 v = __bfloat1622float2(h[e]);
+              f[2 * e] = v.x;
+              f[2 * e + 1] = v.y;
+              amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+            }
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float scale = fmaxf(amax, 1e-10f) / 448.0f;
             const float inv = 1.0f / scale;
-            const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v01.x * inv, v01.y * inv), __NV_SATFINITE, __NV_E4M3);
-            const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v23.x * inv, v23.y * inv), __NV_SATFINITE, __NV_E4M3);
-            const uint32_t q4 = (uint32_t)lo | ((uint32_t)hi << 16);
-            for (int j = 0; j < K; ++j) {
-              const int row = rows[j];
-              if (row < 0) continue;
-              ((uint32_t*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes))[g * 32 + lane] = q4;
-              if (lane == 0) a.recv_scale[dests[j]][(size_t)row * nscale + g] = scale;
+            uint4 q16;
+            uint32_t* qw = (uint32_t*)&q16;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * e] * inv, f[4 * e + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * e + 2] * inv, f[4 * e + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              qw[e] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
+            if (g < nscale) {
+              for (int j = 0; j < K; ++j) {
+                const int row = rows[j];
+                if (row < 0) continue;
+                ((uint4*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes))[g * 8 + part] = q16;
+                if (part == 0) a.recv_scale[dests[j]][(size_t)row * nscale + g] = scale;
+              }
             }
           }
         }

@@ -32,7 +32,7 @@ class _Args(C.Structure):
     _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("out", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("rank", C.c_int), ("npes", C.c_int),
                 ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
                 ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
-                ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES)]
+                ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p)]
 
 
 _ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
@@ -110,7 +110,7 @@ class GemmReduceScatter:
     The output tensor is owned by the object and overwritten by the next call.
     """
 
-    def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0):
+    def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0, use_multicast: bool = True):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
@@ -137,6 +137,10 @@ class GemmReduceScatter:
         if self.npes > 1:
             for q in range(self.npes):
                 self._peer[q] = (core.peer_ptr(self.recv, q), core.peer_ptr(self.flags, q), core.peer_ptr(self.out, q) if mode == "ar" else 0)
+            # All-reduce: the reduced tiles go out through the NVLink-multicast alias of `out` where there is one.
+            self._out_mc = 0
+            if mode == "ar" and use_multicast:
+                self._out_mc = int(H.load().nvshmemx_mc_ptr(0, C.c_void_p(self.out.data_ptr())) or 0)
             core.barrier_all()
             torch.cuda.synchronize()
 
@@ -158,7 +162,11 @@ class GemmReduceScatter:
                 a.recv_peer[q] = self._peer[q][0] + half
                 a.flags_peer[q] = self._peer[q][1]
                 a.out_peer[q] = self._peer[q][2]
+            a.out_mc = self._out_mc
         _launch(a, torch.cuda.current_stream().cuda_stream)
+        if self.mode == "ar" and self.npes > 1:
+            # Tiles written by the other PEs are complete once everyone's kernel has ended.
+            self.core.barrier_all(stream=torch.cuda.current_stream())
         return self.out
 
     __call__ = forward
