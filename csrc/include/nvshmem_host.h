@@ -264,6 +264,32 @@ int nvshmemx_collective_launch_query_gridsize(const void* func, dim3 block_dims,
  * every later API call do this on their own; call it after loading such a library at run time when
  * its kernels are launched before any other call into this library. */
 void nvshmemx_b200_module_sync(void);
+
+#if defined(__cplusplus) && !defined(BSHMEM_NO_INLINE_LAUNCH)
+/* A kernel's host-side handle belongs to the CUDA runtime instance of the program that defines it.  A program
+ * that links the CUDA runtime statically (nvcc's default) has its own instance, so the occupancy query and the
+ * cooperative launch are compiled into the caller; the library is only asked to refresh the device state. */
+static inline int bshmemx_inline_collective_launch_query_gridsize(const void* func, dim3 block, void** args, size_t smem, int* gridsize) {
+  (void)args;
+  if (!gridsize) return NVSHMEMX_ERROR_INVALID_VALUE;
+  int per_sm = 0, dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return NVSHMEMX_ERROR_INTERNAL;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, func, (int)(block.x * block.y * block.z), smem) != cudaSuccess) return NVSHMEMX_ERROR_INTERNAL;
+  *gridsize = per_sm * sms;
+  return NVSHMEMX_SUCCESS;
+}
+static inline int bshmemx_inline_collective_launch(const void* func, dim3 grid, dim3 block, void** args, size_t smem, cudaStream_t stream) {
+  if (nvshmemx_init_status() < NVSHMEM_STATUS_IS_INITIALIZED) return NVSHMEMX_ERROR_INVALID_VALUE;
+  nvshmemx_b200_module_sync();
+  int max_grid = 0;
+  if (bshmemx_inline_collective_launch_query_gridsize(func, block, args, smem, &max_grid) != NVSHMEMX_SUCCESS) return NVSHMEMX_ERROR_COLLECTIVE_LAUNCH_FAILED;
+  if (grid.x == 0) grid = dim3((unsigned)max_grid, 1, 1);
+  if ((int)(grid.x * grid.y * grid.z) > max_grid) return NVSHMEMX_ERROR_COLLECTIVE_LAUNCH_FAILED;  /* the CTAs could not all be resident */
+  return cudaLaunchCooperativeKernel(func, grid, block, args, smem, stream) == cudaSuccess ? NVSHMEMX_SUCCESS : NVSHMEMX_ERROR_COLLECTIVE_LAUNCH_FAILED;
+}
+#define nvshmemx_collective_launch bshmemx_inline_collective_launch
+#define nvshmemx_collective_launch_query_gridsize bshmemx_inline_collective_launch_query_gridsize
+#endif
 /* Error bits recorded by device code since the last clear (BSHMEM_ERR_*): bounded waits
  * report a time-out here instead of hanging the GPU. */
 uint32_t nvshmemx_b200_error_bits(void);

@@ -67,6 +67,14 @@ class SymmetricHeap {
     return mc_base_ + ((const char*)p - base());
   }
   HeapAllocator& allocator() { return alloc_; }
+  // Maps a caller-owned device allocation (made with cuMemCreate, shareable as a POSIX file descriptor,
+  // a multiple of granule() bytes) into the window of every PE, at the same offset everywhere, and returns
+  // this PE's symmetric address of it.  Collective; every PE passes a buffer of the same size.  The range is
+  // not handed to the allocator.  (reference: nvshmemx_buffer_register_symmetric, src/host/mem/mem_heap.cpp)
+  virtual int attach_external(void* user_ptr, size_t bytes, void** mapped) { (void)user_ptr; (void)bytes; (void)mapped; return HEAP_ERR_ARGS; }
+  // Unmaps a range made by attach_external from every window.  Collective.  The offsets are not reused.
+  virtual int detach_external(void* mapped, size_t bytes) { (void)mapped; (void)bytes; return HEAP_ERR_ARGS; }
+  size_t granule() const { return granularity_; }
   // Compares the allocator history digest across PEs (error checks).
   int check_symmetry();
   int chunks() const { return nchunks_; }

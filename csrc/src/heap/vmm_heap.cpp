@@ -35,6 +35,7 @@ struct Chunk {
   CUmemGenericAllocationHandle own = 0;
   CUmemGenericAllocationHandle mc = 0;
   bool mc_bound = false, mc_mapped = false;
+  bool external = false;  // caller-owned memory: mapped here, never created here
 };
 
 class VmmHeap final : public SymmetricHeap {
@@ -129,13 +130,71 @@ class VmmHeap final : public SymmetricHeap {
   }
 
   int grow(size_t bytes) override {
-    const int tmo = (int)options().BOOTSTRAP_TIMEOUT_MS;
     Chunk c{backed_, bytes};
     CUresult r = d_->cuMemCreate_(&c.own, bytes, &prop_, 0);
     if (r != CUDA_SUCCESS) {
       ERROR_PRINT("VMM heap: cuMemCreate(%zu) failed: %s", bytes, cu_error_string(r).c_str());
       return HEAP_ERR_OOM;
     }
+    return map_chunk(c, true);
+  }
+
+  int attach_external(void* user_ptr, size_t bytes, void** mapped) override {
+    // Every PE must come with a usable buffer before anything is mapped anywhere.
+    Chunk c{backed_, bytes};
+    c.external = true;
+    int32_t ok = 1;
+    if (!user_ptr || bytes == 0 || bytes % granularity_ || backed_ + bytes > stride_) ok = 0;
+    if (ok) {
+      CUdeviceptr range_base = 0;
+      size_t range_size = 0;
+      if (d_->cuMemGetAddressRange_(&range_base, &range_size, (CUdeviceptr)user_ptr) != CUDA_SUCCESS || range_base != (CUdeviceptr)user_ptr || range_size < bytes) ok = 0;
+    }
+    if (ok && d_->cuMemRetainAllocationHandle_(&c.own, user_ptr) != CUDA_SUCCESS) ok = 0;
+    if (ok) {
+      CUmemAllocationProp up{};
+      if (d_->cuMemGetAllocationPropertiesFromHandle_(&up, c.own) != CUDA_SUCCESS || up.location.type != CU_MEM_LOCATION_TYPE_DEVICE || up.location.id != ordinal_ ||
+          !(up.requestedHandleTypes & CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR)) {
+        d_->cuMemRelease_(c.own);
+        c.own = 0;
+        ok = 0;
+      }
+    }
+    std::vector<int32_t> votes(npes_);
+    if (boot_->allgather(&ok, votes.data(), sizeof(int32_t), boot_) != 0) return HEAP_ERR_EXCHANGE;
+    if (!std::all_of(votes.begin(), votes.end(), [](int32_t v) { return v == 1; })) {
+      if (!ok) ERROR_PRINT("VMM heap: the buffer to register must be one cuMemCreate allocation on this device, shareable as a POSIX file descriptor, whose size is a multiple of %zu bytes", granularity_);
+      if (c.own) d_->cuMemRelease_(c.own);
+      return HEAP_ERR_ARGS;
+    }
+    int st = map_chunk(c, false);
+    if (st == HEAP_OK) *mapped = base() + c.offset;
+    return st;
+  }
+
+  int detach_external(void* mapped, size_t bytes) override {
+    cudaDeviceSynchronize();
+    for (auto& c : chunks_) {
+      if (!c.external || !c.own || base() + c.offset != (char*)mapped || c.bytes != bytes) continue;
+      if (nvls_) {
+        // The multicast window covers the whole heap or nothing: with a hole in it, it goes.
+        if (boot_->barrier(boot_) != 0) return HEAP_ERR_EXCHANGE;
+        disable_nvls();
+      }
+      if (boot_->barrier(boot_) != 0) return HEAP_ERR_EXCHANGE;  // nobody touches the range any more
+      for (int pe = 0; pe < npes_; ++pe) d_->cuMemUnmap_((CUdeviceptr)(peer_base(pe) + c.offset), c.bytes);
+      d_->cuMemRelease_(c.own);
+      c.own = 0;
+      return boot_->barrier(boot_) == 0 ? HEAP_OK : HEAP_ERR_EXCHANGE;
+    }
+    return HEAP_ERR_ARGS;
+  }
+
+  // Maps chunk `c` (its handle in c.own) at offset backed_ of every PE's window and appends it to the heap.
+  int map_chunk(Chunk c, bool to_allocator) {
+    const int tmo = (int)options().BOOTSTRAP_TIMEOUT_MS;
+    const size_t bytes = c.bytes;
+    CUresult r;
     CUmemAccessDesc acc{};
     acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     acc.location.id = ordinal_;
@@ -174,7 +233,7 @@ class VmmHeap final : public SymmetricHeap {
       if (st != HEAP_OK) return st;
     }
     chunks_.push_back(c);
-    alloc_.add_chunk(backed_, bytes);
+    if (to_allocator) alloc_.add_chunk(backed_, bytes);
     backed_ += bytes;
     ++nchunks_;
     INFO(SUB_MEM, "VMM heap grew to %zu bytes (%d chunks)", backed_, nchunks_);
@@ -267,6 +326,7 @@ class VmmHeap final : public SymmetricHeap {
     for (auto& c : chunks_) drop_multicast(&c);
     if (boot_ && npes_ > 1) boot_->barrier(boot_);
     for (auto& c : chunks_) {
+      if (!c.own) continue;  // an external range that was detached
       for (int pe = 0; pe < npes_; ++pe) d_->cuMemUnmap_((CUdeviceptr)(peer_base(pe) + c.offset), c.bytes);
       d_->cuMemRelease_(c.own);
     }

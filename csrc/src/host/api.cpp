@@ -13,6 +13,7 @@
 #include <type_traits>
 #include <vector>
 
+#define BSHMEM_NO_INLINE_LAUNCH  // this file defines the exported versions
 #include "../../include/nvshmem_host.h"
 #include "../coll/coll_host.h"
 #include "../state/runtime.h"
@@ -326,11 +327,46 @@ void* nvshmemx_mc_ptr(nvshmem_team_t team, const void* ptr) {
 int nvshmemx_buffer_register(void*, size_t) { return NVSHMEMX_SUCCESS; }
 int nvshmemx_buffer_unregister(void*) { return NVSHMEMX_SUCCESS; }
 void nvshmemx_buffer_unregister_all(void) {}
-void* nvshmemx_buffer_register_symmetric(void*, size_t, int) {
-  ERROR_PRINT("nvshmemx_buffer_register_symmetric: mapping caller-owned allocations into the heap is not implemented; allocate with nvshmem_malloc");
-  return nullptr;
+// Maps a caller-owned VMM allocation into the symmetric heap (collective; same size on every PE) and returns
+// its symmetric address; the caller's own mapping stays valid and aliases it.
+static void republish_heap(Runtime& r) {
+  r.dstate.heap_size = r.heap->backed();
+  r.dstate.mc_base = (uint64_t)r.heap->mc_base();
+  r.dstate.nvls_world = r.heap->mc_base() != nullptr;
+  teams_refresh_nvls(r);
+  push_device_state();
 }
-int nvshmemx_buffer_unregister_symmetric(void*, size_t) { return NVSHMEMX_ERROR_NOT_SUPPORTED; }
+void* nvshmemx_buffer_register_symmetric(void* buf_ptr, size_t size, int flags) {
+  (void)flags;
+  if (!ready("nvshmemx_buffer_register_symmetric")) return nullptr;
+  Runtime& r = rt();
+  void* mapped = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(r.mu);
+    if (!r.have_gpu) {
+      ERROR_PRINT("nvshmemx_buffer_register_symmetric needs the GPU heap back end");
+      return nullptr;
+    }
+    int st = r.heap->attach_external(buf_ptr, size, &mapped);
+    if (st != HEAP_OK) {
+      ERROR_PRINT("nvshmemx_buffer_register_symmetric(%p, %zu) failed (status %d; sizes are multiples of %zu bytes)", buf_ptr, size, st, r.heap->granule());
+      return nullptr;
+    }
+    republish_heap(r);
+  }
+  host_barrier_all_blocking();
+  return mapped;
+}
+int nvshmemx_buffer_unregister_symmetric(void* mmap_ptr, size_t size) {
+  if (!ready("nvshmemx_buffer_unregister_symmetric")) return NVSHMEMX_ERROR_INVALID_VALUE;
+  Runtime& r = rt();
+  host_barrier_all_blocking();
+  std::lock_guard<std::mutex> lk(r.mu);
+  int st = r.heap->detach_external(mmap_ptr, size);
+  if (st != HEAP_OK) return NVSHMEMX_ERROR_INVALID_VALUE;
+  republish_heap(r);
+  return NVSHMEMX_SUCCESS;
+}
 
 // ------------------------------------------------------------------ teams
 int nvshmem_team_my_pe(nvshmem_team_t team) {

@@ -219,8 +219,17 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   }
   r.have_gpu = use_vmm;
   if (use_vmm) {
-    if (device_hint >= 0) r.device = device_hint;
-    else if (cudaGetDevice(&r.device) != cudaSuccess) r.device = 0;
+    if (device_hint >= 0) {
+      r.device = device_hint;
+    } else {
+      // No device named: a process that already holds a CUDA context keeps its device; one that has not touched
+      // CUDA yet gets the device of its rank on the node, which is what programs that call cudaSetDevice(mype_node)
+      // after nvshmem_init() expect (reference: examples/ring-bcast.cu, init-then-select pattern).
+      CUcontext ctx = nullptr;
+      const bool has_ctx = cu()->cuCtxGetCurrent_(&ctx) == CUDA_SUCCESS && ctx != nullptr;
+      if (!has_ctx) r.device = r.mype_node % ndev;
+      else if (cudaGetDevice(&r.device) != cudaSuccess) r.device = 0;
+    }
     if (cudaSetDevice(r.device) != cudaSuccess || cudaFree(nullptr) != cudaSuccess) {
       ERROR_PRINT("cannot select CUDA device %d", r.device);
       return ST_GPU_NOT_SELECTED;

@@ -124,6 +124,7 @@ void watchdog_stop(Runtime& r);
 // ---- teams (team.cpp)
 int teams_init(Runtime& r);
 void teams_finalize(Runtime& r);
+void teams_refresh_nvls(Runtime& r);  // after the heap's multicast window changed
 Team* team_get(int handle);
 int team_translate_pe(int src_team, int src_pe, int dst_team);
 int team_split_strided(int parent, int start, int stride, int size, uint64_t uniqueid, int num_contexts, int* new_team);

@@ -93,6 +93,21 @@ static int publish_team(Runtime& r, Team* t) {
   return local_write(r.team_pool_dev + t->idx, &d, sizeof(d)) ? ST_INTERNAL : ST_SUCCESS;
 }
 
+// After the heap's multicast window changed (it went away, or moved): rewrites the NVLS fields of every team.
+void teams_refresh_nvls(Runtime& r) {
+  const uint64_t mc = (uint64_t)r.heap->mc_base();
+  for (auto& up : r.teams) {
+    Team* t = up.get();
+    if (!t || t->idx < 0) continue;
+    if (!mc) t->nvls = false;
+    bshmemi_team_t& d = r.team_pool_host[t->idx];
+    if (d.has_nvls == (t->nvls ? 1 : 0) && d.mc_base == (t->nvls ? mc : 0)) continue;
+    d.has_nvls = t->nvls;
+    d.mc_base = t->nvls ? mc : 0;
+    local_write(r.team_pool_dev + t->idx, &d, sizeof(d));
+  }
+}
+
 static Team* install_team(Runtime& r, int idx, int start, int stride, int size, const std::vector<int>* members, int parent) {
   auto t = std::make_unique<Team>();
   t->idx = idx;

@@ -45,7 +45,7 @@ def _headers_mtime() -> float:
 
 
 def _compile(src: Path, extra: list[str], verbose: bool, hdr_mtime: float) -> Path:
-    rel = src.relative_to(CSRC)
+    rel = src.relative_to(CSRC) if CSRC in src.parents else src.relative_to(ROOT)
     obj = OBJ / (str(rel).replace("/", "__") + ".o")
     obj.parent.mkdir(parents=True, exist_ok=True)
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
@@ -98,8 +98,13 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
         "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
     }
     built: dict[str, Path] = {}
+    if only in (None, "examples") and (ROOT / "examples").is_dir():
+        # One program per source file, linked against the host library (run them with `python -m nvshmem_b200.launch`).
+        ex_libs = ["-L", str(LIB), "-lbshmem_host", "-lcuda", "-Xlinker", "-rpath=$ORIGIN/../../nvshmem_b200/lib"]
+        for src in sorted((ROOT / "examples").glob("*.cu")) + sorted((ROOT / "examples").glob("*.cpp")):
+            groups["example:" + src.stem] = ([src], ROOT / "examples" / "bin" / src.stem, False, ex_libs)
     for name, (srcs, out, shared, libs) in groups.items():
-        if only and name != only:
+        if only and name != only and not (only == "examples" and name.startswith("example:")):
             continue
         if not srcs:
             continue
