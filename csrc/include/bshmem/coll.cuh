@@ -22,7 +22,7 @@
 namespace bshmem {
 
 enum ReduceOp { OP_AND = 0, OP_OR = 1, OP_XOR = 2, OP_MIN = 3, OP_MAX = 4, OP_SUM = 5, OP_PROD = 6 };
-enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4 };
+enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4, RED_LL = 5 };
 enum FcollectAlgo { FC_AUTO = 0, FC_PUSH = 1, FC_LL = 2, FC_NVLS = 3 };
 enum RsAlgo { RS_AUTO = 0, RS_PULL = 1, RS_NVLS = 2 };
 enum BcastAlgo { BC_AUTO = 0, BC_PUSH = 1, BC_LL = 2, BC_NVLS = 3, BC_PULL = 4 };
@@ -240,6 +240,68 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int which, size
   *hi = b < n ? b : n;
 }
 
+// ------------------------------------------------------------------ allreduce, flag-in-data (small messages)
+// Every member pushes its `n` elements as 8-byte packets (4 bytes of payload + the 4-byte generation of
+// this call) into slot `my_pe` of every member's packet buffer; each member then polls the packets of all
+// members and reduces them locally.  One link crossing, no barrier: arrival of a packet is its own signal.
+// The buffer halves and the generation counter are the ones the flag-in-data fcollect uses, so the two may
+// be mixed freely on a team.  Needs n * sizeof(T) to be a multiple of 4 and at most ll_bytes / (4 * size).
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int allreduce_ll(const bshmemi_team_t* t, T* dst, const T* src, size_t n, int slot) {
+  typedef typename Acc<T>::type A;
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[slot] + 1;
+  const uint32_t flag = (uint32_t)gen;
+  const size_t words = n * sizeof(T) / 4;
+  uint64_t* buf = (uint64_t*)(t->ll_base + (gen & 1) * (t->ll_bytes / 2));  // [size][words] packets
+  const uint32_t* s32 = (const uint32_t*)src;
+  for (size_t i = rank; i < words * size; i += G) {
+    const int p = (int)(i / words);
+    const size_t w = i % words;
+    *(volatile uint64_t*)translate(buf + (size_t)me * words + w, team_world_pe(t, p)) = ((uint64_t)flag << 32) | s32[w];
+  }
+  group_sync<SCOPE>();  // in place: every word of src has been sent before any of dst is written
+  // One unit = the packets of max(4, sizeof(T)) bytes: one 8-byte element, one 4-byte element or two 2-byte ones.
+  constexpr int UW = sizeof(T) > 4 ? (int)sizeof(T) / 4 : 1;     // packets per unit
+  constexpr int UE = sizeof(T) >= 4 ? 1 : 4 / (int)sizeof(T);    // elements per unit
+  const size_t units = words / UW;
+  int err = 0;
+  const uint64_t start = global_timer_ns(), limit = bshmemi_state_d.wait_timeout_ns;
+  for (size_t u = rank; u < units; u += G) {
+    A acc[UE];
+    for (int p = 0; p < size; ++p) {
+      uint32_t raw[UW];
+#pragma unroll
+      for (int k = 0; k < UW; ++k) {
+        const volatile uint64_t* pk = buf + (size_t)p * words + u * UW + k;
+        uint64_t packet = *pk;
+        uint32_t spins = 0;
+        while ((uint32_t)(packet >> 32) != flag) {
+          packet = *pk;
+          if ((++spins & 0xff) == 0 && global_timer_ns() - start > limit) {
+            record_timeout((const void*)pk, flag, packet >> 32, BSHMEM_WHERE_COLL);
+            err = 1;
+            break;
+          }
+        }
+        raw[k] = (uint32_t)packet;
+      }
+      T e[UE];
+      memcpy(e, raw, UW * 4);
+#pragma unroll
+      for (int k = 0; k < UE; ++k) acc[k] = p == 0 ? to_acc<T>(e[k]) : combine<A, OP>(acc[k], to_acc<T>(e[k]));
+    }
+#pragma unroll
+    for (int k = 0; k < UE; ++k) dst[u * UE + k] = from_acc<T>(acc[k]);
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[slot] = gen;
+  return err;
+}
+
 // ------------------------------------------------------------------ allreduce
 // `src` and `dst` are symmetric; in-place is allowed (it then uses two-shot).
 // Works on elements [lo, hi) so that CTA c of a multi-CTA launch can own a slice
@@ -258,6 +320,13 @@ __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, 
   const bool nvls_ok = OP == OP_SUM && MultimemSum<T>::supported && t->has_nvls && (bytes % 16) == 0 &&
                        (((uintptr_t)(src + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
   if (algo == RED_AUTO) algo = bshmemi_state_d.reduce_algo;
+  // Flag-in-data: whole small messages only (one group owns the team's packet buffer).
+  const bool ll_ok = lo == 0 && slot == 0 && bytes > 0 && (bytes & 3) == 0 && ((uintptr_t)src & 3) == 0 && 4 * bytes * size <= t->ll_bytes;
+  if (algo == RED_AUTO && ll_ok && bytes <= bshmemi_state_d.fcollect_ll_threshold) algo = RED_LL;
+  if (algo == RED_LL) {
+    if (ll_ok) return allreduce_ll<T, OP, SCOPE>(t, dst, src, hi, slot);
+    algo = RED_AUTO;
+  }
   if (algo == RED_AUTO) {
     if (nvls_ok) algo = ((hi - lo) <= bshmemi_state_d.reduce_nvls_threshold && dst != src) ? RED_NVLS_ONESHOT : RED_NVLS_TWOSHOT;
     else algo = (bytes <= bshmemi_state_d.reduce_oneshot_threshold && dst != src) ? RED_ONESHOT_PULL : RED_TWOSHOT;

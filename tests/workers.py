@@ -502,7 +502,7 @@ def collectives_on_stream():
     sizes = [1, 3, 8, 255, 1024, 4097, 65536, 1 << 20]
     cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.int32, "min"), (torch.int64, "xor"), (torch.float64, "prod"), (torch.uint8, "and"),
              (torch.int16, "or")]
-    red_algos = ["auto", "oneshot", "twoshot"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
+    red_algos = ["auto", "oneshot", "twoshot", "ll"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
     for dtype, op in cases:
         for count in sizes:
             if dtype.is_floating_point:
@@ -516,7 +516,7 @@ def collectives_on_stream():
             src.copy_(make(count))
             allsrc = _gather(src)
             want = _oracle(op, allsrc)
-            for algo in (red_algos if op == "sum" else red_algos[:3]):
+            for algo in (red_algos if op == "sum" else red_algos[:4]):
                 dst.zero_()
                 nv.barrier_all()
                 nv.reduce(0, dst, src, op, algo=algo)
