@@ -113,8 +113,45 @@ def get_multicast_buffer(team: int, buf: Buffer) -> Buffer:
     return view
 
 
-def register_external_buffer(buf) -> Buffer:
-    raise NvshmemError("mapping caller-owned allocations into the symmetric heap is not implemented; allocate with buffer()/tensor()")
+def register_external_buffer(buf, size: int | None = None) -> Buffer:
+    """Collective: maps caller-owned device memory into the symmetric heap and returns the symmetric view.
+
+    `buf` is a :class:`Buffer`, an int address or anything with ``data_ptr()`` / ``nbytes``.  The memory must be one
+    ``cuMemCreate`` allocation of this GPU, shareable as a POSIX file descriptor, whose size is a multiple of the heap's
+    growth granule (512 MB by default) and the same on every PE: memory from ``cudaMalloc`` or torch's default allocator
+    does not qualify (reference: nvshmem4py/nvshmem/core/memory.py, register_external_buffer; the reference's
+    torch_mempool example allocates such memory through a pluggable allocator).
+    """
+    if isinstance(buf, Buffer):
+        ptr, nbytes = buf.ptr, buf.size
+    elif hasattr(buf, "data_ptr"):
+        ptr, nbytes = int(buf.data_ptr()), int(buf.numel() * buf.element_size())
+    else:
+        ptr, nbytes = int(buf), size
+    if size is not None:
+        nbytes = int(size)
+    if not nbytes:
+        raise NvshmemInvalid("register_external_buffer needs the size of the allocation")
+    lib = H.load()
+    lib.nvshmemx_buffer_register_symmetric.restype = C.c_void_p
+    lib.nvshmemx_buffer_register_symmetric.argtypes = [C.c_void_p, C.c_size_t, C.c_int]
+    mapped = lib.nvshmemx_buffer_register_symmetric(C.c_void_p(ptr), nbytes, 0)
+    if not mapped:
+        raise NvshmemError("the buffer cannot be registered: it must be a cuMemCreate allocation of this GPU with a POSIX-FD handle type "
+                           "and a size that is a multiple of the heap's growth granule")
+    view = Buffer(mapped, nbytes, BufferKind.EXTERNAL, True, owner=buf)
+    _tracked[mapped] = {"buffer": view, "ref_count": 1, "kind": BufferKind.EXTERNAL, "freed": False}
+    return view
+
+
+def unregister_external_buffer(view: Buffer) -> None:
+    """Collective: undoes :func:`register_external_buffer`."""
+    lib = H.load()
+    lib.nvshmemx_buffer_unregister_symmetric.restype = C.c_int
+    lib.nvshmemx_buffer_unregister_symmetric.argtypes = [C.c_void_p, C.c_size_t]
+    if lib.nvshmemx_buffer_unregister_symmetric(C.c_void_p(view.ptr), view.size) != 0:
+        raise NvshmemInvalid(f"{view!r} was not made by register_external_buffer")
+    _tracked.pop(view.ptr, None)
 
 
 # ------------------------------------------------------------------ torch interop
