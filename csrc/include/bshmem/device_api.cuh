@@ -221,5 +221,62 @@ BSHMEM_DEVX int nvshmemx_double2_maxloc_reduce_block(nvshmem_team_t team, double
   return n == 1 ? bshmem::maxloc_double2<bshmem::SCOPE_BLOCK>(team, d, s) : 1;
 }
 
+// ------------------------------------------------------------------ byte collectives at warp / block scope
+BSHMEM_DEVX int nvshmemx_alltoallmem_warp(nvshmem_team_t team, void* d, const void* s, size_t bytes) { return bshmem::alltoall<char, bshmem::SCOPE_WARP>(team, (char*)d, (const char*)s, bytes); }
+BSHMEM_DEVX int nvshmemx_alltoallmem_block(nvshmem_team_t team, void* d, const void* s, size_t bytes) { return bshmem::alltoall<char, bshmem::SCOPE_BLOCK>(team, (char*)d, (const char*)s, bytes); }
+BSHMEM_DEVX int nvshmemx_fcollectmem_warp(nvshmem_team_t team, void* d, const void* s, size_t bytes) { return bshmem::fcollect<char, bshmem::SCOPE_WARP>(team, (char*)d, (const char*)s, bytes); }
+BSHMEM_DEVX int nvshmemx_fcollectmem_block(nvshmem_team_t team, void* d, const void* s, size_t bytes) { return bshmem::fcollect<char, bshmem::SCOPE_BLOCK>(team, (char*)d, (const char*)s, bytes); }
+BSHMEM_DEVX int nvshmemx_broadcastmem_warp(nvshmem_team_t team, void* d, const void* s, size_t bytes, int root) { return bshmem::broadcast<char, bshmem::SCOPE_WARP>(team, (char*)d, (const char*)s, bytes, root); }
+BSHMEM_DEVX int nvshmemx_broadcastmem_block(nvshmem_team_t team, void* d, const void* s, size_t bytes, int root) { return bshmem::broadcast<char, bshmem::SCOPE_BLOCK>(team, (char*)d, (const char*)s, bytes, root); }
+
+// ------------------------------------------------------------------ sized strided and signalling variants at warp / block scope
+#define BSHMEM_DEV_SIZED_MORE(BITS, T)                                                                                                   \
+  BSHMEM_DEVX void nvshmemx_iput##BITS##_warp(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe) { bshmem::iput<T, bshmem::SCOPE_WARP>((T*)d, (const T*)s, dst, sst, n, pe); } \
+  BSHMEM_DEVX void nvshmemx_iput##BITS##_block(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe) { bshmem::iput<T, bshmem::SCOPE_BLOCK>((T*)d, (const T*)s, dst, sst, n, pe); } \
+  BSHMEM_DEVX void nvshmemx_iget##BITS##_warp(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe) { bshmem::iget<T, bshmem::SCOPE_WARP>((T*)d, (const T*)s, dst, sst, n, pe); } \
+  BSHMEM_DEVX void nvshmemx_iget##BITS##_block(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe) { bshmem::iget<T, bshmem::SCOPE_BLOCK>((T*)d, (const T*)s, dst, sst, n, pe); } \
+  BSHMEM_DEVX void nvshmem_put##BITS##_signal_nbi(void* d, const void* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { bshmem::putmem_signal<bshmem::SCOPE_THREAD>(d, s, n * (BITS / 8), sig, v, op, pe); } \
+  BSHMEM_DEVX void nvshmemx_put##BITS##_signal_nbi_warp(void* d, const void* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { bshmem::putmem_signal<bshmem::SCOPE_WARP>(d, s, n * (BITS / 8), sig, v, op, pe); } \
+  BSHMEM_DEVX void nvshmemx_put##BITS##_signal_nbi_block(void* d, const void* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { bshmem::putmem_signal<bshmem::SCOPE_BLOCK>(d, s, n * (BITS / 8), sig, v, op, pe); }
+BSHMEM_SIZES(BSHMEM_DEV_SIZED_MORE)
+#undef BSHMEM_DEV_SIZED_MORE
+
+// ------------------------------------------------------------------ queue-pair variants
+// On transports with queue pairs the caller may pick the one an operation travels on.  Peers here are reached with
+// plain loads and stores over NVLink, which have no queues: the handle is accepted and ignored, and quiet / fence on
+// a set of queue pairs are quiet / fence.  (reference: src/include/host/nvshmemx_api.h, "QPair (qp) device APIs")
+#define BSHMEM_DEV_QP(N, T)                                                                                                              \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_p(T* d, const T v, int pe, nvshmemx_qp_handle_t) { bshmem::p<T>(d, v, pe); }                         \
+  BSHMEM_DEVX T nvshmemx_qp_##N##_g(const T* s, int pe, nvshmemx_qp_handle_t) { return bshmem::g<T>(s, pe); }                             \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::putmem<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_get(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::getmem<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_nbi(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_nbi<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_get_nbi(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::getmem_nbi<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_signal(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_signal<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), sig, v, op, pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_signal_nbi(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_signal<bshmem::SCOPE_THREAD>(d, s, n * sizeof(T), sig, v, op, pe); }
+BSHMEM_RMA_TYPES(BSHMEM_DEV_QP)
+#undef BSHMEM_DEV_QP
+#define BSHMEM_DEV_QP_SCOPED(N, T, SUF, SC)                                                                                              \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_##SUF(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::putmem<SC>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_get_##SUF(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::getmem<SC>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_nbi_##SUF(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_nbi<SC>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_get_nbi_##SUF(T* d, const T* s, size_t n, int pe, nvshmemx_qp_handle_t) { bshmem::getmem_nbi<SC>(d, s, n * sizeof(T), pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_signal_##SUF(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_signal<SC>(d, s, n * sizeof(T), sig, v, op, pe); } \
+  BSHMEM_DEVX void nvshmemx_qp_##N##_put_signal_nbi_##SUF(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, nvshmemx_qp_handle_t) { bshmem::putmem_signal<SC>(d, s, n * sizeof(T), sig, v, op, pe); }
+#define BSHMEM_DEV_QP_WARP(N, T) BSHMEM_DEV_QP_SCOPED(N, T, warp, bshmem::SCOPE_WARP)
+#define BSHMEM_DEV_QP_BLOCK(N, T) BSHMEM_DEV_QP_SCOPED(N, T, block, bshmem::SCOPE_BLOCK)
+BSHMEM_RMA_TYPES(BSHMEM_DEV_QP_WARP)
+BSHMEM_RMA_TYPES(BSHMEM_DEV_QP_BLOCK)
+#undef BSHMEM_DEV_QP_WARP
+#undef BSHMEM_DEV_QP_BLOCK
+#undef BSHMEM_DEV_QP_SCOPED
+BSHMEM_DEVX void nvshmemx_qp_signal_op(uint64_t* sig, uint64_t v, int op, int pe, nvshmemx_qp_handle_t) { bshmem::signal_op(sig, v, op, pe); }
+BSHMEM_DEVX void nvshmemx_qp_quiet(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+BSHMEM_DEVX void nvshmemx_qp_quiet_warp(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+BSHMEM_DEVX void nvshmemx_qp_quiet_block(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+BSHMEM_DEVX void nvshmemx_qp_fence(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+BSHMEM_DEVX void nvshmemx_qp_fence_warp(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+BSHMEM_DEVX void nvshmemx_qp_fence_block(int, nvshmemx_qp_handle_t*, int) { bshmem::fence_sys(); }
+
 #undef BSHMEM_DEV
 #undef BSHMEM_DEVX

@@ -178,7 +178,12 @@ BSHMEM_RMA_TYPES(BSHMEM_DECL_RMA)
   BSHMEM_HD void nvshmem_iget##BITS(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe);           \
   void nvshmemx_put##BITS##_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);             \
   void nvshmemx_get##BITS##_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);             \
-  void nvshmemx_put##BITS##_signal_on_stream(void* dest, const void* src, size_t nelems, uint64_t* sig, uint64_t signal, int sig_op, int pe, cudaStream_t s);
+  void nvshmemx_put##BITS##_signal_on_stream(void* dest, const void* src, size_t nelems, uint64_t* sig, uint64_t signal, int sig_op, int pe, cudaStream_t s); \
+  void nvshmemx_put##BITS##_signal_nbi_on_stream(void* dest, const void* src, size_t nelems, uint64_t* sig, uint64_t signal, int sig_op, int pe, cudaStream_t s); \
+  void nvshmemx_put##BITS##_nbi_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);         \
+  void nvshmemx_get##BITS##_nbi_on_stream(void* dest, const void* src, size_t nelems, int pe, cudaStream_t s);         \
+  void nvshmemx_iput##BITS##_on_stream(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe, cudaStream_t s); \
+  void nvshmemx_iget##BITS##_on_stream(void* dest, const void* src, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe, cudaStream_t s);
 BSHMEM_SIZES(BSHMEM_DECL_SIZED)
 #undef BSHMEM_DECL_SIZED
 
@@ -254,6 +259,14 @@ BSHMEM_STANDARD_REDUCE_TYPES(BSHMEM_DECL_ARITH)
 #undef BSHMEM_DECL_BITWISE
 #undef BSHMEM_DECL_ARITH
 #undef BSHMEM_DECL_REDUCE_OP
+
+/* ---------------------------------------------------------------- queue pairs
+ * Handles for the nvshmemx_qp_* device calls.  Peers reached by loads and stores have no queues: every handle
+ * names the same (only) path, and an MPI communicator cannot be used to initialise (no MPI bootstrap is built). */
+typedef int nvshmemx_qp_handle_t;
+enum { NVSHMEMX_QP_HOST = 0, NVSHMEMX_QP_DEFAULT = 1, NVSHMEMX_QP_ANY = 0x7fffffff, NVSHMEMX_QP_ALL = 0x7fffffff };
+int nvshmemx_qp_create(int num_qps, nvshmemx_qp_handle_t** out_qp_array);
+int nvshmemx_set_attr_mpi_comm_args(void* mpi_comm, nvshmemx_init_attr_t* attr);
 
 /* ---------------------------------------------------------------- collective launch */
 int nvshmemx_collective_launch(const void* func, dim3 grid_dims, dim3 block_dims, void** args, size_t shared_mem, cudaStream_t stream);

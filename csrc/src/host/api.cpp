@@ -549,6 +549,29 @@ BSHMEM_RMA_TYPES(BSHMEM_DEF_RMA)
   void nvshmemx_put##BITS##_signal_on_stream(void* d, const void* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, cudaStream_t st) { nvshmemx_putmem_signal_on_stream(d, s, n * (BITS / 8), sig, v, op, pe, st); }
 BSHMEM_SIZES(BSHMEM_DEF_SIZED)
 #undef BSHMEM_DEF_SIZED
+#define BSHMEM_DEF_SIZED_MORE(BITS, T)                                                                                                   \
+  void nvshmemx_put##BITS##_signal_nbi_on_stream(void* d, const void* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe, cudaStream_t st) { nvshmemx_putmem_signal_on_stream(d, s, n * (BITS / 8), sig, v, op, pe, st); } \
+  void nvshmemx_put##BITS##_nbi_on_stream(void* d, const void* s, size_t n, int pe, cudaStream_t st) { rma(d, s, n * (BITS / 8), pe, true, COPY_STREAM, st, "nvshmemx_put" #BITS "_nbi_on_stream"); } \
+  void nvshmemx_get##BITS##_nbi_on_stream(void* d, const void* s, size_t n, int pe, cudaStream_t st) { rma(d, s, n * (BITS / 8), pe, false, COPY_STREAM, st, "nvshmemx_get" #BITS "_nbi_on_stream"); } \
+  void nvshmemx_iput##BITS##_on_stream(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe, cudaStream_t st) { rma_strided(d, s, dst, sst, n, BITS / 8, pe, true, COPY_STREAM, st, "nvshmemx_iput" #BITS "_on_stream"); } \
+  void nvshmemx_iget##BITS##_on_stream(void* d, const void* s, ptrdiff_t dst, ptrdiff_t sst, size_t n, int pe, cudaStream_t st) { rma_strided(d, s, dst, sst, n, BITS / 8, pe, false, COPY_STREAM, st, "nvshmemx_iget" #BITS "_on_stream"); }
+BSHMEM_SIZES(BSHMEM_DEF_SIZED_MORE)
+#undef BSHMEM_DEF_SIZED_MORE
+
+// Queue-pair handles: one path to every peer, so every handle is the default one.
+int nvshmemx_qp_create(int num_qps, nvshmemx_qp_handle_t** out_qp_array) {
+  if (num_qps <= 0 || !out_qp_array) return NVSHMEMX_ERROR_INVALID_VALUE;
+  nvshmemx_qp_handle_t* h = (nvshmemx_qp_handle_t*)malloc(sizeof(nvshmemx_qp_handle_t) * (size_t)num_qps);
+  if (!h) return NVSHMEMX_ERROR_OUT_OF_MEMORY;
+  for (int i = 0; i < num_qps; ++i) h[i] = NVSHMEMX_QP_DEFAULT;
+  *out_qp_array = h;
+  return NVSHMEMX_SUCCESS;
+}
+int nvshmemx_set_attr_mpi_comm_args(void* mpi_comm, nvshmemx_init_attr_t* attr) {
+  if (!attr) return NVSHMEMX_ERROR_INVALID_VALUE;
+  attr->mpi_comm = mpi_comm;  // recorded; initialising with it is refused (no MPI bootstrap is built)
+  return NVSHMEMX_SUCCESS;
+}
 
 // ------------------------------------------------------------------ on-stream waits
 #define BSHMEM_DEF_WAIT(N, T)                                                                                                           \
