@@ -18,3 +18,7 @@ from .collective import (reduce, reducescatter, alltoall, fcollect, broadcast, b
                          collective_on_buffer, maxloc)
 from .teams import (Teams, team_split_strided, team_split_2d, team_destroy, team_init, team_translate_pe, get_team_unique_id)  # noqa: F401
 from .types import ComparisonType, SignalOp, NvshmemError, NvshmemInvalid, NvshmemStream  # noqa: F401
+from .compat import (UniqueID, TeamConfig, TeamUniqueId, BufferTypes, InitStatus, NvshmemStreamsType, NvshmemWarning, MutableEnum, Version,  # noqa: F401
+                     NvshmemKernelObject, NvshmemResource, module_finalize, library_finalize, dtype_nbytes, get_size, tensor_get_buffer,
+                     unregister_external_tensor, array, bytearray, array_get_buffer, free_array, get_peer_array, get_multicast_array,
+                     register_external_array, unregister_external_array)

@@ -31,3 +31,27 @@ def test_every_reference_function_name_is_declared(tmp_path):
     assert len(ref) > 2500, "the reference headers did not expand"
     missing = sorted(ref - mine - KNOWN_REFERENCE_TYPOS)
     assert not missing, f"{len(missing)} names of the reference API are not declared: {missing[:20]}"
+
+
+# The names the reference's Python package exports from ``nvshmem.core`` (union of the ``__all__`` lists of
+# nvshmem4py/nvshmem/core/{collective,direct,init_fini,memory,rma,teams,nvshmem_types}.py and interop/{torch,cupy}.py).
+NVSHMEM4PY_NAMES = """
+BufferTypes ComparisonType InitStatus MutableEnum NvshmemError NvshmemInvalid NvshmemKernelObject NvshmemResource
+NvshmemStream NvshmemStreamsType SignalOp TeamConfig TeamUniqueId Teams UniqueID Version
+alltoall array array_get_buffer barrier barrier_all broadcast buffer bytearray
+bytetensor collective_on_buffer fcollect finalize free free_array free_tensor get
+get_multicast_array get_multicast_buffer get_multicast_tensor get_peer_array get_peer_buffer get_peer_tensor get_team_unique_id get_unique_id
+get_version init init_status library_finalize library_init module_finalize module_init my_pe
+n_pes put put_signal quiet reduce reducescatter register_external_array register_external_buffer
+register_external_tensor signal_op signal_wait sync sync_all team_destroy team_init team_my_pe
+team_n_pes team_split_2d team_split_strided team_translate_pe tensor tensor_get_buffer unregister_external_array unregister_external_buffer
+unregister_external_tensor
+""".split()
+
+
+def test_python_layer_exports_the_reference_names():
+    import nvshmem.core as core  # the alias package resolves to nvshmem_b200.core
+    import nvshmem_b200.core as mine
+    assert core is mine
+    missing = [n for n in NVSHMEM4PY_NAMES if not hasattr(core, n)]
+    assert not missing, missing
