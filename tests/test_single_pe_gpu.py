@@ -133,3 +133,21 @@ def test_moe_dispatch_combine_single_pe(nv):
     import tests.workers as W
     W._moe_check(nv, "bf16", T=200, H=512, K=4, E=16, seed=11)
     W._moe_check(nv, "fp8", T=128, H=1024, K=8, E=32, seed=12)
+
+
+@pytest.mark.parametrize("payload,tol", [("bf16", 0.03), ("fp8", 0.08)])
+def test_moe_block_matches_fp32_reference_single_pe(nv, payload, tol):
+    """Router + dispatch + expert MLPs + combine against a plain PyTorch fp32 version of the same block."""
+    from nvshmem_b200.models.moe_block import ExpertParallelMoE, reference_forward
+    from nvshmem_b200.ops import fused_gemm as fg
+    T, H, F, E, K = 192, 256, 384, 8, 2
+    block = ExpertParallelMoE(T, H, F, E, K, payload=payload, seed=3, wait_limit_ms=5000)
+    torch.manual_seed(17)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    got = block(x)
+    torch.cuda.synchronize()
+    fg.check_errors()
+    want = reference_forward(x, block.router, block.w_in, block.w_out, K)
+    err = (got.float() - want).abs().max().item()
+    assert err <= tol * want.abs().max().item() + 1e-3, (payload, err, want.abs().max().item())
+    block.close()
