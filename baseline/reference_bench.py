@@ -52,7 +52,7 @@ def run(args, M, N, K_LOCAL) -> dict:
     lib_path = REF / "lib" / "libnvshmem_host.so"
     plugin = REF / "lib" / "nvshmem_bootstrap_uid.so"
     if not lib_path.exists() or not plugin.exists():
-        return unavailable("baseline/_ref holds no reference build (pip cannot install /root/reference: no setup.py/pyproject.toml; the CMake build was not found)")
+        return unavailable("baseline/_ref holds no reference build (the reference is a CMake project that pip cannot install; its CMake build was not found)")
     import torch
     import torch.distributed as dist
     from bench import ClockSampler, timed_runs  # shared timing harness

@@ -1,5 +1,5 @@
 """Runs the UNMODIFIED reference perftest binaries (``baseline/_ref/bin/perftest``) through the PMI
-launcher and stores their own output under ``gpurun_out/ref_perftest/``.  These are the numbers the
+launcher and stores their own output under ``--out`` (default ``perf_out/ref_perftest/``).  These are the numbers the
 library's own perftest drivers are compared with.
 
   python -m baseline.reference_perftest --npes 2 --group p2p          # put/get/signal/atomic, 2 PEs
@@ -53,8 +53,9 @@ def main() -> int:
     ap.add_argument("--group", default="p2p", choices=["p2p", "coll"])
     ap.add_argument("--timeout", type=float, default=120.0)
     ap.add_argument("--only", default="")
+    ap.add_argument("--out", default="perf_out/ref_perftest")
     args = ap.parse_args()
-    out_dir = Path("gpurun_out/ref_perftest")
+    out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     if not (REF / "bin" / "perftest").exists():
         print("no reference build under baseline/_ref")

@@ -90,7 +90,7 @@ def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--list", default="p2p", choices=sorted(LISTS))
     ap.add_argument("--npes", default="2", help="comma-separated PE counts")
-    ap.add_argument("--out", default="gpurun_out/perftest")
+    ap.add_argument("--out", default="perf_out/perftest")
     ap.add_argument("--timeout", type=float, default=600.0, help="seconds per test")
     args = ap.parse_args()
     counts = [int(x) for x in args.npes.split(",") if x]
