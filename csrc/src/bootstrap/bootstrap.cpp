@@ -52,6 +52,7 @@ int bootstrap_init(int mode, const bshmem_uniqueid_t* id, int rank, int nranks, 
   memset(handle, 0, sizeof(*handle));
   int st;
   if (mode == BOOT_PLUGIN) st = bootstrap_plugin_init(nullptr, (void*)id, handle);
+  else if (mode == BOOT_PMI) st = bootstrap_pmi_init(handle);
   else st = bootstrap_uid_init(id, rank, nranks, handle);
   if (st != BOOT_OK) return st;
   return bootstrap_fill_node_info(handle);

@@ -41,7 +41,7 @@ typedef int (*bshmem_bootstrap_plugin_init_fn)(void* attr, bshmem_bootstrap_hand
 
 namespace bshmem {
 
-enum BootstrapMode { BOOT_UID = 0, BOOT_PLUGIN = 1 };
+enum BootstrapMode { BOOT_UID = 0, BOOT_PLUGIN = 1, BOOT_PMI = 2 };
 
 enum BootstrapStatus {
   BOOT_OK = 0,
@@ -61,6 +61,9 @@ int bootstrap_uid_get_unique_id(bshmem_uniqueid_t* id);
 // the id may be null: the root address comes from the variable and rank 0
 // starts the root thread itself.
 int bootstrap_uid_init(const bshmem_uniqueid_t* id, int rank, int nranks, bshmem_bootstrap_handle_t* handle);
+// PMI-1 client: rank, size and a socket to the process manager come from PMI_RANK, PMI_SIZE and PMI_FD.
+bool bootstrap_pmi_available();
+int bootstrap_pmi_init(bshmem_bootstrap_handle_t* handle);
 // Loads NVSHMEM_BOOTSTRAP_PLUGIN (or `path`) and calls its init entry point.
 int bootstrap_plugin_init(const char* path, void* attr, bshmem_bootstrap_handle_t* handle);
 // Chooses the mode from NVSHMEM_BOOTSTRAP and initialises `handle`.

@@ -148,6 +148,10 @@ int do_init(unsigned int flags, nvshmemx_init_attr_t* attr, bool hostlib_only) {
     return runtime_init((const bshmem_uniqueid_t*)attr->args.uid_args.id, attr->args.uid_args.myrank, attr->args.uid_args.nranks, device, hostlib_only, BOOT_UID);
   }
   if (mode == "PLUGIN") return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_PLUGIN);
+  // Started by a PMI process manager (mpiexec / nvshmrun / srun): asked for by name, or recognised by the
+  // manager's variables when nothing names a rank for the unique-id bootstrap.
+  if (mode == "PMI" || (bootstrap_pmi_available() && !getenv("RANK") && !getenv("NVSHMEM_BOOTSTRAP_UID_RANK")))
+    return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_PMI);
   // Plain nvshmem_init(): a launcher must have told us who we are.  torchrun-style
   // variables are understood; the session id names the root's address.
   const char* rank = getenv("NVSHMEM_BOOTSTRAP_UID_RANK") ? getenv("NVSHMEM_BOOTSTRAP_UID_RANK") : getenv("RANK");
