@@ -277,6 +277,9 @@ int nvshmemx_collective_launch_query_gridsize(const void* func, dim3 block_dims,
  * every later API call do this on their own; call it after loading such a library at run time when
  * its kernels are launched before any other call into this library. */
 void nvshmemx_b200_module_sync(void);
+/* On-stream alltoall / fcollect / broadcast of at least `min_bytes` (whole buffer) use the copy engines from now on
+ * (0 = never, the default; also NVSHMEM_CE_COLLECTIVES_MIN_BYTES).  Call it with the same value on every PE. */
+void nvshmemx_b200_set_ce_collectives(size_t min_bytes);
 
 #if defined(__cplusplus) && !defined(BSHMEM_NO_INLINE_LAUNCH)
 /* A kernel's host-side handle belongs to the CUDA runtime instance of the program that defines it.  A program

@@ -199,12 +199,58 @@ int coll_reducescatter_on_stream(int team, void* dst, const void* src, size_t nr
   return launch_status("reducescatter");
 }
 
+// ------------------------------------------------------------------ copy-engine variants
+// Large alltoall / fcollect / broadcast as one cudaMemcpyAsync per peer into the peer's mapped window, then the
+// barrier kernel: the copy engines move the data and no SM is busy meanwhile.  Stream order puts the copies
+// before the barrier, whose system-scope fence and flag exchange then tell every member that the data of all
+// members has landed.  Off unless NVSHMEM_CE_COLLECTIVES_MIN_BYTES (or nvshmemx_b200_set_ce_collectives) names a
+// size; NVSHMEM_DISABLE_CE_COLLECTIVES wins.  (reference: src/host/stream/coll/*: "copy-engine collectives")
+static bool ce_wanted(size_t total_bytes, int algo_auto) {
+  const size_t min_bytes = rt().ce_min_bytes.load();
+  return algo_auto && min_bytes != 0 && total_bytes >= min_bytes && !options().DISABLE_CE_COLLECTIVES;
+}
+static int ce_copy(void* dst_local_addr, const void* src, size_t bytes, int world_pe, cudaStream_t stream) {
+  void* remote = rt().heap->translate(dst_local_addr, world_pe);
+  if (!remote) return ST_INVALID_VALUE;
+  return cudaMemcpyAsync(remote, src, bytes, cudaMemcpyDeviceToDevice, stream) == cudaSuccess ? ST_SUCCESS : ST_INTERNAL;
+}
+static int ce_fcollect(Team* t, void* dst, const void* src, size_t block_bytes, cudaStream_t stream) {
+  int st = ST_SUCCESS;
+  for (int i = 1; i <= t->size && !st; ++i) {  // the member after me first, my own copy last
+    const int m = (t->my_pe + i) % t->size;
+    st = ce_copy((char*)dst + (size_t)t->my_pe * block_bytes, src, block_bytes, t->members[m], stream);
+  }
+  return st ? st : coll_barrier_on_stream(t->idx, stream, true);
+}
+static int ce_alltoall(Team* t, void* dst, const void* src, size_t block_bytes, cudaStream_t stream) {
+  int st = ST_SUCCESS;
+  for (int i = 1; i <= t->size && !st; ++i) {
+    const int m = (t->my_pe + i) % t->size;
+    st = ce_copy((char*)dst + (size_t)t->my_pe * block_bytes, (const char*)src + (size_t)m * block_bytes, block_bytes, t->members[m], stream);
+  }
+  return st ? st : coll_barrier_on_stream(t->idx, stream, true);
+}
+static int ce_broadcast(Team* t, void* dst, const void* src, size_t bytes, int root, cudaStream_t stream) {
+  int st = ST_SUCCESS;
+  if (t->my_pe == root)
+    for (int i = 1; i <= t->size && !st; ++i) {
+      const int m = (t->my_pe + i) % t->size;
+      if (m == root && dst == src) continue;
+      st = ce_copy(dst, src, bytes, t->members[m], stream);
+    }
+  return st ? st : coll_barrier_on_stream(t->idx, stream, true);
+}
+
 int coll_fcollect_on_stream(int team, void* dst, const void* src, size_t block_bytes, cudaStream_t stream, int algo) {
   NvtxRange nvtx(NVTX_COLL, "fcollect_on_stream");
   int st = check_team(team, "fcollect");
   if (st) return st;
   if (block_bytes == 0) return ST_SUCCESS;
   const size_t total = block_bytes * team_get(team)->size;
+  if (ce_wanted(total, algo == FC_AUTO) && rt().heap->contains(dst)) {
+    rt().n_coll++;
+    return ce_fcollect(team_get(team), dst, src, block_bytes, stream);
+  }
   const int threads = (int)std::min<long>(1024, std::max<long>(32, options().FCOLLECT_NTHREADS));
   fcollect_kernel<<<ctas_for(total, (size_t)64 << 10), threads, 0, stream>>>(team, dst, src, block_bytes, algo);
   rt().n_coll++;
@@ -217,6 +263,10 @@ int coll_alltoall_on_stream(int team, void* dst, const void* src, size_t block_b
   if (st) return st;
   if (block_bytes == 0) return ST_SUCCESS;
   const size_t total = block_bytes * team_get(team)->size;
+  if (ce_wanted(total, 1) && rt().heap->contains(dst)) {
+    rt().n_coll++;
+    return ce_alltoall(team_get(team), dst, src, block_bytes, stream);
+  }
   alltoall_kernel<<<ctas_for(total, (size_t)64 << 10), 512, 0, stream>>>(team, dst, src, block_bytes);
   rt().n_coll++;
   return launch_status("alltoall");
@@ -228,6 +278,10 @@ int coll_broadcast_on_stream(int team, void* dst, const void* src, size_t bytes,
   if (st) return st;
   if (root < 0 || root >= team_get(team)->size) return ST_INVALID_VALUE;
   if (bytes == 0) return ST_SUCCESS;
+  if (ce_wanted(bytes, algo == BC_AUTO) && rt().heap->contains(dst)) {
+    rt().n_coll++;
+    return ce_broadcast(team_get(team), dst, src, bytes, root, stream);
+  }
   broadcast_kernel<<<ctas_for(bytes, (size_t)64 << 10), 512, 0, stream>>>(team, dst, src, bytes, root, algo);
   rt().n_coll++;
   return launch_status("broadcast");

@@ -721,6 +721,7 @@ int nvshmemx_collective_launch(const void* func, dim3 grid, dim3 block, void** a
 }
 
 // ------------------------------------------------------------------ library extensions
+void nvshmemx_b200_set_ce_collectives(size_t min_bytes) { rt().ce_min_bytes = min_bytes; }
 void nvshmemx_b200_module_sync(void) {
   if (is_initialized()) push_device_state();
 }

@@ -314,6 +314,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   d.barrier_tg_dissem_kval = (int)std::max<long>(o.BARRIER_TG_DISSEM_KVAL, 2);
   d.bcast_tree_kval = (int)std::max<long>(o.BCAST_TREE_KVAL, 2);
   d.debug_checks = o.ENABLE_ERROR_CHECKS;
+  r.ce_min_bytes = o.CE_COLLECTIVES_MIN_BYTES;
   d.reduce_nvls_threshold = o.REDUCE_NVLS_THRESHOLD;
   d.reduce_oneshot_threshold = o.REDUCE_ONESHOT_THRESHOLD;
   d.fcollect_ll_threshold = o.FCOLLECT_LL_THRESHOLD;

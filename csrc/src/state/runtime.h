@@ -107,6 +107,7 @@ struct Runtime {
   std::map<std::string, uint64_t> algo_counts;
   uint64_t* host_scratch64 = nullptr;        // symmetric uint64[4 + 2*words] for internal reductions (team index agreement)
   void* malloc_sentinel = nullptr;
+  std::atomic<size_t> ce_min_bytes{0};       // copy-engine collectives from this size on (0: never)
 };
 
 Runtime& rt();

@@ -39,6 +39,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Use the host-memory heap back end instead of CUDA virtual memory management") \
   X(DISABLE_P2P,           bool,        Bool, false,            Hidden,      "Treat peers as not load/store reachable (init then fails: no remote transport is built)") \
   X(DISABLE_CE_COLLECTIVES,bool,        Bool, false,            Collectives, "Never use copy engines for on-stream alltoall/fcollect/broadcast") \
+  X(CE_COLLECTIVES_MIN_BYTES, size_t,   Size, 0,                Collectives, "On-stream alltoall/fcollect/broadcast of at least this many bytes go through copy engines (0: never)") \
   X(MAX_TEAMS,             long,        Long, 128,              OpenShmem,   "Maximum number of simultaneous teams")                     \
   X(MAX_MEMORY_PER_GPU,    size_t,      Size, (size_t)256 << 30,Memory,      "Virtual address window reserved per PE for the symmetric heap") \
   X(CUMEM_GRANULARITY,     size_t,      Size, (size_t)512 << 20,Memory,      "Granularity of physical heap growth")                      \

@@ -9,7 +9,7 @@ RMA calls (``put``, ``get``, ``put_signal``, ``signal_op``, ``signal_wait``,
 """
 from .init_fini import (finalize, get_unique_id, get_version, init, init_status, is_initialized,  # noqa: F401
                         library_init, module_init)
-from .direct import my_pe, n_pes, team_my_pe, team_n_pes, error_bits, clear_errors, set_wait_timeout_ms, topology, heap_info  # noqa: F401
+from .direct import my_pe, n_pes, team_my_pe, team_n_pes, error_bits, clear_errors, set_wait_timeout_ms, set_ce_collectives, topology, heap_info  # noqa: F401
 from .memory import (Buffer, buffer, free, get_peer_buffer, get_multicast_buffer, register_external_buffer, unregister_external_buffer,  # noqa: F401
                      tensor, bytetensor, free_tensor, get_peer_tensor, get_multicast_tensor, register_external_tensor,
                      tensor_ptr, peer_ptr)

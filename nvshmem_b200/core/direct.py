@@ -41,6 +41,15 @@ def set_wait_timeout_ms(ms: int) -> None:
     H.load().nvshmemx_b200_set_wait_timeout_ms(int(ms))
 
 
+def set_ce_collectives(min_bytes: int) -> None:
+    """On-stream alltoall / fcollect / broadcast of at least `min_bytes` use the copy engines (0: never, the default).
+    Every PE must set the same value."""
+    lib = H.load()
+    lib.nvshmemx_b200_set_ce_collectives.restype = None
+    lib.nvshmemx_b200_set_ce_collectives.argtypes = [C.c_size_t]
+    lib.nvshmemx_b200_set_ce_collectives(int(min_bytes))
+
+
 def topology() -> str:
     return H.load().nvshmemx_b200_topology().decode()
 

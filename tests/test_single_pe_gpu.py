@@ -151,3 +151,24 @@ def test_moe_block_matches_fp32_reference_single_pe(nv, payload, tol):
     err = (got.float() - want).abs().max().item()
     assert err <= tol * want.abs().max().item() + 1e-3, (payload, err, want.abs().max().item())
     block.close()
+
+
+def test_copy_engine_collectives_on_one_pe(nv):
+    """The copy-engine variants of fcollect / alltoall / broadcast (one memcpy per member + barrier)."""
+    n = 1 << 16
+    src = nv.tensor((n,), torch.float32)
+    dst = nv.tensor((n,), torch.float32)
+    src.copy_(torch.arange(n, device="cuda", dtype=torch.float32))
+    nv.set_ce_collectives(1)
+    try:
+        for coll in ("fcollect", "alltoall", "broadcast"):
+            dst.zero_()
+            nv.collective_on_buffer(coll, 0, dst, src, op="sum")
+            nv.barrier_all()
+            torch.cuda.synchronize()
+            assert torch.equal(dst, src), coll
+    finally:
+        nv.set_ce_collectives(0)
+    assert nv.error_bits() == 0
+    nv.free_tensor(src)
+    nv.free_tensor(dst)
