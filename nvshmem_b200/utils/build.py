@@ -92,7 +92,8 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
     hdr = _headers_mtime()
     jobs = jobs or min(8, os.cpu_count() or 4)
     groups = {
-        "host": (_sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), LIB / "libbshmem_host.so", True, ["-ldl", "-lpthread", "-lrt"]),
+        "host": (_sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), LIB / "libbshmem_host.so", True,
+                 ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
         "fused": (_sources("fused"), LIB / "libbshmem_fused.so", True, ["-ldl"]),
         "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
         "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
