@@ -49,3 +49,23 @@ def test_uid_based_init(tmp_path):
     if n < 2:
         pytest.skip("needs two GPUs")
     _run("uid-based-init", n, env={"UID_FILE": str(tmp_path / "uid.bin")})
+
+
+def test_launcher_reports_the_first_failure_and_stops_the_other_ranks():
+    import sys
+    import time
+    from nvshmem_b200.launch import launch
+    code = ("import os, sys, time\n"
+            "r = int(os.environ['RANK']); assert os.environ['WORLD_SIZE'] == '3' and os.environ['LOCAL_RANK'] == str(r)\n"
+            "assert os.environ['NVSHMEM_BOOTSTRAP_UID_SESSION_ID'].startswith('127.0.0.1:')\n"
+            "sys.exit(7) if r == 1 else time.sleep(60)\n")
+    t0 = time.time()
+    status, outs = launch(3, [sys.executable, "-c", code], timeout=50, capture=True)
+    assert status == 7 and time.time() - t0 < 30  # the sleeping ranks were terminated, not waited for
+
+
+def test_launcher_times_out():
+    import sys
+    from nvshmem_b200.launch import launch
+    status, _ = launch(2, [sys.executable, "-c", "import time; time.sleep(60)"], timeout=1.5, capture=True)
+    assert status == 124
