@@ -231,4 +231,27 @@ int perf_coll_latency(int kind, void* dst, const void* src, size_t n, int iters,
   k_coll_latency<<<1, threads, 0, s>>>(kind, dst, src, n, iters);
   return OK();
 }
+// Issues `iters` on-stream calls of one kind back to back from C, the way the reference's host perftests do
+// (no interpreter between the launches).  kind: 0 float sum all-reduce, 1 float sum reduce-scatter, 2 fcollect,
+// 3 alltoall, 4 broadcast from PE 0, 5 barrier_all, 6 sync_all, 7 putmem to `pe`, 8 getmem from `pe`.
+// `bytes` is the whole buffer per PE (block size = bytes / npes where the call works on blocks).
+int perf_onstream_loop(int kind, void* dst, const void* src, size_t bytes, int pe, int iters, cudaStream_t s) {
+  const int n = nvshmem_n_pes();
+  int st = 0;
+  for (int i = 0; i < iters && !st; ++i) {
+    switch (kind) {
+      case 0: st = nvshmemx_float_sum_reduce_on_stream(NVSHMEM_TEAM_WORLD, (float*)dst, (const float*)src, bytes / 4, s); break;
+      case 1: st = nvshmemx_float_sum_reducescatter_on_stream(NVSHMEM_TEAM_WORLD, (float*)dst, (const float*)src, bytes / 4 / n, s); break;
+      case 2: st = nvshmemx_fcollectmem_on_stream(NVSHMEM_TEAM_WORLD, dst, src, bytes / n, s); break;
+      case 3: st = nvshmemx_alltoallmem_on_stream(NVSHMEM_TEAM_WORLD, dst, src, bytes / n, s); break;
+      case 4: st = nvshmemx_broadcastmem_on_stream(NVSHMEM_TEAM_WORLD, dst, src, bytes, 0, s); break;
+      case 5: nvshmemx_barrier_all_on_stream(s); break;
+      case 6: nvshmemx_sync_all_on_stream(s); break;
+      case 7: nvshmemx_putmem_on_stream(dst, src, bytes, pe, s); break;
+      case 8: nvshmemx_getmem_on_stream(dst, src, bytes, pe, s); break;
+      default: return 1;
+    }
+  }
+  return st;
+}
 }

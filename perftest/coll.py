@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--graph", action="store_true", help="also time the collectives replayed from a CUDA graph")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--c-loop", action="store_true", help="also issue the automatic choice of each on-stream call from a C loop (eager, no interpreter between launches)")
     ap.add_argument("--cold", action="store_true", help="also time single calls with the L2 flushed before each (8 MB and up)")
     ap.add_argument("--algos", default="all", help="'all' or 'best': only the automatic choice of each collective")
     args = ap.parse_args()
@@ -91,6 +92,23 @@ def main():
         break_after_first = False
     # barrier / sync latency: on-stream and device-initiated
     lib = env.devlib()
+    if args.c_loop:
+        # The same calls issued eagerly from C, as the reference's host perftests issue theirs.
+        lib.perf_onstream_loop.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
+        kinds = ((0, "allreduce_on_stream", "allreduce"), (1, "reducescatter_on_stream", "reducescatter"), (2, "fcollect_on_stream", "fcollect"),
+                 (3, "alltoall_on_stream", "alltoall"), (4, "broadcast_on_stream", "broadcast"))
+        for size in sizes_pow2(lo, hi):
+            if size % (4 * n):
+                continue
+            iters = 20 if size <= (16 << 20) else 8
+            for kind, name, fac in kinds:
+                ms = env.time_ms(lambda: ok(lib.perf_onstream_loop(kind, C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), size, 0, iters, stream_ptr())), iters=3, warmup=1)
+                us = ms * 1e3 / iters
+                env.record(test=name, algo="auto", dtype="fp32", bytes_per_pe=size, us=round(us, 2), busbw_GBps=round(size / (us * 1e-6) / 1e9 * busbw_factor(fac, n), 2),
+                           npes=n, nvls=nvls, issue="c-loop")
+        for kind, name in ((5, "barrier_all_on_stream"), (6, "sync_all_on_stream")):
+            ms = env.time_ms(lambda: ok(lib.perf_onstream_loop(kind, None, None, 0, 0, 100, stream_ptr())), iters=3, warmup=1)
+            env.record(test=name, us=round(ms * 1e3 / 100, 2), npes=n, issue="c-loop")
     ms = env.time_graph_ms(lambda st: nv.barrier_all(stream=st), iters=50)
     env.record(test="barrier_all_on_stream", us=round(ms * 1e3, 2), npes=n, issue="graph")
     ms = env.time_graph_ms(lambda st: nv.sync_all(stream=st), iters=50)
