@@ -326,11 +326,59 @@ void* nvshmemx_mc_ptr(nvshmem_team_t team, const void* ptr) {
   if (!t || !t->nvls) return nullptr;
   return rt().heap->mc_translate(ptr);
 }
-// Local buffer registration only matters to NIC transports; with load/store
-// peers every device buffer is already usable as a local source or target.
-int nvshmemx_buffer_register(void*, size_t) { return NVSHMEMX_SUCCESS; }
-int nvshmemx_buffer_unregister(void*) { return NVSHMEMX_SUCCESS; }
-void nvshmemx_buffer_unregister_all(void) {}
+// Local buffer registration matters most to NIC transports; with load/store peers every device buffer is
+// already usable as a local source or target.
+// What registration does here: it keeps a sorted table of the ranges (double registration and unknown
+// unregistration are errors, as in the reference), and page-locks pageable host memory so that stream-ordered
+// puts and gets with it as the local side run asynchronously.  (reference: src/host/mem/mem.cpp:32-443)
+namespace {
+struct LocalRange {
+  char* base;
+  size_t bytes;
+  bool pinned_here;
+};
+std::vector<LocalRange> g_local_ranges;  // sorted by base; guarded by g_local_mu
+std::mutex g_local_mu;
+}  // namespace
+int nvshmemx_buffer_register(void* addr, size_t length) {
+  if (!addr || length == 0) return NVSHMEMX_ERROR_INVALID_VALUE;
+  std::lock_guard<std::mutex> lk(g_local_mu);
+  char* b = (char*)addr;
+  auto it = std::lower_bound(g_local_ranges.begin(), g_local_ranges.end(), b, [](const LocalRange& r, char* p) { return r.base < p; });
+  if (it != g_local_ranges.end() && it->base < b + length) return NVSHMEMX_ERROR_INVALID_VALUE;        // overlaps the next range
+  if (it != g_local_ranges.begin() && (it - 1)->base + (it - 1)->bytes > b) return NVSHMEMX_ERROR_INVALID_VALUE;  // overlaps the previous one
+  bool pinned = false;
+  if (rt().have_gpu) {
+    cudaPointerAttributes attr{};
+    const bool known = cudaPointerGetAttributes(&attr, addr) == cudaSuccess && attr.type != cudaMemoryTypeUnregistered;
+    cudaGetLastError();
+    if (!known) {
+      if (cudaHostRegister(addr, length, cudaHostRegisterPortable) != cudaSuccess) {
+        cudaGetLastError();
+        return NVSHMEMX_ERROR_INTERNAL;
+      }
+      pinned = true;
+    }
+  }
+  g_local_ranges.insert(it, LocalRange{b, length, pinned});
+  return NVSHMEMX_SUCCESS;
+}
+int nvshmemx_buffer_unregister(void* addr) {
+  std::lock_guard<std::mutex> lk(g_local_mu);
+  for (auto it = g_local_ranges.begin(); it != g_local_ranges.end(); ++it)
+    if (it->base == (char*)addr) {
+      if (it->pinned_here) cudaHostUnregister(addr);
+      g_local_ranges.erase(it);
+      return NVSHMEMX_SUCCESS;
+    }
+  return NVSHMEMX_ERROR_INVALID_VALUE;
+}
+void nvshmemx_buffer_unregister_all(void) {
+  std::lock_guard<std::mutex> lk(g_local_mu);
+  for (auto& r : g_local_ranges)
+    if (r.pinned_here) cudaHostUnregister(r.base);
+  g_local_ranges.clear();
+}
 // Maps a caller-owned VMM allocation into the symmetric heap (collective; same size on every PE) and returns
 // its symmetric address; the caller's own mapping stays valid and aliases it.
 static void republish_heap(Runtime& r) {

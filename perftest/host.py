@@ -12,7 +12,7 @@ import time
 
 import torch
 
-from .common import Env, sizes_pow2, stream_ptr
+from .common import Env, ok, sizes_pow2, stream_ptr
 from .rma import parse_size
 
 
@@ -29,12 +29,23 @@ def main():
     hi = parse_size(args.max_bytes)
     sym = nv.tensor((hi,), torch.uint8)
     local = torch.empty(hi, dtype=torch.uint8, device=env.dev)
+    try:
+        dev = env.devlib()
+        dev.perf_onstream_loop.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
+    except (OSError, AssertionError):
+        dev = None
     for size in sizes_pow2(8, hi):
         iters = 20 if size <= (1 << 20) else 5
         for name, fn in (("host_put_on_stream", lambda: lib.nvshmemx_putmem_on_stream(C.c_void_p(sym.data_ptr()), C.c_void_p(local.data_ptr()), size, right, stream_ptr())),
                          ("host_get_on_stream", lambda: lib.nvshmemx_getmem_on_stream(C.c_void_p(local.data_ptr()), C.c_void_p(sym.data_ptr()), size, right, stream_ptr()))):
             ms = env.time_ms(fn, iters=iters, warmup=2)
             env.record(test=name, bytes=size, us=round(ms * 1e3, 2), GBps=round(size / (ms * 1e-3) / 1e9, 2), npes=n)
+        if dev is not None:
+            # the same calls issued from a C loop (no interpreter between them), as the reference's host perftests do
+            for kind, name, d, sbuf in ((7, "host_put_on_stream", sym, local), (8, "host_get_on_stream", local, sym)):
+                reps = 50
+                ms = env.time_ms(lambda: ok(dev.perf_onstream_loop(kind, C.c_void_p(d.data_ptr()), C.c_void_p(sbuf.data_ptr()), size, right, reps, stream_ptr())), iters=3, warmup=1)
+                env.record(test=name, bytes=size, us=round(ms * 1e3 / reps, 2), GBps=round(size / (ms * 1e-3 / reps) / 1e9, 2), npes=n, issue="c-loop")
         t0 = time.perf_counter()
         for _ in range(iters):
             lib.nvshmem_putmem(C.c_void_p(sym.data_ptr()), C.c_void_p(local.data_ptr()), size, right)

@@ -186,3 +186,26 @@ def test_python_layer_imports_and_reports_version():
     import nvshmem_b200.core as nv
     v = nv.get_version()
     assert v["openshmem_spec_version"] == (1, 3) and v["libnvshmem_version"][0] == 3
+
+
+def test_local_buffer_registration_table():
+    """Sorted, non-overlapping table of registered local ranges (no GPU: bookkeeping only)."""
+    import ctypes as C
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    lib.nvshmemx_buffer_register.argtypes = [C.c_void_p, C.c_size_t]
+    lib.nvshmemx_buffer_unregister.argtypes = [C.c_void_p]
+    buf = C.create_string_buffer(1 << 16)
+    base = C.addressof(buf)
+    assert lib.nvshmemx_buffer_register(base + 4096, 8192) == 0
+    assert lib.nvshmemx_buffer_register(base + 4096, 8192) != 0          # registered twice
+    assert lib.nvshmemx_buffer_register(base + 8192, 4096) != 0          # inside a registered range
+    assert lib.nvshmemx_buffer_register(base, 4097) != 0                 # runs into the next range
+    assert lib.nvshmemx_buffer_register(base, 4096) == 0                 # adjacent below is fine
+    assert lib.nvshmemx_buffer_register(base + 12288, 4096) == 0         # adjacent above too
+    assert lib.nvshmemx_buffer_register(None, 16) != 0 and lib.nvshmemx_buffer_register(base + 32768, 0) != 0
+    assert lib.nvshmemx_buffer_unregister(base + 100) != 0               # not the start of a range
+    assert lib.nvshmemx_buffer_unregister(base + 4096) == 0
+    assert lib.nvshmemx_buffer_register(base + 6000, 100) == 0           # the hole can be used again
+    lib.nvshmemx_buffer_unregister_all()
+    assert lib.nvshmemx_buffer_unregister(base) != 0
