@@ -206,6 +206,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   r.init_status = INIT_IS_BOOTSTRAPPED;
   log_set_pe(r.mype);
   print_options_if_asked(r);
+  log_process_diagnostics();
 
   // ---- which back end
   int ndev = 0;

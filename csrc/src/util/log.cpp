@@ -1,5 +1,12 @@
 #include "log.h"
 
+#include <execinfo.h>
+#include <sched.h>
+#include <signal.h>
+#include <unistd.h>
+
+#include <string>
+
 #include <sys/syscall.h>
 #include <unistd.h>
 
@@ -109,6 +116,44 @@ void log_write(LogLevel lvl, uint32_t, const char* file, int line, const char* f
   else
     fprintf(out, "%s:%d:%ld [%d] NVSHMEM %s %s\n", g_host, (int)getpid(), (long)syscall(SYS_gettid), g_dev, tag, body);
   fflush(out);
+}
+
+static void segv_backtrace(int sig) {
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  const char msg[] = "bshmem: caught SIGSEGV, backtrace follows\n";
+  ssize_t ignored = write(STDERR_FILENO, msg, sizeof(msg) - 1);
+  (void)ignored;
+  backtrace_symbols_fd(frames, n, STDERR_FILENO);
+  signal(sig, SIG_DFL);  // the default action (core dump / termination) happens on return
+  raise(sig);
+}
+
+void log_process_diagnostics() {
+  if (log_level() < LOG_INFO) return;
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  if (sched_getaffinity(0, sizeof(set), &set) == 0) {
+    std::string list;
+    int run_start = -1;
+    for (int c = 0; c <= CPU_SETSIZE; ++c) {
+      const bool on = c < CPU_SETSIZE && CPU_ISSET(c, &set);
+      if (on && run_start < 0) run_start = c;
+      if (!on && run_start >= 0) {
+        if (!list.empty()) list += ",";
+        list += std::to_string(run_start);
+        if (c - 1 > run_start) list += "-" + std::to_string(c - 1);
+        run_start = -1;
+      }
+    }
+    INFO(SUB_INIT, "process %d may run on CPUs %s", (int)getpid(), list.c_str());
+  }
+  static bool installed = false;
+  if (!installed) {
+    installed = true;
+    struct sigaction old {};
+    if (sigaction(SIGSEGV, nullptr, &old) == 0 && old.sa_handler == SIG_DFL) signal(SIGSEGV, segv_backtrace);  // never replaces a handler the program set
+  }
 }
 
 }  // namespace bshmem

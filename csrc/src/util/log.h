@@ -28,6 +28,9 @@ enum LogSubsys : uint32_t {
 void log_init();                    // (re)reads the environment
 void log_set_device(int dev);       // shown in the [dev] field
 void log_set_pe(int pe);
+// With NVSHMEM_DEBUG at INFO or above: prints the CPUs this process may run on, and installs a SIGSEGV handler
+// that writes a backtrace to stderr before the default action takes over (reference: src/host/util/util.cpp:25-38,166).
+void log_process_diagnostics();
 int log_level();
 uint32_t log_mask();
 bool log_enabled(LogLevel lvl, uint32_t subsys);
