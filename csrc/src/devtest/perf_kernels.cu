@@ -173,12 +173,29 @@ __global__ void __launch_bounds__(1024) k_coll_latency(int kind, void* dst, cons
 }
 
 #define OK() (cudaGetLastError() == cudaSuccess ? 0 : 1)
+// Tile all-reduce / all-gather latency at block scope: `iters` collectives on a rows x cols fp32 tile of a
+// row-major matrix with `ld` columns (reference: perftest/device/tile/tile_allreduce_latency.cu, tile_allgather_latency.cu).
+__global__ void __launch_bounds__(1024) k_tile_latency(int kind, float* dst, float* src, int rows, int cols, int ld, int iters) {
+  using namespace nvshmemx;
+  auto lay = make_layout(make_shape(rows, cols), make_stride(ld, ConstInt<1>{}));
+  // all-gather: every PE's tile lands in its own slot of the destination
+  Tensor<float, decltype(lay)> s(src, lay), d(kind == 2 ? dst + (size_t)nvshmem_my_pe() * rows * ld : dst, lay);
+  auto start = make_shape(0, 0);
+  auto bound = make_shape(rows, ld);
+  for (int i = 0; i < iters; ++i) {
+    if (kind == 0) tile_sum_reduce_block<decltype(s), decltype(d), decltype(start), NVLS_ONE_SHOT_PULL_NBI>(NVSHMEM_TEAM_WORLD, s, d, start, bound, 0);
+    else if (kind == 1) tile_sum_reduce_block<decltype(s), decltype(d), decltype(start), NVLS_TWO_SHOT_PUSH_NBI>(NVSHMEM_TEAM_WORLD, s, d, start, bound, 0, 0);
+    else tile_allgather_block<decltype(s), decltype(d), decltype(start), NVLS_ONE_SHOT_PUSH_NBI>(NVSHMEM_TEAM_WORLD, s, d, start, bound, 0);
+    tile_collective_wait_block<NVLS_ONE_SHOT_PUSH_NBI>(NVSHMEM_TEAM_WORLD, 0);
+  }
+}
+
 extern "C" {
 int perf_preload(void) {
   cudaFuncAttributes a;
   const void* fns[] = {(const void*)k_bw, (const void*)k_pg_rate, (const void*)k_put_latency, (const void*)k_get_latency, (const void*)k_pingpong,
                        (const void*)k_signal_pingpong, (const void*)k_atomic_rate, (const void*)k_atomic_latency, (const void*)k_barrier_latency,
-                       (const void*)k_coll_latency};
+                       (const void*)k_coll_latency, (const void*)k_tile_latency};
   int bad = 0, i = 0;
   for (const void* f : fns) {
     cudaError_t e = cudaFuncGetAttributes(&a, f);
@@ -229,6 +246,10 @@ int perf_barrier_latency(int iters, int scope, int sync_only, int threads, cudaS
 }
 int perf_coll_latency(int kind, void* dst, const void* src, size_t n, int iters, int threads, cudaStream_t s) {
   k_coll_latency<<<1, threads, 0, s>>>(kind, dst, src, n, iters);
+  return OK();
+}
+int perf_tile_latency(int kind, float* dst, float* src, int rows, int cols, int ld, int iters, int threads, cudaStream_t s) {
+  k_tile_latency<<<1, threads, 0, s>>>(kind, dst, src, rows, cols, ld, iters);
   return OK();
 }
 // Issues `iters` on-stream calls of one kind back to back from C, the way the reference's host perftests do

@@ -25,7 +25,7 @@ from pathlib import Path
 LISTS = {
     # (driver module, arguments, PE counts it supports: None = any)
     "p2p": [("rma", ["--max-bytes", "256M"], (2,)), ("host", [], (2,))],
-    "coll": [("coll", ["--max-bytes", "128M", "--algos", "best"], None)],
+    "coll": [("coll", ["--max-bytes", "128M", "--algos", "best"], None), ("tile", [], None)],
     "coll-all-algos": [("coll", ["--max-bytes", "32M", "--algos", "all", "--cold"], None)],
     "fused": [("fused", [], None), ("moe", [], None)],
     "kernels": [("kernel_case", ["--kernel", k], (1,)) for k in ("gemm", "gemm_bench", "moe_dispatch", "moe_dispatch_fp8", "moe_combine", "allreduce")],
