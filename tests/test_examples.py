@@ -69,3 +69,15 @@ def test_launcher_times_out():
     from nvshmem_b200.launch import launch
     status, _ = launch(2, [sys.executable, "-c", "import time; time.sleep(60)"], timeout=1.5, capture=True)
     assert status == 124
+
+
+def test_host_plumbing_benchmark_runs_without_a_gpu():
+    """Config (a): bootstrap, host-heap bring-up, the seeded 64-call allocation sequence, barriers, a team."""
+    import json
+    import sys
+    from nvshmem_b200.launch import launch
+    status, outs = launch(2, [sys.executable, "-m", "perftest.plumbing"], timeout=120, capture=True,
+                          env_extra={"NVSHMEM_HEAP_BACKEND": "HOST", "PYTHONPATH": str(ROOT)})
+    assert status == 0, outs
+    row = json.loads([l for l in "".join(outs).splitlines() if l.startswith("{")][0])
+    assert row["offsets_identical"] is True and row["npes"] == 2 and row["team_status"] == 0
