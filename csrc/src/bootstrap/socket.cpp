@@ -252,8 +252,9 @@ int sock_accept(int listen_fd, uint64_t magic, int timeout_ms, int* fd_out, cons
     uint64_t got = 0;
     int st = sock_recv(fd, &got, sizeof(got), (int)std::max<int64_t>(1, std::min<int64_t>(deadline - now_ms(), 5000)));
     if (st != SOCK_OK || got != magic) {
+      // Not one of ours: wrong number, or a connection that closed or stayed silent before sending one.
       close(fd);
-      return st == SOCK_OK ? SOCK_BAD_MAGIC : st;
+      return SOCK_BAD_MAGIC;
     }
     *fd_out = fd;
     return SOCK_OK;

@@ -81,3 +81,12 @@ def test_host_plumbing_benchmark_runs_without_a_gpu():
     assert status == 0, outs
     row = json.loads([l for l in "".join(outs).splitlines() if l.startswith("{")][0])
     assert row["offsets_identical"] is True and row["npes"] == 2 and row["team_status"] == 0
+
+
+def test_stray_connections_do_not_disturb_the_bootstrap():
+    import sys
+    from nvshmem_b200.launch import launch
+    status, outs = launch(3, [sys.executable, str(ROOT / "tests" / "stray_child.py")], timeout=120, capture=True,
+                          env_extra={"NVSHMEM_HEAP_BACKEND": "HOST", "NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "30000"})
+    assert status == 0, outs
+    assert "bootstrap survived the strays" in "".join(outs)
