@@ -209,3 +209,26 @@ def test_local_buffer_registration_table():
     assert lib.nvshmemx_buffer_register(base + 6000, 100) == 0           # the hole can be used again
     lib.nvshmemx_buffer_unregister_all()
     assert lib.nvshmemx_buffer_unregister(base) != 0
+
+
+def test_unique_id_with_a_foreign_version_is_refused():
+    """An id made by another ABI version (or a corrupted one) is rejected before any connection is attempted."""
+    import ctypes as C
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    uid = H.UniqueId()
+    assert lib.nvshmemx_get_uniqueid(C.byref(uid)) == 0
+    good_version = uid.version
+    assert good_version == (1 << 16) + 128
+    uid.version = good_version + (1 << 16)
+    lib.bshmem_test_boot_init.restype = C.c_void_p
+    lib.bshmem_test_boot_strerror.restype = C.c_char_p
+    st = C.c_int(0)
+    h = lib.bshmem_test_boot_init(C.byref(uid), 0, 1, C.byref(st))
+    assert not h and st.value == 3, st.value  # BOOT_ERR_VERSION
+    assert b"version" in lib.bshmem_test_boot_strerror(st.value)
+    # the untouched id still works for a job of one
+    uid.version = good_version
+    h = lib.bshmem_test_boot_init(C.byref(uid), 0, 1, C.byref(st))
+    assert h and st.value == 0
+    lib.bshmem_test_boot_finalize(C.c_void_p(h))
