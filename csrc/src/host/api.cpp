@@ -812,6 +812,7 @@ uint64_t nvshmemx_b200_heap_info(int what) {
     case 5: return r.heap->allocator().bytes_in_use();
     case 6: return r.heap->allocator().history_digest();
     case 7: return r.have_gpu ? 1 : 0;
+    case 8: return (uint64_t)(int64_t)r.device;  // CUDA device of this PE (-1 on the host back end)
     default: return 0;
   }
 }

@@ -118,7 +118,8 @@ class NvshmemResource:
 
     @property
     def device_id(self) -> int:
-        return int(H.load().nvshmemx_b200_heap_info(6))
+        dev = int(H.load().nvshmemx_b200_heap_info(8))
+        return dev - (1 << 64) if dev >= (1 << 63) else dev  # -1 on the host-memory back end
 
 
 def module_finalize(mod) -> None:
