@@ -35,3 +35,9 @@ def test_root_drops_a_registration_everyone_times_out():
 
 def test_rank_that_never_joins_gives_error_status():
     run_workers("rank_never_joins", 3, env={"NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "1500"}, timeout=120)
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_python_layer_on_host_heap(n):
+    run_workers("python_layer_on_host_heap", n)
+

@@ -55,6 +55,62 @@ def gather_objects(obj):
 
 # ====================================================================== host-only (also valid on GPU)
 @worker
+def python_layer_on_host_heap():
+    """The nvshmem4py-style layer end to end with no GPU: symmetric tensors over the host-memory heap, put / get /
+    put-with-signal on a 'stream' (immediate on this back end), peer views, teams, tracked frees."""
+    nv = setup()
+    n, me = nv.n_pes(), nv.my_pe()
+    assert n == WORLD and me == RANK and nv.init_status() >= 2 and nv.is_initialized()
+    assert nv.team_my_pe(nv.Teams.TEAM_WORLD) == me and nv.team_n_pes(nv.Teams.TEAM_WORLD) == n
+    right, left = (me + 1) % n, (me - 1) % n
+    t = nv.tensor((4, 16), torch.float32, zero=True)
+    assert tuple(t.shape) == (4, 16) and t.dtype == torch.float32 and float(t.abs().sum()) == 0.0
+    src = torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me
+    nv.barrier_all() if GPU else H_barrier()
+    nv.put(t, src, right)
+    H_barrier()
+    assert torch.equal(t, torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * left)
+    back = torch.empty(4, 16, dtype=torch.float32)
+    nv.get(back, t, right)
+    assert torch.equal(back, torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me)  # what I wrote there
+    # put with signal: the signal word on the target counts arrivals
+    sig = nv.tensor((1,), torch.int64, zero=True)
+    H_barrier()
+    nv.put_signal(t, src * 2, sig, 5, nv.SignalOp.SIGNAL_ADD, right)
+    H_barrier()
+    assert nv.signal_fetch(sig) == 5 and torch.equal(t, (torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * left) * 2)
+    nv.signal_op(sig, 9, nv.SignalOp.SIGNAL_SET, right)
+    H_barrier()
+    assert nv.signal_fetch(sig) == 9
+    # a peer view aliases the neighbour's memory (process-shared mapping on this back end)
+    peer = nv.get_peer_tensor(t, right)
+    assert torch.equal(peer, (torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me) * 2)
+    # teams through the Python layer
+    if n >= 2:
+        evens = nv.team_split_strided(nv.Teams.TEAM_WORLD, 0, 2, (n + 1) // 2)
+        if me % 2 == 0:
+            assert nv.team_my_pe(evens) == me // 2 and nv.team_n_pes(evens) == (n + 1) // 2
+            assert nv.team_translate_pe(evens, nv.team_my_pe(evens), nv.Teams.TEAM_WORLD) == me
+            nv.team_destroy(evens)
+        else:
+            assert evens == -1 or nv.team_my_pe(evens) == -1
+    # helpers of the compatibility module
+    assert nv.get_size((4, 16), torch.float32) == 256 and nv.tensor_get_buffer(t).size >= 256
+    assert nv.NvshmemResource().device_id == (int(os.environ["LOCAL_RANK"]) if GPU else -1)
+    H_barrier()
+    nv.free_tensor(sig)
+    nv.free_tensor(t)
+    teardown(nv)
+
+
+def H_barrier():
+    from nvshmem_b200.bindings import host as H
+    if GPU:
+        torch.cuda.synchronize()
+    H.load().nvshmem_barrier_all()
+
+
+@worker
 def alloc_symmetry():
     """Seeded 64-call malloc/align/free sequence: every PE must see identical offsets."""
     nv = setup()
