@@ -145,6 +145,9 @@ static int ctas_for(size_t bytes, size_t threshold) {
   return clamp_ctas(32);
 }
 
+// Host-memory heap (no GPU): the data collectives run on the CPU, at once ("on stream" has no meaning there).
+static bool host_mode() { return is_initialized() && !rt().have_gpu; }
+
 static int check_team(int team, const char* what) {
   Runtime& r = rt();
   if (!is_initialized()) {
@@ -172,6 +175,7 @@ static int launch_status(const char* what) {
 }
 
 int coll_reduce_on_stream(int team, void* dst, const void* src, size_t n, int dtype, int op, cudaStream_t stream, int algo) {
+  if (host_mode()) return n ? emul_reduce(team, dst, src, n, dtype, op) : ST_SUCCESS;
   NvtxRange nvtx(NVTX_COLL, "reduce_on_stream");
   int st = check_team(team, "reduce");
   if (st) return st;
@@ -186,6 +190,7 @@ int coll_reduce_on_stream(int team, void* dst, const void* src, size_t n, int dt
 }
 
 int coll_reducescatter_on_stream(int team, void* dst, const void* src, size_t nreduce, int dtype, int op, cudaStream_t stream, int algo) {
+  if (host_mode()) return nreduce ? emul_reducescatter(team, dst, src, nreduce, dtype, op) : ST_SUCCESS;
   NvtxRange nvtx(NVTX_COLL, "reducescatter_on_stream");
   int st = check_team(team, "reducescatter");
   if (st) return st;
@@ -242,6 +247,7 @@ static int ce_broadcast(Team* t, void* dst, const void* src, size_t bytes, int r
 }
 
 int coll_fcollect_on_stream(int team, void* dst, const void* src, size_t block_bytes, cudaStream_t stream, int algo) {
+  if (host_mode()) return block_bytes ? emul_fcollect(team, dst, src, block_bytes) : ST_SUCCESS;
   NvtxRange nvtx(NVTX_COLL, "fcollect_on_stream");
   int st = check_team(team, "fcollect");
   if (st) return st;
@@ -258,6 +264,7 @@ int coll_fcollect_on_stream(int team, void* dst, const void* src, size_t block_b
 }
 
 int coll_alltoall_on_stream(int team, void* dst, const void* src, size_t block_bytes, cudaStream_t stream) {
+  if (host_mode()) return block_bytes ? emul_alltoall(team, dst, src, block_bytes) : ST_SUCCESS;
   NvtxRange nvtx(NVTX_COLL, "alltoall_on_stream");
   int st = check_team(team, "alltoall");
   if (st) return st;
@@ -273,6 +280,7 @@ int coll_alltoall_on_stream(int team, void* dst, const void* src, size_t block_b
 }
 
 int coll_broadcast_on_stream(int team, void* dst, const void* src, size_t bytes, int root, cudaStream_t stream, int algo) {
+  if (host_mode()) return bytes ? emul_broadcast(team, dst, src, bytes, root) : ST_SUCCESS;
   NvtxRange nvtx(NVTX_COLL, "broadcast_on_stream");
   int st = check_team(team, "broadcast");
   if (st) return st;

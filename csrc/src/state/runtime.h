@@ -141,6 +141,12 @@ int host_barrier_all_blocking();
 // CPU implementations over the host-memory heap (host_emul.cpp)
 int emul_team_sync(int team);
 int emul_allreduce_and_u64(int team, uint64_t* data, int words);
+// CPU versions of the data collectives (host_emul_coll.cpp); dtype / op as in the device code
+int emul_reduce(int team, void* dst, const void* src, size_t n, int dtype, int op);
+int emul_reducescatter(int team, void* dst, const void* src, size_t nreduce, int dtype, int op);
+int emul_fcollect(int team, void* dst, const void* src, size_t block_bytes);
+int emul_alltoall(int team, void* dst, const void* src, size_t block_bytes);
+int emul_broadcast(int team, void* dst, const void* src, size_t bytes, int root);
 
 }  // namespace bshmem
 

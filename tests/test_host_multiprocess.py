@@ -41,3 +41,8 @@ def test_rank_that_never_joins_gives_error_status():
 def test_python_layer_on_host_heap(n):
     run_workers("python_layer_on_host_heap", n)
 
+
+@pytest.mark.parametrize("n", [2, 3, 4])
+def test_collectives_on_host_heap(n):
+    run_workers("collectives_on_host_heap", n)
+

@@ -103,6 +103,113 @@ def python_layer_on_host_heap():
     teardown(nv)
 
 
+@worker
+def collectives_on_host_heap():
+    """The data collectives of the Python layer with no GPU (CPU versions over the host-memory heap) against a
+    local oracle: every rank can regenerate every rank's input from its seed."""
+    nv = setup()
+    n, me = nv.n_pes(), nv.my_pe()
+
+    def data(rank, count, dtype):
+        g = torch.Generator().manual_seed(1000 + 17 * rank + count)
+        if dtype.is_floating_point:
+            return (torch.rand(count, generator=g) * 2 - 0.5).to(dtype)
+        return torch.randint(1, 90, (count,), generator=g).to(dtype)
+
+    def oracle(op, stacked, dtype):
+        acc = stacked.double() if dtype.is_floating_point else stacked.long()
+        if op == "sum":
+            out = acc.sum(0)
+        elif op == "prod":
+            out = acc.prod(0)
+        elif op == "min":
+            out = acc.min(0).values
+        elif op == "max":
+            out = acc.max(0).values
+        else:
+            out = acc[0]
+            for k in range(1, acc.shape[0]):
+                out = {"and": out & acc[k], "or": out | acc[k], "xor": out ^ acc[k]}[op]
+        return out
+
+    cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.float64, "min"), (torch.int32, "sum"), (torch.int64, "xor"),
+             (torch.uint8, "and"), (torch.int16, "or"), (torch.float32, "prod")]
+    for dtype, op in cases:
+        for count in (1, 7, 256, 4099):
+            if op == "prod" and count > 256:
+                continue
+            src, dst = nv.tensor((count,), dtype), nv.tensor((count,), dtype)
+            src.copy_(data(me, count, dtype))
+            want = oracle(op, torch.stack([data(r, count, dtype) for r in range(n)]), dtype)
+            nv.reduce(nv.Teams.TEAM_WORLD, dst, src, op)
+            if dtype.is_floating_point:
+                tol = {torch.bfloat16: 2 ** -6, torch.float16: 2 ** -9}.get(dtype, 1e-5) * max(1.0, float(want.abs().max()))
+                assert float((dst.double() - want).abs().max()) <= tol, ("reduce", dtype, op, count)
+            else:
+                assert torch.equal(dst.long(), want.to(dtype).long()), ("reduce", dtype, op, count)
+            work = nv.tensor((count,), dtype)
+            work.copy_(data(me, count, dtype))
+            nv.reduce(nv.Teams.TEAM_WORLD, work, work, op)  # in place
+            assert torch.equal(work, dst), ("reduce in place", dtype, op, count)
+            for t in (src, dst, work):
+                nv.free_tensor(t)
+    for dtype in (torch.float32, torch.int32, torch.bfloat16):
+        for blk in (1, 5, 300):
+            full = nv.tensor((blk * n,), dtype)
+            part = nv.tensor((blk,), dtype)
+            gathered = nv.tensor((blk * n,), dtype, zero=True)
+            mine = data(me, blk * n, dtype)
+            full.copy_(mine)
+            # reducescatter: my block of the element-wise sum
+            nv.reducescatter(nv.Teams.TEAM_WORLD, part, full, "sum")
+            want = oracle("sum", torch.stack([data(r, blk * n, dtype) for r in range(n)]), dtype)[me * blk:(me + 1) * blk]
+            tol = 2 ** -6 * max(1.0, float(want.abs().max())) if dtype == torch.bfloat16 else 1e-5 * max(1.0, float(want.abs().max()))
+            assert float((part.double() - want.double()).abs().max()) <= tol, ("reducescatter", dtype, blk)
+            # fcollect: everyone's first block, in rank order
+            nv.fcollect(nv.Teams.TEAM_WORLD, gathered, full[:blk])
+            assert torch.equal(gathered, torch.cat([data(r, blk * n, dtype)[:blk] for r in range(n)])), ("fcollect", dtype, blk)
+            # alltoall: block me of every rank's buffer
+            H_barrier()
+            nv.alltoall(nv.Teams.TEAM_WORLD, gathered, full)
+            assert torch.equal(gathered, torch.cat([data(r, blk * n, dtype)[me * blk:(me + 1) * blk] for r in range(n)])), ("alltoall", dtype, blk)
+            # broadcast from the last rank
+            H_barrier()
+            nv.broadcast(nv.Teams.TEAM_WORLD, gathered, full, root=n - 1)
+            assert torch.equal(gathered, data(n - 1, blk * n, dtype)), ("broadcast", dtype, blk)
+            H_barrier()
+            for t in (full, part, gathered):
+                nv.free_tensor(t)
+    # a sub-team: the even ranks reduce among themselves
+    if n >= 3:
+        evens = nv.team_split_strided(nv.Teams.TEAM_WORLD, 0, 2, (n + 1) // 2)
+        v = nv.tensor((8,), torch.float32)
+        out = nv.tensor((8,), torch.float32)
+        v.fill_(float(me + 1))
+        H_barrier()
+        if me % 2 == 0:
+            nv.reduce(evens, out, v, "sum")
+            assert float(out[0]) == float(sum(r + 1 for r in range(0, n, 2)))
+            nv.team_destroy(evens)
+        H_barrier()
+        nv.free_tensor(v)
+        nv.free_tensor(out)
+    # the typed C entry points (blocking and "on stream") reach the same CPU code
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    a32, b32 = nv.tensor((5,), torch.int32), nv.tensor((5,), torch.int32)
+    a32.copy_(torch.arange(5, dtype=torch.int32) + me)
+    H_barrier()
+    assert lib.nvshmem_int_sum_reduce(0, C.c_void_p(b32.data_ptr()), C.c_void_p(a32.data_ptr()), C.c_size_t(5)) == 0
+    assert b32.tolist() == [n * k + n * (n - 1) // 2 for k in range(5)]
+    assert lib.nvshmemx_int_max_reduce_on_stream(0, C.c_void_p(b32.data_ptr()), C.c_void_p(a32.data_ptr()), C.c_size_t(5), None) == 0
+    assert b32.tolist() == [k + n - 1 for k in range(5)]
+    H_barrier()
+    nv.free_tensor(a32)
+    nv.free_tensor(b32)
+    assert nv.error_bits() == 0
+    teardown(nv)
+
+
 def H_barrier():
     from nvshmem_b200.bindings import host as H
     if GPU:
