@@ -6,6 +6,8 @@
 //  src/host/comm/putget.cpp, sync.cpp, quiet.cpp, src/host/coll/**, src/host/team/team.cu)
 #include <string.h>
 
+#include <sched.h>
+#include <time.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -116,7 +118,47 @@ void signal_on_stream(uint64_t* sig, uint64_t value, int op, int pe, cudaStream_
 
 void wait_on_stream(const void* ivar, int cmp, uint64_t value, int width, bool is_signed, cudaStream_t stream) {
   Runtime& r = rt();
-  if (!r.have_gpu) return;
+  if (!r.have_gpu) {
+    // Host-memory heap: the "stream" is the calling thread, which polls the word itself, with the same bound
+    // as every other wait; a wait that runs out sets the time-out bit instead of blocking for ever.
+    auto read = [&]() -> int64_t {
+      switch (width) {
+        case 8: return (int64_t)__atomic_load_n((const uint64_t*)ivar, __ATOMIC_ACQUIRE);
+        case 4: return is_signed ? (int64_t)__atomic_load_n((const int32_t*)ivar, __ATOMIC_ACQUIRE) : (int64_t)__atomic_load_n((const uint32_t*)ivar, __ATOMIC_ACQUIRE);
+        default: return is_signed ? (int64_t)__atomic_load_n((const int16_t*)ivar, __ATOMIC_ACQUIRE) : (int64_t)__atomic_load_n((const uint16_t*)ivar, __ATOMIC_ACQUIRE);
+      }
+    };
+    auto holds = [&](int64_t v) {
+      const bool u = width == 8 && !is_signed;  // full-width unsigned values compare as unsigned
+      const uint64_t a = (uint64_t)v, b = value;
+      const int64_t sb = (int64_t)value;
+      switch (cmp) {
+        case NVSHMEM_CMP_EQ: return a == b;
+        case NVSHMEM_CMP_NE: return a != b;
+        case NVSHMEM_CMP_GT: return u ? a > b : v > sb;
+        case NVSHMEM_CMP_GE: return u ? a >= b : v >= sb;
+        case NVSHMEM_CMP_LT: return u ? a < b : v < sb;
+        case NVSHMEM_CMP_LE: return u ? a <= b : v <= sb;
+        default: return true;
+      }
+    };
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    const long limit_ms = (long)(r.dstate.wait_timeout_ns / 1000000ull);  // follows nvshmemx_b200_set_wait_timeout_ms
+    for (unsigned spins = 0; !holds(read()); ++spins) {
+      if ((spins & 1023) == 1023) {
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        if ((t1.tv_sec - t0.tv_sec) * 1000 + (t1.tv_nsec - t0.tv_nsec) / 1000000 > limit_ms) {
+          if (r.status_host) r.status_host->error_bits |= BSHMEM_ERR_WAIT_TIMEOUT;
+          ERROR_PRINT("wait on %p timed out after %ld ms", ivar, limit_ms);
+          return;
+        }
+        sched_yield();
+      }
+    }
+    return;
+  }
   const CuTable* d = cu();
   if (width == 8 && !is_signed && r.topo.stream_memops && d && d->cuStreamWaitValue64_ && (cmp == NVSHMEM_CMP_GE || cmp == NVSHMEM_CMP_EQ)) {
     unsigned flags = (cmp == NVSHMEM_CMP_GE ? CU_STREAM_WAIT_VALUE_GEQ : CU_STREAM_WAIT_VALUE_EQ) | CU_STREAM_WAIT_VALUE_FLUSH;

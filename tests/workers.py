@@ -82,6 +82,22 @@ def python_layer_on_host_heap():
     nv.signal_op(sig, 9, nv.SignalOp.SIGNAL_SET, right)
     H_barrier()
     assert nv.signal_fetch(sig) == 9
+    # signal_wait really waits on this back end: the left neighbour raises my signal after a delay
+    import time
+    if me % 2 == 1 or n == 1:
+        time.sleep(0.3)
+    nv.signal_op(sig, 20, nv.SignalOp.SIGNAL_SET, right)
+    nv.signal_wait(sig, 20, nv.ComparisonType.CMP_GE)
+    assert nv.signal_fetch(sig) == 20 and nv.error_bits() == 0
+    H_barrier()
+    # a signal that nobody sends: the wait gives up after the bound and reports it
+    nv.set_wait_timeout_ms(200)
+    t0 = time.time()
+    nv.signal_wait(sig, 1000, nv.ComparisonType.CMP_EQ)
+    assert 0.15 < time.time() - t0 < 5.0 and nv.error_bits() & 1, nv.error_bits()
+    nv.clear_errors()
+    nv.set_wait_timeout_ms(5000)
+    H_barrier()
     # a peer view aliases the neighbour's memory (process-shared mapping on this back end)
     peer = nv.get_peer_tensor(t, right)
     assert torch.equal(peer, (torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me) * 2)
