@@ -46,3 +46,7 @@ def test_python_layer_on_host_heap(n):
 def test_collectives_on_host_heap(n):
     run_workers("collectives_on_host_heap", n)
 
+
+def test_typed_host_api_all_types():
+    run_workers("typed_host_api_all_types", 3)
+

@@ -226,6 +226,83 @@ def collectives_on_host_heap():
     teardown(nv)
 
 
+@worker
+def typed_host_api_all_types():
+    """Every RMA type name of the API through its host entry points (p, g, put, get, iput, iget, put_nbi + quiet) on the
+    host-memory heap: checks the generated type tables (names, element sizes, strides), not the transport."""
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    n, me = nv.n_pes(), nv.my_pe()
+    right, left = (me + 1) % n, (me - 1) % n
+    types = {"char": C.c_char, "schar": C.c_byte, "short": C.c_short, "int": C.c_int, "long": C.c_long, "longlong": C.c_longlong, "uchar": C.c_ubyte,
+             "ushort": C.c_ushort, "uint": C.c_uint, "ulong": C.c_ulong, "ulonglong": C.c_ulonglong, "int8": C.c_int8, "int16": C.c_int16, "int32": C.c_int32,
+             "int64": C.c_int64, "uint8": C.c_uint8, "uint16": C.c_uint16, "uint32": C.c_uint32, "uint64": C.c_uint64, "size": C.c_size_t, "ptrdiff": C.c_ssize_t,
+             "float": C.c_float, "double": C.c_double, "half": C.c_uint16, "bfloat16": C.c_uint16}
+    lib.nvshmem_malloc.restype = C.c_void_p
+    for name, ct in types.items():
+        es = C.sizeof(ct)
+        count = 12
+        sym = lib.nvshmem_calloc(2 * count, es)
+        assert sym
+        Arr = ct * count
+        raw16 = name in ("half", "bfloat16")  # passed through as bit patterns
+        def val(rank, k):
+            v = (rank * 13 + k * 3 + 1) % 100
+            return bytes([v]) if name == "char" else (float(v) if name in ("float", "double") else v)
+        mine = Arr(*[val(me, k) for k in range(count)])
+        # put to the right neighbour's first half; get it back
+        getattr(lib, f"nvshmem_{name}_put")(C.c_void_p(sym), mine, C.c_size_t(count), right)
+        lib.nvshmem_barrier_all()
+        local = (ct * (2 * count)).from_address(sym)
+        assert [local[k] for k in range(count)] == [val(left, k) for k in range(count)], (name, "put")
+        back = Arr()
+        getattr(lib, f"nvshmem_{name}_get")(back, C.c_void_p(sym), C.c_size_t(count), right)
+        assert list(back) == [val(me, k) for k in range(count)], (name, "get")
+        # strided: every second element of mine into every third slot of the right neighbour's second half
+        lib.nvshmem_barrier_all()
+        fn = getattr(lib, f"nvshmem_{name}_iput")
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_ssize_t, C.c_ssize_t, C.c_size_t, C.c_int]
+        fn(C.c_void_p(sym + count * es), mine, 3, 2, 4, right)
+        lib.nvshmem_barrier_all()
+        assert [local[count + 3 * k] for k in range(4)] == [val(left, 2 * k) for k in range(4)], (name, "iput")
+        got = (ct * 4)()
+        fn = getattr(lib, f"nvshmem_{name}_iget")
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_ssize_t, C.c_ssize_t, C.c_size_t, C.c_int]
+        fn(got, C.c_void_p(sym + count * es), 1, 3, 4, right)
+        assert list(got) == [val(me, 2 * k) for k in range(4)], (name, "iget")
+        # non-blocking put + quiet, and the scalar forms (not for the 16-bit floating types, whose scalars are structs)
+        lib.nvshmem_barrier_all()
+        getattr(lib, f"nvshmem_{name}_put_nbi")(C.c_void_p(sym), mine, C.c_size_t(count), left)
+        lib.nvshmem_quiet()
+        lib.nvshmem_barrier_all()
+        assert [local[k] for k in range(count)] == [val(right, k) for k in range(count)], (name, "put_nbi")
+        if not raw16:
+            p, g = getattr(lib, f"nvshmem_{name}_p"), getattr(lib, f"nvshmem_{name}_g")
+            p.argtypes, g.argtypes, g.restype = [C.c_void_p, ct, C.c_int], [C.c_void_p, C.c_int], ct
+            lib.nvshmem_barrier_all()
+            p(C.c_void_p(sym), val(me, 5), right)
+            lib.nvshmem_barrier_all()
+            assert local[0] == val(left, 5), (name, "p")
+            assert g(C.c_void_p(sym), right) == val(me, 5), (name, "g")
+        lib.nvshmem_barrier_all()
+        lib.nvshmem_free(C.c_void_p(sym))
+    # sized forms: 8 .. 128 bits
+    for bits in (8, 16, 32, 64, 128):
+        es, count = bits // 8, 6
+        sym = lib.nvshmem_calloc(count, es)
+        src = bytes([(me * 31 + k) % 251 for k in range(count * es)])
+        getattr(lib, f"nvshmem_put{bits}")(C.c_void_p(sym), src, C.c_size_t(count), right)
+        lib.nvshmem_barrier_all()
+        assert C.string_at(sym, count * es) == bytes([(left * 31 + k) % 251 for k in range(count * es)]), bits
+        back = C.create_string_buffer(count * es)
+        getattr(lib, f"nvshmem_get{bits}")(back, C.c_void_p(sym), C.c_size_t(count), right)
+        assert back.raw == src, bits
+        lib.nvshmem_barrier_all()
+        lib.nvshmem_free(C.c_void_p(sym))
+    teardown(nv)
+
+
 def H_barrier():
     from nvshmem_b200.bindings import host as H
     if GPU:
