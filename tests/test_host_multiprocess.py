@@ -50,3 +50,7 @@ def test_collectives_on_host_heap(n):
 def test_typed_host_api_all_types():
     run_workers("typed_host_api_all_types", 3)
 
+
+def test_host_atomics_all_types():
+    run_workers("host_atomics_all_types", 4)
+

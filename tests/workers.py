@@ -303,6 +303,85 @@ def typed_host_api_all_types():
     teardown(nv)
 
 
+@worker
+def host_atomics_all_types():
+    """Every atomic of the API for every type class through the host entry points: all PEs hammer one word on PE 0
+    (add / inc / fetch forms must not lose updates), then bitwise and exchange forms with known outcomes."""
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    n, me = nv.n_pes(), nv.my_pe()
+    bitwise = {"uint": C.c_uint, "ulong": C.c_ulong, "ulonglong": C.c_ulonglong, "int32": C.c_int32, "uint32": C.c_uint32, "int64": C.c_int64, "uint64": C.c_uint64}
+    standard = dict(bitwise, int=C.c_int, long=C.c_long, longlong=C.c_longlong, size=C.c_size_t, ptrdiff=C.c_ssize_t)
+    extended = dict(standard, float=C.c_float, double=C.c_double)
+    lib.nvshmem_calloc.restype = C.c_void_p
+
+    def fn(name, res, *args):
+        f = getattr(lib, name)
+        f.restype, f.argtypes = res, list(args)
+        return f
+
+    for tname, ct in standard.items():
+        word = lib.nvshmem_calloc(2, 8)
+        tgt = C.c_void_p(word)
+        iters = 25
+        lib.nvshmem_barrier_all()
+        seen = set()
+        for _ in range(iters):
+            fn(f"nvshmem_{tname}_atomic_inc", None, C.c_void_p, C.c_int)(tgt, 0)
+            fn(f"nvshmem_{tname}_atomic_add", None, C.c_void_p, ct, C.c_int)(tgt, 2, 0)
+            seen.add(fn(f"nvshmem_{tname}_atomic_fetch_inc", ct, C.c_void_p, C.c_int)(tgt, 0))
+            seen.add(fn(f"nvshmem_{tname}_atomic_fetch_add", ct, C.c_void_p, ct, C.c_int)(tgt, 3, 0))
+        lib.nvshmem_barrier_all()
+        total = fn(f"nvshmem_{tname}_atomic_fetch", ct, C.c_void_p, C.c_int)(tgt, 0)
+        assert total == n * iters * 7, (tname, total)
+        assert len(seen) == 2 * iters, (tname, "fetch forms returned a value twice")  # every fetched value is a distinct moment
+        # compare-and-swap: exactly one PE wins the race from the known value
+        lib.nvshmem_barrier_all()
+        old = fn(f"nvshmem_{tname}_atomic_compare_swap", ct, C.c_void_p, ct, ct, C.c_int)(tgt, n * iters * 7, 1000 + me, 0)
+        winners = gather_objects(old == n * iters * 7)
+        assert sum(winners) == 1, (tname, winners)
+        lib.nvshmem_barrier_all()
+        lib.nvshmem_free(tgt)
+    for tname, ct in extended.items():
+        word = lib.nvshmem_calloc(2, 8)
+        tgt = C.c_void_p(word)
+        lib.nvshmem_barrier_all()
+        fn(f"nvshmem_{tname}_atomic_set", None, C.c_void_p, ct, C.c_int)(tgt, 40 + me, (me + 1) % n)
+        lib.nvshmem_barrier_all()
+        left = (me - 1) % n
+        assert fn(f"nvshmem_{tname}_atomic_fetch", ct, C.c_void_p, C.c_int)(tgt, me) == 40 + left, tname
+        prev = fn(f"nvshmem_{tname}_atomic_swap", ct, C.c_void_p, ct, C.c_int)(tgt, 90 + me, me)
+        assert prev == 40 + left, tname
+        lib.nvshmem_barrier_all()
+        lib.nvshmem_free(tgt)
+    for tname, ct in bitwise.items():
+        word = lib.nvshmem_calloc(2, 8)
+        tgt = C.c_void_p(word)
+        lib.nvshmem_barrier_all()
+        fn(f"nvshmem_{tname}_atomic_or", None, C.c_void_p, ct, C.c_int)(tgt, 1 << me, 0)       # every PE sets its bit on PE 0
+        lib.nvshmem_barrier_all()
+        allbits = (1 << n) - 1
+        assert fn(f"nvshmem_{tname}_atomic_fetch", ct, C.c_void_p, C.c_int)(tgt, 0) == allbits, tname
+        lib.nvshmem_barrier_all()
+        before = fn(f"nvshmem_{tname}_atomic_fetch_xor", ct, C.c_void_p, ct, C.c_int)(tgt, 1 << me, 0)  # and clears it again
+        assert before & (1 << me), tname
+        lib.nvshmem_barrier_all()
+        assert fn(f"nvshmem_{tname}_atomic_fetch", ct, C.c_void_p, C.c_int)(tgt, 0) == 0, tname
+        lib.nvshmem_barrier_all()
+        if me == 0:
+            fn(f"nvshmem_{tname}_atomic_set", None, C.c_void_p, ct, C.c_int)(tgt, 0xFF, 0)
+        lib.nvshmem_barrier_all()
+        fn(f"nvshmem_{tname}_atomic_and", None, C.c_void_p, ct, C.c_int)(tgt, 0xFF ^ (1 << me), 0)
+        lib.nvshmem_barrier_all()
+        assert fn(f"nvshmem_{tname}_atomic_fetch_and", ct, C.c_void_p, ct, C.c_int)(tgt, 0xFF, 0) == 0xFF ^ allbits, tname
+        got = fn(f"nvshmem_{tname}_atomic_fetch_or", ct, C.c_void_p, ct, C.c_int)(tgt, 0, 0)
+        assert got == 0xFF ^ allbits, tname
+        lib.nvshmem_barrier_all()
+        lib.nvshmem_free(tgt)
+    teardown(nv)
+
+
 def H_barrier():
     from nvshmem_b200.bindings import host as H
     if GPU:
