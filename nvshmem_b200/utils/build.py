@@ -104,15 +104,26 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
         ex_libs = ["-L", str(LIB), "-lbshmem_host", "-lcuda", "-Xlinker", "-rpath=$ORIGIN/../../nvshmem_b200/lib"]
         for src in sorted((ROOT / "examples").glob("*.cu")) + sorted((ROOT / "examples").glob("*.cpp")):
             groups["example:" + src.stem] = ([src], ROOT / "examples" / "bin" / src.stem, False, ex_libs)
-    for name, (srcs, out, shared, libs) in groups.items():
-        if only and name != only and not (only == "examples" and name.startswith("example:")):
-            continue
-        if not srcs:
-            continue
+    def wanted(name: str) -> bool:
+        return not only or name == only or (only == "examples" and name.startswith("example:"))
+
+    def build_group(item):
+        name, (srcs, out, shared, libs) = item
         with ThreadPoolExecutor(jobs) as ex:
             objs = list(ex.map(lambda s: _compile(s, [], verbose, hdr), srcs))
         _link(objs, out, shared, libs)
-        built[name] = out
+        return name, out
+
+    # The libraries in order (later ones link against the host library), then the one-file example programs side by side.
+    for item in groups.items():
+        if wanted(item[0]) and item[1][0] and not item[0].startswith("example:"):
+            name, out = build_group(item)
+            built[name] = out
+    examples = [item for item in groups.items() if item[0].startswith("example:") and wanted(item[0])]
+    if examples:
+        with ThreadPoolExecutor(jobs) as ex:
+            for name, out in ex.map(build_group, examples):
+                built[name] = out
     return built
 
 
