@@ -24,8 +24,10 @@ bool parse_size(const char* text, size_t* out) {
     case 't': case 'T': mult = 1024.0 * 1024 * 1024 * 1024; break;
     default: return false;
   }
-  // Characters after the multiplier are ignored ("20kk" == "20k").
-  *out = (size_t)std::ceil(v * mult);
+  // Characters after the multiplier are ignored ("20kk" == "20k", "20KiB" == "20k"), as the reference's parser does.
+  const double bytes = std::ceil(v * mult);
+  if (!std::isfinite(bytes) || bytes >= 18446744073709551616.0) return false;  // does not fit 64 bits
+  *out = (size_t)bytes;
   return true;
 }
 

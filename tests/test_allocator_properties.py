@@ -67,3 +67,37 @@ def test_random_sequences_keep_the_heap_consistent(seq):
     finally:
         lib.bshmem_test_alloc_delete(a)
         lib.bshmem_test_alloc_delete(b)
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.integers(0, 1 << 40), st.sampled_from(["", "k", "K", "m", "M", "g", "G", "t", "T"]))
+def test_size_parser_round_trips_every_suffix(value, suffix):
+    lib = H.load()
+    shift = {"": 0, "k": 10, "m": 20, "g": 30, "t": 40}[suffix.lower()]
+    if value >> (63 - shift):
+        return  # would overflow 64 bits
+    out = C.c_ulonglong(0)
+    assert lib.bshmem_test_parse_size(f"{value}{suffix}".encode(), C.byref(out)) == 0
+    assert out.value == value << shift
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.text(alphabet="0123456789kKmMgGtT.-+ xyzeinf", max_size=12))
+def test_size_parser_accepts_only_a_number_with_an_optional_multiplier(text):
+    """Whatever the text: accepted means it starts with a non-negative finite number, optionally followed by one of
+    k/m/g/t (what follows the multiplier is ignored), and the value fits 64 bits."""
+    import math
+    import re
+    lib = H.load()
+    out = C.c_ulonglong(0)
+    ok = lib.bshmem_test_parse_size(text.encode(), C.byref(out)) == 0
+    m = re.match(r"\s*\+?((\d+\.?\d*|\.\d+)([eE][+-]?\d+)?)\s*([kKmMgGtT]?)", text)
+    if ok:
+        assert m is not None, text
+        shift = {"": 0, "k": 10, "m": 20, "g": 30, "t": 40}[m.group(4).lower()]
+        want = math.ceil(float(m.group(1)) * (1 << shift))
+        assert want < 1 << 64 and abs(out.value - want) <= max(1, want >> 50), (text, out.value, want)
+    elif m is not None and m.end() == len(text):
+        # a clean number + multiplier is only refused when it does not fit
+        shift = {"": 0, "k": 10, "m": 20, "g": 30, "t": 40}[m.group(4).lower()]
+        assert float(m.group(1)) * (1 << shift) >= (1 << 64) * (1 - 2 ** -40), text
