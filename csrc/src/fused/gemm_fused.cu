@@ -469,3 +469,15 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
 }
 
 extern "C" int bshmem_fused_gemm_smem_bytes(void) { return SMEM_BYTES; }
+
+// Test hook (host only): the tile that position `t` of the tile order names, for the checks of the order's
+// invariants (every tile once, own rows last, pairs share their columns).  out = {m_tile, n_tile, peer, m_local, idx_in_peer}.
+extern "C" int bshmem_fused_test_tile_info(int mode, int M, int N, int rank, int npes, int t, int* out) {
+  if (npes < 1 || M % (BM * npes) || N % BN || t < 0 || t >= (M / BM) * (N / BN)) return 1;
+  FusedParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = mode; p.M = M; p.N = N; p.rank = rank; p.npes = npes;
+  const TileInfo ti = tile_info(p, t);
+  out[0] = ti.m_tile; out[1] = ti.n_tile; out[2] = ti.peer; out[3] = ti.m_local; out[4] = ti.idx_in_peer;
+  return 0;
+}

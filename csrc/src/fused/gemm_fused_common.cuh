@@ -55,7 +55,7 @@ struct TileInfo {
 
 // Tile order.  Blocks of rows are visited peer by peer (RS/AR: rank+1, rank+2, …, own last; AG: own, rank-1, …);
 // inside a block m runs fastest so that concurrently running CTAs share B tiles through L2.
-__device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
+__host__ __device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
   const int tiles_n = p.N / BN;
   const int tmr = (p.M / p.npes) / BM;
   const int per_peer = tmr * tiles_n;
