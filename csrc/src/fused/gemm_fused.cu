@@ -333,6 +333,46 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
 
 static int g_attr_set_for_device = -1;
 
+// How the all-gather senders split this PE's shard: `n_comm` sender CTAs take one unit each; a unit is either a
+// whole number of 128-row blocks or one of `parts` equal parts of a block (so that arrival counters per block
+// work); it is copied in `piece`-byte bulk copies.  With `pair_wanted` the count must be even (sender CTAs come in
+// whole clusters); if no even count nests, the plan falls back to single CTAs.
+struct AgPlan {
+  int n_comm, parts, tiles_per_unit;
+  bool pair;
+  uint64_t unit_bytes;
+  uint32_t piece;
+};
+static int plan_ag(int rows_per_pe, int K, int n_comm_req, bool pair_wanted, AgPlan* out) {
+  const int tmr = rows_per_pe / BM;
+  auto pick = [&](bool even) {
+    int n = n_comm_req > 0 ? n_comm_req : 16;
+    auto fits = [&](int c) {
+      const bool nests = (c % tmr == 0 && rows_per_pe % c == 0 && BM % (rows_per_pe / c) == 0) || tmr % c == 0;
+      return nests && !(even && (c & 1));
+    };
+    while (n > 1 && !fits(n)) --n;
+    return n;
+  };
+  out->pair = pair_wanted;
+  int n_comm = pick(pair_wanted);
+  if (pair_wanted && (n_comm & 1)) {
+    out->pair = false;
+    n_comm = pick(false);
+  }
+  const size_t shard_bytes = (size_t)rows_per_pe * K * 2;
+  out->n_comm = n_comm;
+  out->unit_bytes = shard_bytes / n_comm;
+  // Largest power-of-two piece (16 B .. COMM_PIECE) that divides a unit.
+  uint32_t piece = COMM_PIECE;
+  while (piece > 16 && out->unit_bytes % piece) piece >>= 1;
+  if (out->unit_bytes % piece) return BSHMEM_FUSED_ERR_SHAPE;
+  out->piece = piece;
+  out->parts = n_comm >= tmr ? n_comm / tmr : 1;
+  out->tiles_per_unit = n_comm >= tmr ? 1 : tmr / n_comm;
+  return 0;
+}
+
 // CTA pairs are the default where the shape allows them; BSHMEM_FUSED_2CTA=0 selects one CTA per tile.
 static bool pair_wanted() {
   static const bool on = [] {
@@ -395,32 +435,20 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   }
   if (mode == BSHMEM_FUSED_AG && npes > 1) {
     if (!a->ag_flags_local) return BSHMEM_FUSED_ERR_ARGS;
-    // One unit of the shard per sender CTA; units and 128-row blocks must nest.  Pairs need an even count.
-    auto pick_n_comm = [&](bool even) {
-      int n = a->n_comm > 0 ? a->n_comm : 16;
-      auto fits = [&](int c) {
-        const bool nests = (c % tmr == 0 && rows_per_pe % c == 0 && BM % (rows_per_pe / c) == 0) || tmr % c == 0;
-        return nests && !(even && (c & 1));
-      };
-      while (n > 1 && !fits(n)) --n;
-      return n;
-    };
-    int n_comm = pick_n_comm(pair);
-    if (pair && (n_comm & 1)) {
+    AgPlan plan;
+    st = plan_ag(rows_per_pe, a->K, a->n_comm, pair, &plan);
+    if (st) return st;
+    if (pair && !plan.pair) {  // no even sender count nests with the tiles: one CTA per tile instead
       pair = false;
       grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
-      n_comm = pick_n_comm(false);
     }
+    const int n_comm = plan.n_comm;
     const size_t shard_bytes = (size_t)rows_per_pe * a->K * 2;
     p.n_comm = n_comm;
-    p.ag_unit_bytes = shard_bytes / n_comm;
-    // Largest power-of-two piece (16 B .. COMM_PIECE) that divides a unit.
-    uint32_t piece = COMM_PIECE;
-    while (piece > 16 && p.ag_unit_bytes % piece) piece >>= 1;
-    if (p.ag_unit_bytes % piece) return BSHMEM_FUSED_ERR_SHAPE;
-    p.ag_piece_bytes = piece;
-    p.ag_parts = n_comm >= tmr ? n_comm / tmr : 1;
-    p.ag_tiles_per_unit = n_comm >= tmr ? 1 : tmr / n_comm;
+    p.ag_unit_bytes = plan.unit_bytes;
+    p.ag_piece_bytes = plan.piece;
+    p.ag_parts = plan.parts;
+    p.ag_tiles_per_unit = plan.tiles_per_unit;
     p.ag_src = (const char*)a->A + (size_t)a->rank * shard_bytes;
     p.ag_flags_local = a->ag_flags_local;
     for (int q = 0; q < npes; ++q) {
@@ -469,6 +497,16 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
 }
 
 extern "C" int bshmem_fused_gemm_smem_bytes(void) { return SMEM_BYTES; }
+
+// Test hook (host only): the sender plan of the all-gather mode.  out = {n_comm, pair, unit_bytes, piece, parts, tiles_per_unit}.
+extern "C" int bshmem_fused_test_ag_plan(int M, int K, int npes, int n_comm_req, int pair_wanted, long long* out) {
+  if (npes < 1 || M <= 0 || K <= 0 || M % (BM * npes) || K % BK) return BSHMEM_FUSED_ERR_SHAPE;
+  AgPlan plan;
+  int st = plan_ag(M / npes, K, n_comm_req, pair_wanted != 0 && (M / npes) % (2 * BM) == 0, &plan);
+  if (st) return st;
+  out[0] = plan.n_comm; out[1] = plan.pair; out[2] = (long long)plan.unit_bytes; out[3] = plan.piece; out[4] = plan.parts; out[5] = plan.tiles_per_unit;
+  return 0;
+}
 
 // Test hook (host only): the tile that position `t` of the tile order names, for the checks of the order's
 // invariants (every tile once, own rows last, pairs share their columns).  out = {m_tile, n_tile, peer, m_local, idx_in_peer}.

@@ -66,3 +66,36 @@ def test_cta_pairs_get_two_row_tiles_of_one_column_block(mode, npes, M, N):
         for u in range(0, len(tiles), 2):
             a, b = tiles[u], tiles[u + 1]
             assert a[1] == b[1] and a[2] == b[2] and b[0] == a[0] + 1 and a[3] % 2 == 0, (rank, u, a, b)
+
+
+def test_all_gather_sender_plan_invariants():
+    """The split of a PE's shard over the sender CTAs: units cover the shard exactly, nest with the 128-row blocks
+    (arrival counters are per block), are copied in power-of-two pieces, and come in even numbers for CTA pairs."""
+    lib = _lib()
+    lib.bshmem_fused_test_ag_plan.argtypes = [C.c_int] * 5 + [C.POINTER(C.c_longlong)]
+    out = (C.c_longlong * 6)()
+    checked = 0
+    for npes in (2, 3, 4, 8):
+        for tmr in (1, 2, 3, 4, 6, 8, 16):
+            for K in (64, 192, 1024, 8192):
+                for req in (0, 1, 2, 3, 5, 8, 16, 24, 32):
+                    for pair in (0, 1):
+                        M = npes * tmr * BM
+                        assert lib.bshmem_fused_test_ag_plan(M, K, npes, req, pair, out) == 0, (npes, tmr, K, req, pair)
+                        n_comm, is_pair, unit, piece, parts, per_unit = [int(v) for v in out]
+                        rows = tmr * BM
+                        shard = rows * K * 2
+                        assert 1 <= n_comm <= (req or 16) and n_comm * unit == shard
+                        assert piece & (piece - 1) == 0 and 16 <= piece <= 16384 and unit % piece == 0
+                        if n_comm >= tmr:
+                            assert n_comm % tmr == 0 and parts == n_comm // tmr and per_unit == 1
+                            assert rows % n_comm == 0 and BM % (rows // n_comm) == 0      # a unit is a whole fraction of one block
+                        else:
+                            assert tmr % n_comm == 0 and parts == 1 and per_unit == tmr // n_comm
+                        if is_pair:
+                            assert pair and tmr % 2 == 0 and n_comm % 2 == 0
+                        checked += 1
+    assert checked > 1000
+    # the benchmark's all-gather shape: 16 senders, half a block each, 16 KB pieces
+    assert lib.bshmem_fused_test_ag_plan(8192, 8192, 8, 0, 1, out) == 0
+    assert [int(v) for v in out] == [16, 1, 1 << 20, 16384, 2, 1]
