@@ -96,6 +96,7 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
                  ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
         "fused": (_sources("fused"), LIB / "libbshmem_fused.so", True, ["-ldl"]),
         "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
+        "plugins": (_sources("bootstrap_plugins"), LIB / "libbshmem_bootstrap_file.so", True, []),
         "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
     }
     built: dict[str, Path] = {}

@@ -90,3 +90,28 @@ def test_stray_connections_do_not_disturb_the_bootstrap():
                           env_extra={"NVSHMEM_HEAP_BACKEND": "HOST", "NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "30000"})
     assert status == 0, outs
     assert "bootstrap survived the strays" in "".join(outs)
+
+
+def test_bootstrap_plugin_is_loaded_and_carries_a_job(tmp_path):
+    """NVSHMEM_BOOTSTRAP=PLUGIN with the file-exchange plugin: the whole bring-up (node info, heap, teams, barriers)
+    runs over a plugin's allgather / alltoall / barrier."""
+    import sys
+    from nvshmem_b200.bindings import host as H
+    from nvshmem_b200.launch import launch
+    plugin = H.lib_path("libbshmem_bootstrap_file.so")
+    assert plugin.exists(), "python -m nvshmem_b200.utils.build --only=plugins"
+    env = {"NVSHMEM_BOOTSTRAP": "PLUGIN", "NVSHMEM_BOOTSTRAP_PLUGIN": str(plugin), "BSHMEM_FILE_BOOTSTRAP_DIR": str(tmp_path),
+           "NVSHMEM_HEAP_BACKEND": "HOST", "NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "30000", "PYTHONPATH": str(ROOT)}
+    status, outs = launch(3, [sys.executable, "-m", "perftest.plumbing"], timeout=120, capture=True, env_extra=env)
+    assert status == 0, outs
+    assert '"offsets_identical": true' in "".join(outs)
+    leftovers = [p.name for p in tmp_path.iterdir()]
+    assert leftovers == [], leftovers  # every rank removed its files
+
+
+def test_bootstrap_plugin_errors_are_reported(tmp_path):
+    import sys
+    from nvshmem_b200.launch import launch
+    env = {"NVSHMEM_BOOTSTRAP": "PLUGIN", "NVSHMEM_BOOTSTRAP_PLUGIN": str(tmp_path / "no_such_plugin.so"), "NVSHMEM_HEAP_BACKEND": "HOST", "PYTHONPATH": str(ROOT)}
+    status, outs = launch(1, [sys.executable, "-m", "perftest.plumbing"], timeout=60, capture=True, env_extra=env)
+    assert status != 0 and "dlopen" in "".join(outs)
