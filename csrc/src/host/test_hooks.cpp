@@ -89,6 +89,17 @@ void* bshmem_test_boot_init_pmi(int* status) {
   }
   return h;
 }
+void* bshmem_test_boot_init_plugin(int* status) {
+  options_reload();
+  auto* h = new bshmem_bootstrap_handle_t();
+  int st = bootstrap_init(BOOT_PLUGIN, nullptr, 0, 0, h);
+  if (status) *status = st;
+  if (st != BOOT_OK) {
+    delete h;
+    return nullptr;
+  }
+  return h;
+}
 int bshmem_test_boot_rank(void* h) { return ((bshmem_bootstrap_handle_t*)h)->pg_rank; }
 int bshmem_test_boot_size(void* h) { return ((bshmem_bootstrap_handle_t*)h)->pg_size; }
 int bshmem_test_boot_allgather(void* h, const void* send, void* recv, int bytes) {

@@ -115,3 +115,13 @@ def test_bootstrap_plugin_errors_are_reported(tmp_path):
     env = {"NVSHMEM_BOOTSTRAP": "PLUGIN", "NVSHMEM_BOOTSTRAP_PLUGIN": str(tmp_path / "no_such_plugin.so"), "NVSHMEM_HEAP_BACKEND": "HOST", "PYTHONPATH": str(ROOT)}
     status, outs = launch(1, [sys.executable, "-m", "perftest.plumbing"], timeout=60, capture=True, env_extra=env)
     assert status != 0 and "dlopen" in "".join(outs)
+
+
+def test_bootstrap_plugin_collectives(tmp_path):
+    import sys
+    from nvshmem_b200.bindings import host as H
+    from nvshmem_b200.launch import launch
+    env = {"NVSHMEM_BOOTSTRAP_PLUGIN": str(H.lib_path("libbshmem_bootstrap_file.so")), "BSHMEM_FILE_BOOTSTRAP_DIR": str(tmp_path), "NVSHMEM_BOOTSTRAP_TIMEOUT_MS": "30000"}
+    status, outs = launch(4, [sys.executable, str(ROOT / "tests" / "plugin_child.py")], timeout=120, capture=True, env_extra=env)
+    assert status == 0, outs
+    assert "plugin collectives ok" in "".join(outs) and list(tmp_path.iterdir()) == []
