@@ -219,8 +219,8 @@ int do_init(unsigned int flags, nvshmemx_init_attr_t* attr, bool hostlib_only) {
 
 template <class T>
 static void wait_all_impl(T* ivars, size_t n, const int* status, int cmp, const T* values, T value, cudaStream_t s) {
-  // 64-bit unsigned arrays go through one kernel; other widths wait entry by entry.
-  if (!is_initialized() || !rt().have_gpu) return;
+  // Entry by entry (on the host-memory back end the calling thread polls each word, with the usual bound).
+  if (!is_initialized()) return;
   for (size_t i = 0; i < n; ++i) {
     if (status && status[i]) continue;
     wait_on_stream(ivars + i, cmp, (uint64_t)(values ? values[i] : value), (int)sizeof(T), std::is_signed<T>::value, s);

@@ -98,6 +98,19 @@ def python_layer_on_host_heap():
     nv.clear_errors()
     nv.set_wait_timeout_ms(5000)
     H_barrier()
+    # typed waits on arrays: the right neighbour fills my three words one by one; negative values compare as signed
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    words = nv.tensor((3,), torch.int64, zero=True)
+    H_barrier()
+    for k in range(3):
+        lib.nvshmem_long_p(C.c_void_p(words.data_ptr() + 8 * k), C.c_long(-5 + k), left)
+    status = (C.c_int * 3)(0, 0, 0)
+    lib.nvshmemx_long_wait_until_all_on_stream.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_long, C.c_void_p]
+    lib.nvshmemx_long_wait_until_all_on_stream(C.c_void_p(words.data_ptr()), 3, status, int(nv.ComparisonType.CMP_LT), 0, None)
+    assert words.tolist() == [-5, -4, -3] and nv.error_bits() == 0
+    H_barrier()
+    nv.free_tensor(words)
     # a peer view aliases the neighbour's memory (process-shared mapping on this back end)
     peer = nv.get_peer_tensor(t, right)
     assert torch.equal(peer, (torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me) * 2)
