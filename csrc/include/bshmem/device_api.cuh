@@ -28,7 +28,7 @@ BSHMEM_DEV(int, nvshmem_n_pes, (void), { return bshmem::n_pes(); })
 BSHMEM_DEV(void*, nvshmem_ptr, (const void* dest, int pe), { return bshmem::ptr(dest, pe); })
 BSHMEM_DEV(void*, nvshmemx_mc_ptr, (nvshmem_team_t team, const void* p), {
   const bshmemi_team_t* t = bshmem::team_ptr(team);
-  return t && t->has_nvls ? bshmem::mc_ptr(p) : nullptr;
+  return t && t->has_nvls && bshmem::in_heap(p) ? (void*)(t->mc_base + ((uint64_t)p - bshmemi_state_d.heap_base)) : nullptr;
 })
 BSHMEM_DEV(int, nvshmem_team_my_pe, (nvshmem_team_t team), { return bshmem::team_my_pe(team); })
 BSHMEM_DEV(int, nvshmem_team_n_pes, (nvshmem_team_t team), { return bshmem::team_n_pes(team); })

@@ -36,21 +36,27 @@ typedef struct {
   uint64_t epoch;            /* call counter of this buffer set, starting at 1, identical on all PEs */
   uint32_t wait_limit_ms;    /* bound of every in-kernel wait; 0 = 10 s */
   int max_ctas;              /* 0 = one per SM */
-  int n_comm;                /* AG: CTAs that only send (0 = 16) */
-  int* error_flag;           /* device int, OR-ed with 1 (GEMM CTA gave up) / 2 (sender gave up) */
+  int n_comm;                /* unused (kept for layout compatibility): no CTA is set aside for sending */
+  int* error_flag;           /* device int, OR-ed with 1 when a CTA gave up on a bounded wait */
   /* RS / AR */
-  void* recv_local;                           /* [npes][M/npes][N] bf16 receive slots (pick the half of this call's parity) */
+  void* recv_local;                           /* push path: [npes][M/npes][N] bf16 receive slots (pick the half of this call's parity) */
   void* recv_peer[BSHMEM_FUSED_MAX_PES];      /* the same buffer on each PE */
   uint64_t* flags_local;                      /* [npes][(M/npes/128)*(N/256)] */
   uint64_t* flags_peer[BSHMEM_FUSED_MAX_PES];
   void* out_peer[BSHMEM_FUSED_MAX_PES];       /* AR only */
   /* AG */
   void* ag_peer[BSHMEM_FUSED_MAX_PES];
-  uint64_t* ag_flags_local;                   /* [npes][M/npes/128] arrival counters */
+  uint64_t* ag_flags_local;                   /* [npes][M/npes/128] arrival counters (rows landed; 128 per call and block) */
   uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
   /* AR, optional: NVLink-multicast alias of `out` (nvshmemx_mc_ptr).  When set, a reduced tile leaves this GPU
    * once and the switch delivers it to every PE; when null it is stored to each PE's out in turn. */
   void* out_mc;
+  /* RS / AR, optional: switch path.  stage_local is this PE's [M][N] bf16 staging buffer in symmetric memory (pick
+   * the half of this call's parity), stage_mc its NVLink-multicast alias.  When both are set (and, for AR, out_mc),
+   * partial tiles stay in the producing GPU's memory and the owner of a tile reads their sum with multimem.ld_reduce;
+   * recv_local / recv_peer / out_peer are then unused. */
+  void* stage_local;
+  void* stage_mc;
 } bshmem_fused_args_t;
 
 /* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */

@@ -118,13 +118,23 @@ __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src,
 }
 
 // ---------------------------------------------------------------- tensor memory
-// Whole-warp calls.  `cols` is a power of two in [32, 512].
+// Whole-warp calls.  `cols` is a power of two in [32, 512].  GROUP is the kernel's .cta_group (all tcgen05
+// instructions of one kernel must agree on it): 1 for a single CTA; 2 for a CTA pair, where one warp of EACH
+// CTA of the pair executes the call and both CTAs' tensor memories get the same columns.
+template <int GROUP = 1>
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+  if constexpr (GROUP == 2) asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+  else asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+template <int GROUP = 1>
+__device__ __forceinline__ void tmem_relinquish() {
+  if constexpr (GROUP == 2) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+template <int GROUP = 1>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  if constexpr (GROUP == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
 // ---------------------------------------------------------------- UMMA descriptors

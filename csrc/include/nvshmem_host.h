@@ -319,6 +319,10 @@ const char* nvshmemx_b200_topology(void);
 /* Heap facts: 0 base of the local window, 1 stride, 2 backed bytes, 3 multicast base, 4 chunks, 5 bytes in use,
  * 6 digest of the allocation history, 7 whether the heap is GPU memory. */
 uint64_t nvshmemx_b200_heap_info(int what);
+/* Detaches this PE from every NVLink multicast object (unmap, unbind, release) without any collective step.
+ * For a process that is about to leave abnormally: peers' GPUs must not be left with a member that vanished
+ * while bound.  NVLS collectives are off on this PE afterwards. */
+void nvshmemx_b200_release_multicast(void);
 /* Explicit algorithm choice for benchmarks (0 = automatic). */
 int nvshmemx_b200_reduce_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t n, int dtype, int op, int algo, cudaStream_t s);
 int nvshmemx_b200_reducescatter_on_stream(nvshmem_team_t team, void* dest, const void* src, size_t n, int dtype, int op, int algo, cudaStream_t s);

@@ -6,17 +6,22 @@
 // One persistent CTA per SM, 256 threads, warp-specialised:
 //   warp 0    TMA producer   4-stage ring of {A 128x64, B 256x64} tiles (128-byte swizzle)
 //   warp 1    MMA issuer     one thread issues tcgen05.mma 128x256x16, accumulators double-buffered in TMEM (2 x 256 columns)
-//   warp 2    TMEM allocator
+//   warp 2    TMEM allocator, then auxiliary (with warp 3): the collective's data movement, see below
 //   warps 4-7 epilogue       tcgen05.ld -> fp32 registers -> (+ peers' partial tiles) -> bf16 -> swizzled smem -> TMA store
-// and the collective rides on the epilogue, tile by tile, over peer memory:
-//   MODE_RS  row-parallel GEMM -> reduce-scatter.  Tiles whose rows belong to another PE are computed first
-//            (nearest destination first, so that each PE feeds a different peer at any time) and TMA-stored as
-//            bf16 partials straight into that PE's receive slot, followed by a release flag per tile.  The PE's own
-//            rows come last: their epilogue waits for the seven flags of the tile and adds the seven partials to
-//            the TMEM accumulator before the single rounding to bf16.  No separate reduction pass exists.
-//   MODE_AR  same, but the finished tile is TMA-stored into every PE's output (allreduce).
-//   MODE_AG  all-gather -> column-parallel GEMM.  A few extra CTAs push this PE's activation shard into every
-//            peer's gathered buffer with bulk copies (nearest peer first) and bump a counter per 128-row block;
+// and the collective runs inside the same kernel, tile by tile, over peer memory:
+//   MODE_RS  row-parallel GEMM -> reduce-scatter, two paths.
+//            Switch path (the staging buffer has an NVLink-multicast alias): every PE walks the tiles in the same
+//            order, TMA-stores each bf16 partial tile into its OWN staging buffer and flags the tile's owner; the
+//            owner's auxiliary warps fetch the sum of all PEs' copies with `multimem.ld_reduce` (added inside the
+//            switch) and write the output.  The epilogue never waits for a peer and never adds partials, the owner
+//            receives one tile instead of npes - 1, and the reduction of a tile overlaps the main loops of later tiles.
+//            Push path (no multicast): tiles whose rows belong to another PE are computed first (nearest destination
+//            first) and TMA-stored as bf16 partials straight into that PE's receive slot, followed by a release flag
+//            per tile.  The PE's own rows come last: their epilogue waits for the flags of the tile and adds the
+//            partials to the TMEM accumulator before the single rounding to bf16.
+//   MODE_AR  same; the reduced tile goes to every PE's output (one `multimem.st` through the switch, or per-PE stores).
+//   MODE_AG  all-gather -> column-parallel GEMM.  The auxiliary warps of all CTAs copy this PE's activation shard into
+//            every peer's gathered buffer (nearest peer first) and count rows into a counter per 128-row block;
 //            the producer warp consumes shards in arrival order (own, then rank-1, rank-2, …) and only waits when a
 //            block has not landed.  Remote data is always read from this GPU's own memory.
 //   MODE_PLAIN  no collective (also what 1 PE runs).
@@ -60,7 +65,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   uint8_t* sB = smem + STAGES * A_STAGE;
   uint8_t* sE = sB + STAGES * B_STAGE;
   uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
-  uint64_t* full = bars;                    // [STAGES]  (the sender CTAs use [0, COMM_BUFS) of the same array)
+  uint64_t* full = bars;                    // [STAGES]
   uint64_t* empty = bars + STAGES;          // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
@@ -68,36 +73,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0;  // sender CTAs come in whole pairs: n_comm is even
-  const bool is_sender = p.mode == BSHMEM_FUSED_AG && (int)blockIdx.x < p.n_comm;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    if (is_sender) {
-      for (int i = 0; i < COMM_BUFS; ++i) mbar_init(&bars[i], 1);
-    } else {
-      for (int i = 0; i < STAGES; ++i) {
-        mbar_init(&full[i], PAIR ? 2 : 1);  // pair: one arrival (with its byte count) from each CTA's producer
-        mbar_init(&empty[i], 1);
-      }
-      for (int i = 0; i < 2; ++i) {
-        mbar_init(&acc_full[i], 1);
-        mbar_init(&acc_empty[i], (PAIR ? 2 : 1) * (EPI_THREADS / 32));  // one arrival per epilogue warp
-      }
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], PAIR ? 2 : 1);  // pair: one arrival (with its byte count) from each CTA's producer
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], (PAIR ? 2 : 1) * (EPI_THREADS / 32));  // one arrival per epilogue warp
     }
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (is_sender) {
-    __syncthreads();
-    ag_sender(p, smem, bars, abort_flag);
-    __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 2);
-    return;
-  }
+  // Every tcgen05 instruction of a kernel carries the same .cta_group: the pair kernel allocates (and later frees)
+  // tensor memory with cta_group::2, one warp of each CTA of the pair taking part.
   if (warp == 2) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    tmem_alloc<PAIR ? 2 : 1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<PAIR ? 2 : 1>();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -108,11 +103,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   const int tiles_n = p.N / BN;
   const int total_tiles = (p.M / BM) * tiles_n;
   const int kblocks = p.K / BK;
-  const int n_send = p.mode == BSHMEM_FUSED_AG ? p.n_comm : 0;
   // Pair: worker u = pair index takes tiles 2u + r, 2(u + workers) + r, …
-  const int first = PAIR ? (((int)blockIdx.x - n_send) & ~1) + (int)cta_rank : (int)blockIdx.x - n_send;
-  const int step = (int)gridDim.x - n_send;
+  const int first = PAIR ? ((int)blockIdx.x & ~1) + (int)cta_rank : (int)blockIdx.x;
+  const int step = (int)gridDim.x;
   const int tmr = (p.M / p.npes) / BM;
+  const bool reduce_mode = (p.mode == BSHMEM_FUSED_RS || p.mode == BSHMEM_FUSED_AR) && p.npes > 1;
 
   if (warp == 0) {
     // ---------------- TMA producer
@@ -125,7 +120,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         const TileInfo ti = tile_info(p, t);
         if (p.mode == BSHMEM_FUSED_AG && ti.peer != p.rank) {
           // The 128 rows of this tile arrive from `peer`; all of K comes with them.
-          if (!wait_flag_ge(p.ag_flags_local + (size_t)ti.peer * tmr + ti.m_local, p.epoch * (uint64_t)p.ag_parts, p.wait_limit_ns, abort_flag)) break;
+          if (!wait_flag_ge(p.ag_flags_local + (size_t)ti.peer * tmr + ti.m_local, p.epoch * (uint64_t)BM, p.wait_limit_ns, abort_flag)) break;
           fence_proxy_async_all();  // peer-written data (generic proxy) before my TMA reads (async proxy)
         }
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -183,18 +178,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else if (warp >= EPI_WARP0) {
+  } else if (warp < EPI_WARP0) {
+    // ---------------- auxiliary warps 2 and 3
+    if (p.mode == BSHMEM_FUSED_AG && p.npes > 1) ag_send_rows(p, (int)threadIdx.x - AUX_WARP0 * 32, abort_flag);
+    else if (reduce_mode && p.sw_reduce) switch_reduce(p, warp - AUX_WARP0, lane, abort_flag);
+  } else {
     // ---------------- epilogue
     const int ew = warp - EPI_WARP0;                 // TMEM lane quarter of this warp
     const int row = ew * 32 + lane;                  // row of the tile handled by this thread
     const bool issuer = threadIdx.x == EPI_WARP0 * 32;
-    const bool reduce_mode = (p.mode == BSHMEM_FUSED_RS || p.mode == BSHMEM_FUSED_AR) && p.npes > 1;
+    const bool sw = reduce_mode && p.sw_reduce;  // every tile goes to the local staging buffer; the auxiliary warps reduce
     int acc = 0;
     uint32_t acc_phase = 0, chunk_counter = 0;
     uint64_t* pending_flag = nullptr;  // flag of the previous remote tile, published once its stores have completed
     for (int t = first; t < total_tiles; t += step) {
       const TileInfo ti = tile_info(p, t);
-      const bool own = !reduce_mode || ti.peer == p.rank;
+      const bool own = !reduce_mode || (!sw && ti.peer == p.rank);
       uint32_t ok = mbar_wait(&acc_full[acc], acc_phase, p.wait_limit_ns, abort_flag) ? 1u : 0u;
       if (issuer && pending_flag) {
         // The previous tile's stores were issued a whole main loop ago: this wait does not stall.
@@ -290,7 +289,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
           }
         } else if (issuer) {
           const int x = ti.n_tile * BN + c * EPI_COLS;
-          if (!own) {
+          if (sw) {
+            tma_store_2d(&p.tmStage, buf, x, ti.m_tile * BM);
+          } else if (!own) {
             tma_store_2d(&p.tmRecv[ti.peer], buf, x, ti.m_local * BM);
           } else if (p.mode == BSHMEM_FUSED_AR && p.npes > 1) {
             for (int q = 0; q < p.npes; ++q) tma_store_2d(&p.tmOut[(p.rank + q) % p.npes], buf, x, ti.m_tile * BM);
@@ -305,7 +306,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
       }
       // Waiting here for the remote writes would idle the epilogue for a link round trip per tile;
       // the flag goes out at the start of the next tile's epilogue instead (or after the loop).
-      if (!own && issuer) pending_flag = p.flags_peer[ti.peer] + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
+      if (sw) {
+        // The partial tile stays in this GPU's memory: its stores complete within a microsecond or two, and the
+        // owner is told at once so that the reduction runs while the next tiles are computed.
+        if (issuer) {
+          bulk_wait<0>();
+          fence_proxy_async_all();
+          uint64_t* f = (ti.peer == p.rank ? p.flags_local : p.flags_peer[ti.peer]) + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
+          asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(p.epoch) : "memory");
+        }
+      } else if (!own && issuer) {
+        pending_flag = p.flags_peer[ti.peer] + (size_t)p.rank * (tmr * tiles_n) + ti.idx_in_peer;
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) {
@@ -327,51 +339,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   __syncthreads();
   // Pair: neither CTA leaves (or frees tensor memory the leader's MMAs write) before both are done.
   if (PAIR) cluster_sync_all();
-  if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 2) tmem_dealloc<PAIR ? 2 : 1>(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 1);
 }
 
 static int g_attr_set_for_device = -1;
-
-// How the all-gather senders split this PE's shard: `n_comm` sender CTAs take one unit each; a unit is either a
-// whole number of 128-row blocks or one of `parts` equal parts of a block (so that arrival counters per block
-// work); it is copied in `piece`-byte bulk copies.  With `pair_wanted` the count must be even (sender CTAs come in
-// whole clusters); if no even count nests, the plan falls back to single CTAs.
-struct AgPlan {
-  int n_comm, parts, tiles_per_unit;
-  bool pair;
-  uint64_t unit_bytes;
-  uint32_t piece;
-};
-static int plan_ag(int rows_per_pe, int K, int n_comm_req, bool pair_wanted, AgPlan* out) {
-  const int tmr = rows_per_pe / BM;
-  auto pick = [&](bool even) {
-    int n = n_comm_req > 0 ? n_comm_req : 16;
-    auto fits = [&](int c) {
-      const bool nests = (c % tmr == 0 && rows_per_pe % c == 0 && BM % (rows_per_pe / c) == 0) || tmr % c == 0;
-      return nests && !(even && (c & 1));
-    };
-    while (n > 1 && !fits(n)) --n;
-    return n;
-  };
-  out->pair = pair_wanted;
-  int n_comm = pick(pair_wanted);
-  if (pair_wanted && (n_comm & 1)) {
-    out->pair = false;
-    n_comm = pick(false);
-  }
-  const size_t shard_bytes = (size_t)rows_per_pe * K * 2;
-  out->n_comm = n_comm;
-  out->unit_bytes = shard_bytes / n_comm;
-  // Largest power-of-two piece (16 B .. COMM_PIECE) that divides a unit.
-  uint32_t piece = COMM_PIECE;
-  while (piece > 16 && out->unit_bytes % piece) piece >>= 1;
-  if (out->unit_bytes % piece) return BSHMEM_FUSED_ERR_SHAPE;
-  out->piece = piece;
-  out->parts = n_comm >= tmr ? n_comm / tmr : 1;
-  out->tiles_per_unit = n_comm >= tmr ? 1 : tmr / n_comm;
-  return 0;
-}
 
 // CTA pairs are the default where the shape allows them; BSHMEM_FUSED_2CTA=0 selects one CTA per tile.
 static bool pair_wanted() {
@@ -411,7 +383,8 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   const bool reduce_mode = (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1;
   if (mode == BSHMEM_FUSED_AR && npes > 1) {
     p.out_mc = (char*)a->out_mc;
-    for (int q = 0; q < npes && !st; ++q) {
+    const bool sw = a->stage_local && a->stage_mc && a->out_mc;  // the switch path stores through out_mc only
+    for (int q = 0; q < npes && !st && !sw; ++q) {
       if (!a->out_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
       st = make_map(&p.tmOut[q], a->out_peer[q], a->M, a->N, BM);
     }
@@ -420,35 +393,33 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   }
   if (st) return st;
   if (reduce_mode) {
-    if (!a->recv_local || !a->flags_local) return BSHMEM_FUSED_ERR_ARGS;
-    p.recv_local = (const __nv_bfloat16*)a->recv_local;
+    if (!a->flags_local) return BSHMEM_FUSED_ERR_ARGS;
     p.flags_local = a->flags_local;
+    // Switch path: a staging buffer with a multicast alias (and, for the all-reduce, a multicast alias of the output).
+    p.sw_reduce = a->stage_local && a->stage_mc && (mode == BSHMEM_FUSED_RS || a->out_mc);
+    if (p.sw_reduce) {
+      if (((uintptr_t)a->stage_mc & 15) || ((uintptr_t)a->out & 15) || ((uintptr_t)a->out_mc & 15)) return BSHMEM_FUSED_ERR_ALIGNMENT;
+      p.stage_mc = (const char*)a->stage_mc;
+      p.out_local = (char*)a->out;
+      st = make_map(&p.tmStage, a->stage_local, a->M, a->N, BM);
+    } else {
+      if (!a->recv_local) return BSHMEM_FUSED_ERR_ARGS;
+      p.recv_local = (const __nv_bfloat16*)a->recv_local;
+    }
     for (int q = 0; q < npes && !st; ++q) {
       if (q == a->rank) continue;
-      if (!a->recv_peer[q] || !a->flags_peer[q]) return BSHMEM_FUSED_ERR_ARGS;
+      if (!a->flags_peer[q] || (!p.sw_reduce && !a->recv_peer[q])) return BSHMEM_FUSED_ERR_ARGS;
+      p.flags_peer[q] = a->flags_peer[q];
+      if (p.sw_reduce) continue;
       // My slot (index `rank`) inside PE q's receive buffer.
       const char* slot = (const char*)a->recv_peer[q] + (size_t)a->rank * rows_per_pe * a->N * 2;
       st = make_map(&p.tmRecv[q], slot, rows_per_pe, a->N, BM);
-      p.flags_peer[q] = a->flags_peer[q];
     }
     if (st) return st;
   }
   if (mode == BSHMEM_FUSED_AG && npes > 1) {
     if (!a->ag_flags_local) return BSHMEM_FUSED_ERR_ARGS;
-    AgPlan plan;
-    st = plan_ag(rows_per_pe, a->K, a->n_comm, pair, &plan);
-    if (st) return st;
-    if (pair && !plan.pair) {  // no even sender count nests with the tiles: one CTA per tile instead
-      pair = false;
-      grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
-    }
-    const int n_comm = plan.n_comm;
     const size_t shard_bytes = (size_t)rows_per_pe * a->K * 2;
-    p.n_comm = n_comm;
-    p.ag_unit_bytes = plan.unit_bytes;
-    p.ag_piece_bytes = plan.piece;
-    p.ag_parts = plan.parts;
-    p.ag_tiles_per_unit = plan.tiles_per_unit;
     p.ag_src = (const char*)a->A + (size_t)a->rank * shard_bytes;
     p.ag_flags_local = a->ag_flags_local;
     for (int q = 0; q < npes; ++q) {
@@ -457,7 +428,6 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
       p.ag_dst[q] = (char*)a->ag_peer[q] + (size_t)a->rank * shard_bytes;
       p.ag_flags_peer[q] = a->ag_flags_peer[q];
     }
-    if (grid - n_comm < (pair ? 2 : 1)) return BSHMEM_FUSED_ERR_ARGS;
   }
   st = make_map(&p.tmB, a->B, a->N, a->K, pair ? BN / 2 : BN);
   if (st) return st;
@@ -498,22 +468,22 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
 
 extern "C" int bshmem_fused_gemm_smem_bytes(void) { return SMEM_BYTES; }
 
-// Test hook (host only): the sender plan of the all-gather mode.  out = {n_comm, pair, unit_bytes, piece, parts, tiles_per_unit}.
-extern "C" int bshmem_fused_test_ag_plan(int M, int K, int npes, int n_comm_req, int pair_wanted, long long* out) {
-  if (npes < 1 || M <= 0 || K <= 0 || M % (BM * npes) || K % BK) return BSHMEM_FUSED_ERR_SHAPE;
-  AgPlan plan;
-  int st = plan_ag(M / npes, K, n_comm_req, pair_wanted != 0 && (M / npes) % (2 * BM) == 0, &plan);
-  if (st) return st;
-  out[0] = plan.n_comm; out[1] = plan.pair; out[2] = (long long)plan.unit_bytes; out[3] = plan.piece; out[4] = plan.parts; out[5] = plan.tiles_per_unit;
+// Test hook (host only): the rows of a shard that CTA `b` of `grid` sends in the all-gather mode.  out = {lo, hi}.
+extern "C" int bshmem_fused_test_ag_slice(int rows, int grid, int b, int* out) {
+  if (rows <= 0 || grid <= 0 || b < 0 || b >= grid) return 1;
+  ag_slice(rows, grid, b, &out[0], &out[1]);
   return 0;
 }
 
 // Test hook (host only): the tile that position `t` of the tile order names, for the checks of the order's
 // invariants (every tile once, own rows last, pairs share their columns).  out = {m_tile, n_tile, peer, m_local, idx_in_peer}.
+// `mode` may carry BSHMEM_FUSED_TEST_SWITCH_ORDER (0x100) to ask for the order of the switch path of RS / AR.
 extern "C" int bshmem_fused_test_tile_info(int mode, int M, int N, int rank, int npes, int t, int* out) {
   if (npes < 1 || M % (BM * npes) || N % BN || t < 0 || t >= (M / BM) * (N / BN)) return 1;
   FusedParams p;
   memset(&p, 0, sizeof(p));
+  p.sw_reduce = (mode & 0x100) != 0;
+  mode &= 0xff;
   p.mode = mode; p.M = M; p.N = N; p.rank = rank; p.npes = npes;
   const TileInfo ti = tile_info(p, t);
   out[0] = ti.m_tile; out[1] = ti.n_tile; out[2] = ti.peer; out[3] = ti.m_local; out[4] = ti.idx_in_peer;

@@ -23,27 +23,30 @@ constexpr int A_STAGE = BM * BK * 2;
 constexpr int EPI_COLS = 64, EPI_BUF = BM * EPI_COLS * 2, EPI_BUFS = 2;
 constexpr int TMEM_COLS = 512, ACC_COLS = BN;
 constexpr int NTHREADS = 256, EPI_THREADS = 128, EPI_WARP0 = 4;
-constexpr int COMM_PIECE = 16384, COMM_BUFS = 8, COMM_AHEAD = 4;
+constexpr int AUX_WARP0 = 2, AUX_THREADS = 64;   // warps 2 and 3: switch-side reduction (RS / AR) or shard sender (AG)
+constexpr int RED_ROWS = 16;                      // rows of a tile that one auxiliary warp reduces per work item
 constexpr int SMEM_TILES = 4 * (A_STAGE + BN * BK * 2) + EPI_BUFS * EPI_BUF;  // 4 stages of a 128 x 256 tile = 6 stages of a pair's halves
 constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-static_assert(COMM_PIECE * COMM_BUFS <= SMEM_TILES, "the sender's ring must fit in the GEMM's shared memory");
 
 struct alignas(64) FusedParams {
   CUtensorMap tmA, tmB;
   CUtensorMap tmOut[BSHMEM_FUSED_MAX_PES];   // PLAIN/RS/AG: [0] is the local output; AR: output of each PE
-  CUtensorMap tmRecv[BSHMEM_FUSED_MAX_PES];  // RS/AR: my slot in the receive buffer of each PE
+  CUtensorMap tmRecv[BSHMEM_FUSED_MAX_PES];  // RS/AR, push path: my slot in the receive buffer of each PE
+  CUtensorMap tmStage;                       // RS/AR, switch path: this PE's staging buffer [M][N] of partial tiles
+  const char* stage_mc;                      // multicast alias of the staging buffer (non-null selects the switch path)
+  char* out_local;                           // RS switch path: this PE's [M/npes][N] output
   const __nv_bfloat16* recv_local;           // [npes][M/npes][N] partials received from each PE
   uint64_t* flags_local;                     // [npes][tiles per PE]
   uint64_t* flags_peer[BSHMEM_FUSED_MAX_PES];
   const char* ag_src;                        // my shard inside my gathered buffer
   char* ag_dst[BSHMEM_FUSED_MAX_PES];        // the same shard inside each PE's gathered buffer
-  uint64_t* ag_flags_local;                  // [npes][m-tiles per shard]
+  uint64_t* ag_flags_local;                  // [npes][m-tiles per shard]: rows of the 128-row block that have landed (x epoch)
   uint64_t* ag_flags_peer[BSHMEM_FUSED_MAX_PES];
   char* out_mc;                              // AR: multicast alias of the output (null: per-PE stores)
   int* error_flag;
-  uint64_t epoch, wait_limit_ns, ag_unit_bytes;
-  uint32_t ag_piece_bytes;  // size of one bulk copy of the sender (16-byte multiple, at most COMM_PIECE)
-  int M, N, K, rank, npes, mode, n_comm, ag_parts, ag_tiles_per_unit;
+  uint64_t epoch, wait_limit_ns;
+  int M, N, K, rank, npes, mode;
+  int sw_reduce;                             // RS/AR: partial tiles stay local and the owner fetches their sum through the switch
 };
 
 struct TileInfo {
@@ -55,12 +58,24 @@ struct TileInfo {
 
 // Tile order.  Blocks of rows are visited peer by peer (RS/AR: rank+1, rank+2, …, own last; AG: own, rank-1, …);
 // inside a block m runs fastest so that concurrently running CTAs share B tiles through L2.
+// Switch path of RS/AR: every PE walks the output in the same order (m fastest over all rows, then n), so that the
+// partials of a tile are produced at about the same time everywhere and its owner can reduce it right away; owners
+// alternate every M/npes rows, so the reduction traffic is spread evenly over the PEs and over the run.
 __host__ __device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
   const int tiles_n = p.N / BN;
   const int tmr = (p.M / p.npes) / BM;
   const int per_peer = tmr * tiles_n;
-  const int o = t / per_peer, within = t % per_peer;
   TileInfo ti;
+  if (p.sw_reduce) {
+    const int tiles_m = tmr * p.npes;
+    ti.m_tile = t % tiles_m;
+    ti.n_tile = t / tiles_m;
+    ti.peer = ti.m_tile / tmr;
+    ti.m_local = ti.m_tile % tmr;
+    ti.idx_in_peer = ti.n_tile * tmr + ti.m_local;
+    return ti;
+  }
+  const int o = t / per_peer, within = t % per_peer;
   if (p.mode == BSHMEM_FUSED_AG) ti.peer = (p.rank - o + p.npes) % p.npes;
   else ti.peer = (p.rank + 1 + o) % p.npes;
   ti.m_local = within % tmr;
@@ -90,50 +105,92 @@ __device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t want
   }
 }
 
-// ------------------------------------------------------------------ all-gather sender (MODE_AG, extra CTAs)
-__device__ void ag_sender(const FusedParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
-  if (threadIdx.x != 0) return;
-  const int unit = blockIdx.x;  // one unit of my shard per sender CTA
-  const size_t unit_off = (size_t)unit * p.ag_unit_bytes;
-  const uint32_t PIECE = p.ag_piece_bytes;
-  const int pieces = (int)(p.ag_unit_bytes / PIECE);
-  const int tmr = (p.M / p.npes) / BM;
-  uint32_t phase_bits = 0;  // one parity bit per ring slot
-  for (int o = 1; o < p.npes && !*abort_flag; ++o) {
+// ------------------------------------------------------------------ auxiliary warps (warps 2 and 3 of every CTA)
+__device__ __forceinline__ void aux_bar_sync() { named_bar_sync(2, AUX_THREADS); }
+
+// MODE_AG: the 64 auxiliary threads of every CTA copy a slice of this PE's shard (whole rows, split evenly over the
+// grid) into every peer's gathered buffer with 16-byte loads and stores, nearest peer first, and then add the number of
+// rows delivered to the arrival counter of each 128-row block they touched.  No CTA is set aside for sending, so every
+// SM keeps computing; the copies ride in the load/store slots that the tensor-core pipeline leaves idle.
+// Rows [lo, hi) of the shard that CTA `b` of `grid` sends.
+__host__ __device__ __forceinline__ void ag_slice(int rows, int grid, int b, int* lo, int* hi) {
+  *lo = (int)(((long long)b * rows) / grid);
+  *hi = (int)(((long long)(b + 1) * rows) / grid);
+}
+__device__ void ag_send_rows(const FusedParams& p, int at /*0..63*/, volatile int* abort_flag) {
+  const int rows = p.M / p.npes, tmr = rows / BM;
+  int lo, hi;
+  ag_slice(rows, (int)gridDim.x, (int)blockIdx.x, &lo, &hi);
+  if (lo >= hi) return;
+  const size_t row_bytes = (size_t)p.K * 2;
+  const size_t n16 = (size_t)(hi - lo) * row_bytes / 16;  // K is a multiple of 64: rows are whole 16-byte pieces
+  const uint4* src = (const uint4*)(p.ag_src + (size_t)lo * row_bytes);
+  constexpr int UNROLL = 8;
+  for (int o = 1; o < p.npes; ++o) {
+    if (*abort_flag) return;
     const int peer = (p.rank + o) % p.npes;
-    const char* src = p.ag_src + unit_off;
-    char* dst = p.ag_dst[peer] + unit_off;
-    const int ahead = pieces < COMM_AHEAD ? pieces : COMM_AHEAD;
-    for (int q = 0; q < ahead; ++q) {
-      mbar_expect_tx(&bars[q % COMM_BUFS], PIECE);
-      bulk_load(smem + (q % COMM_BUFS) * COMM_PIECE, src + (size_t)q * PIECE, PIECE, &bars[q % COMM_BUFS]);
+    uint4* dst = (uint4*)(p.ag_dst[peer] + (size_t)lo * row_bytes);
+    size_t i = at;
+    for (; i + (size_t)(UNROLL - 1) * AUX_THREADS < n16; i += (size_t)UNROLL * AUX_THREADS) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) v[u] = __ldg(src + i + (size_t)u * AUX_THREADS);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) dst[i + (size_t)u * AUX_THREADS] = v[u];
     }
-    for (int q = 0; q < pieces; ++q) {
-      const int nxt = q + COMM_AHEAD;
-      if (nxt < pieces) {
-        // Ring slot of piece `nxt` was last used by piece nxt-COMM_BUFS, stored COMM_BUFS-COMM_AHEAD iterations ago.
-        bulk_wait_read<COMM_BUFS - COMM_AHEAD - 1>();
-        mbar_expect_tx(&bars[nxt % COMM_BUFS], PIECE);
-        bulk_load(smem + (nxt % COMM_BUFS) * COMM_PIECE, src + (size_t)nxt * PIECE, PIECE, &bars[nxt % COMM_BUFS]);
+    for (; i < n16; i += AUX_THREADS) dst[i] = __ldg(src + i);
+    // The stores of all 64 threads are ordered before thread 0's release by the barrier (cumulativity).
+    aux_bar_sync();
+    if (at == 0) {
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      for (int b = lo / BM; b <= (hi - 1) / BM; ++b) {
+        const int r0 = b * BM > lo ? b * BM : lo, r1 = (b + 1) * BM < hi ? (b + 1) * BM : hi;
+        uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + b;
+        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)(r1 - r0)) : "memory");
       }
-      const int slot = q % COMM_BUFS;
-      if (!mbar_wait(&bars[slot], (phase_bits >> slot) & 1, p.wait_limit_ns, abort_flag)) break;
-      phase_bits ^= 1u << slot;
-      bulk_store(dst + (size_t)q * PIECE, smem + slot * COMM_PIECE, PIECE);
-      bulk_commit();
-    }
-    bulk_wait<0>();  // every byte of the unit has been written to the peer
-    fence_proxy_async_all();
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
-    // Tell the peer which 128-row blocks are (partly) complete.
-    const int first_tile = p.ag_parts > 1 ? unit / p.ag_parts : unit * p.ag_tiles_per_unit;
-    const int ntiles = p.ag_parts > 1 ? 1 : p.ag_tiles_per_unit;
-    for (int j = 0; j < ntiles; ++j) {
-      uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + first_tile + j;
-      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)1) : "memory");
     }
   }
-  bulk_wait<0>();
+}
+
+// MODE_RS / MODE_AR, switch path: reduction of the tiles this PE owns.  Work items are RED_ROWS-row slices of the
+// owned tiles, numbered in the order the tiles are produced and dealt round-robin to all auxiliary warps of the grid.
+// A warp waits until all PEs have flagged the tile, then fetches each row slice with one `multimem.ld_reduce` per lane
+// (a warp covers one 512-byte row of the tile per instruction): the switch adds the PEs' copies in fp32 and returns one
+// bf16 result, so the owner receives one tile instead of npes - 1 partials and adds nothing itself.
+//   RS: the sum is written to this PE's output.   AR: it is written once through the multicast alias of the output.
+__device__ void switch_reduce(const FusedParams& p, int aw /*0..1*/, int lane, volatile int* abort_flag) {
+  const int tiles_n = p.N / BN, tmr = (p.M / p.npes) / BM, per_peer = tmr * tiles_n;
+  constexpr int GROUPS = BM / RED_ROWS;
+  const int items = per_peer * GROUPS;
+  const int nwarps = (int)gridDim.x * 2;
+  const size_t pitch = (size_t)p.N * 2;
+  for (int item = (int)blockIdx.x * 2 + aw; item < items; item += nwarps) {
+    const int tile = item / GROUPS, g = item % GROUPS;
+    const int n_tile = tile / tmr, m_local = tile % tmr;
+    // Lane s watches PE s's flag of this tile; afterwards every lane performs an acquire of its own.
+    uint32_t ok = 1;
+    if (lane < p.npes) ok = wait_flag_ge(p.flags_local + (size_t)lane * per_peer + tile, p.epoch, p.wait_limit_ns, abort_flag) ? 1u : 0u;
+    if (!__all_sync(0xffffffffu, ok)) return;
+    {
+      uint64_t v;
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p.flags_local + (size_t)(lane % p.npes) * per_peer + tile) : "memory");
+    }
+    const size_t row0 = (size_t)m_local * BM + (size_t)g * RED_ROWS;
+    const size_t col_bytes = (size_t)n_tile * BN * 2 + (size_t)lane * 16;
+    const char* src = p.stage_mc + ((size_t)p.rank * tmr * BM + row0) * pitch + col_bytes;
+    uint4 v[RED_ROWS];
+#pragma unroll
+    for (int r = 0; r < RED_ROWS; ++r) v[r] = MultimemSum<__nv_bfloat16>::ld(src + (size_t)r * pitch);
+    if (p.mode == BSHMEM_FUSED_AR) {
+      char* dst = p.out_mc + ((size_t)p.rank * tmr * BM + row0) * pitch + col_bytes;
+#pragma unroll
+      for (int r = 0; r < RED_ROWS; ++r) multimem_st_v4(dst + (size_t)r * pitch, v[r]);
+    } else {
+      char* dst = p.out_local + row0 * pitch + col_bytes;
+#pragma unroll
+      for (int r = 0; r < RED_ROWS; ++r) *(uint4*)(dst + (size_t)r * pitch) = v[r];
+    }
+  }
 }
 
 // ------------------------------------------------------------------ host side

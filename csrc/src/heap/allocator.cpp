@@ -1,5 +1,7 @@
 #include "allocator.h"
 
+#include <stdint.h>
+
 #include <algorithm>
 
 namespace bshmem {
@@ -38,6 +40,9 @@ bool HeapAllocator::allocate(size_t size, size_t alignment, size_t* offset_out) 
   if (size == 0) return false;
   if (alignment < kMinAlign) alignment = kMinAlign;
   if (alignment & (alignment - 1)) return false;
+  // A size whose rounding wraps around, or that no heap could hold, is refused before it turns into a
+  // zero-length block that aliases the next allocation.
+  if (size > SIZE_MAX - kMinAlign || round_up(size, kMinAlign) == 0 || round_up(size, kMinAlign) > capacity_) return false;
   size = round_up(size, kMinAlign);
   for (auto it = free_.begin(); it != free_.end(); ++it) {
     size_t start = it->first, len = it->second;

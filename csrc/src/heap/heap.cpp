@@ -24,6 +24,12 @@ static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 void* SymmetricHeap::allocate(size_t size, size_t alignment, int* status) {
   if (status) *status = HEAP_OK;
   if (size == 0) return nullptr;
+  // Nothing larger than the window can ever fit; refusing it here also keeps `size + alignment` below from wrapping.
+  if (size > stride_ || alignment > stride_) {
+    ERROR_PRINT("symmetric heap: request of %zu bytes (alignment %zu) exceeds the %zu-byte window (NVSHMEM_MAX_MEMORY_PER_GPU)", size, alignment, stride_);
+    if (status) *status = HEAP_ERR_OOM;
+    return nullptr;
+  }
   size_t off = 0;
   if (!alloc_.allocate(size, alignment, &off)) {
     // Grow by the request plus its alignment slack, rounded to the growth granule.
@@ -201,6 +207,18 @@ int FdExchange::allgather_fd(int my_fd, uint32_t seq, std::vector<int>* out, int
 int FdExchange::bcast_fd(int root, int* fd_inout, uint32_t seq, int timeout_ms) {
   if (mype_ == root) {
     for (int pe = 0; pe < npes_; ++pe) {
+      if (pe == root) continue;
+      int st = send_fd(pe, *fd_inout, seq, timeout_ms);
+      if (st != HEAP_OK) return st;
+    }
+    return HEAP_OK;
+  }
+  return recv_fd(root, seq, fd_inout, timeout_ms);
+}
+
+int FdExchange::bcast_fd_group(int root, const std::vector<int>& members, int* fd_inout, uint32_t seq, int timeout_ms) {
+  if (mype_ == root) {
+    for (int pe : members) {
       if (pe == root) continue;
       int st = send_fd(pe, *fd_inout, seq, timeout_ms);
       if (st != HEAP_OK) return st;

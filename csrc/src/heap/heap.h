@@ -74,6 +74,22 @@ class SymmetricHeap {
   virtual int attach_external(void* user_ptr, size_t bytes, void** mapped) { (void)user_ptr; (void)bytes; (void)mapped; return HEAP_ERR_ARGS; }
   // Unmaps a range made by attach_external from every window.  Collective.  The offsets are not reused.
   virtual int detach_external(void* mapped, size_t bytes) { (void)mapped; (void)bytes; return HEAP_ERR_ARGS; }
+  // ---- NVLink multicast windows for teams that do not span the world (GPU back end with NVLS only).
+  // Three steps, each followed by an agreement among the callers (the team code votes between them), so that
+  // no PE waits for a descriptor or binds memory after another PE has failed:
+  //   team_mc_create  the team's first member creates a multicast object covering the heap as backed now;
+  //   team_mc_join    the object's descriptor goes to the other members, every member adds its device;
+  //   team_mc_bind    every member binds its own chunks at their heap offsets and maps the object; `*base`
+  //                   is then the multicast address of heap offset 0 for this team and `*bytes` what it covers.
+  // team_mc_drop undoes whatever was done (local calls only).  A window does not follow later growth of the heap.
+  // (reference: src/host/team/team_internal.cpp:749-851, src/host/team/team_internal_nvls.cpp)
+  virtual int team_mc_create(const std::vector<int>& members, uint32_t tag, int* id) { (void)members; (void)tag; *id = -1; return HEAP_ERR_ARGS; }
+  virtual int team_mc_join(int id, int timeout_ms) { (void)id; (void)timeout_ms; return HEAP_ERR_ARGS; }
+  virtual int team_mc_bind(int id, char** base, size_t* bytes) { (void)id; (void)base; (void)bytes; return HEAP_ERR_ARGS; }
+  virtual void team_mc_drop(int id) { (void)id; }
+  // Detaches this PE from every multicast object (unmap, unbind, release) without talking to any other PE:
+  // for a process that is about to leave abnormally.  The multicast window is gone afterwards.
+  virtual void release_multicast_local() {}
   size_t granule() const { return granularity_; }
   // Compares the allocator history digest across PEs (error checks).
   int check_symmetry();
@@ -105,6 +121,8 @@ class FdExchange {
   int allgather_fd(int my_fd, uint32_t seq, std::vector<int>* out, int timeout_ms);
   // PE `root` sends one descriptor to all the others.
   int bcast_fd(int root, int* fd_inout, uint32_t seq, int timeout_ms);
+  // The same among the PEs listed in `members` only (`root` is one of them); the others do not take part.
+  int bcast_fd_group(int root, const std::vector<int>& members, int* fd_inout, uint32_t seq, int timeout_ms);
   void close_all();
 
  private:

@@ -38,6 +38,18 @@ struct Chunk {
   bool external = false;  // caller-owned memory: mapped here, never created here
 };
 
+// A multicast object of a team that does not span the world: one object covers the heap as it was backed
+// when the team was made, every member's chunks bound at their heap offsets.
+struct TeamMc {
+  std::vector<int> members;
+  uint32_t tag = 0;
+  CUmemGenericAllocationHandle mc = 0;
+  char* base = nullptr;
+  size_t bytes = 0;       // size of the object and of the reservation
+  size_t bound = 0;       // bytes bound so far (from offset 0)
+  bool added = false, mapped = false, live = false;
+};
+
 class VmmHeap final : public SymmetricHeap {
  public:
   explicit VmmHeap(bool want_nvls) : want_nvls_(want_nvls) {}
@@ -301,6 +313,7 @@ class VmmHeap final : public SymmetricHeap {
   // Switches the multicast window off for good: earlier chunks lose their
   // binding too, so that `mc_base()` is either valid for the whole heap or null.
   void disable_nvls() {
+    for (size_t i = 0; i < team_mc_.size(); ++i) team_mc_drop((int)i);
     for (auto& c : chunks_) drop_multicast(&c);
     if (mc_base_) d_->cuMemAddressFree_((CUdeviceptr)mc_base_, stride_);
     mc_base_ = nullptr;
@@ -315,6 +328,115 @@ class VmmHeap final : public SymmetricHeap {
     c->mc_bound = c->mc_mapped = false;
   }
 
+  // ---- team windows
+  int team_mc_create(const std::vector<int>& members, uint32_t tag, int* id) override {
+    *id = -1;
+    if (!nvls_ || members.size() < 2) return HEAP_ERR_ARGS;
+    size_t slot = 0;
+    while (slot < team_mc_.size() && team_mc_[slot].live) ++slot;
+    if (slot == team_mc_.size()) team_mc_.emplace_back();
+    TeamMc& t = team_mc_[slot];
+    t = TeamMc{};
+    t.members = members;
+    t.tag = tag;
+    t.bytes = backed_;
+    t.live = true;
+    *id = (int)slot;
+    if (mype_ != members[0]) return HEAP_OK;
+    CUmulticastObjectProp mp{};
+    mp.numDevices = (unsigned)members.size();
+    mp.size = t.bytes;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    CUresult r = d_->cuMulticastCreate_(&t.mc, &mp);
+    if (r != CUDA_SUCCESS) {
+      WARN("NVLS: no multicast object for a team of %zu PEs (%s); the team uses the peer-to-peer algorithms", members.size(), cu_error_string(r).c_str());
+      t.mc = 0;
+      return HEAP_ERR_DRIVER;
+    }
+    return HEAP_OK;
+  }
+
+  int team_mc_join(int id, int timeout_ms) override {
+    if (id < 0 || id >= (int)team_mc_.size() || !team_mc_[id].live) return HEAP_ERR_ARGS;
+    TeamMc& t = team_mc_[id];
+    const int root = t.members[0];
+    int fd = -1;
+    if (mype_ == root) {
+      if (d_->cuMemExportToShareableHandle_(&fd, t.mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) return HEAP_ERR_DRIVER;
+    }
+    // Sequence numbers of team exchanges live in their own range: only the members take part.
+    int st = fdx_.bcast_fd_group(root, t.members, &fd, 0x80000000u | t.tag, timeout_ms);
+    if (st != HEAP_OK) {
+      if (mype_ == root && fd >= 0) ::close(fd);
+      return st;
+    }
+    CUresult r = CUDA_SUCCESS;
+    if (mype_ != root) r = d_->cuMemImportFromShareableHandle_(&t.mc, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+    if (fd >= 0) ::close(fd);
+    if (r != CUDA_SUCCESS) {
+      t.mc = 0;
+      return HEAP_ERR_DRIVER;
+    }
+    if (d_->cuMulticastAddDevice_(t.mc, dev_) != CUDA_SUCCESS) return HEAP_ERR_DRIVER;
+    t.added = true;
+    return HEAP_OK;
+  }
+
+  int team_mc_bind(int id, char** base, size_t* bytes) override {
+    if (id < 0 || id >= (int)team_mc_.size() || !team_mc_[id].live || !team_mc_[id].added) return HEAP_ERR_ARGS;
+    TeamMc& t = team_mc_[id];
+    for (auto& c : chunks_) {
+      if (c.offset + c.bytes > t.bytes) break;
+      if (!c.own) return HEAP_ERR_ARGS;  // a detached external range left a hole: no window
+      CUresult r = d_->cuMulticastBindMem_(t.mc, c.offset, c.own, 0, c.bytes, 0);
+      if (r != CUDA_SUCCESS) {
+        WARN("NVLS: binding a team window failed (%s)", cu_error_string(r).c_str());
+        return HEAP_ERR_DRIVER;
+      }
+      t.bound = c.offset + c.bytes;
+    }
+    CUdeviceptr va = 0;
+    if (d_->cuMemAddressReserve_(&va, t.bytes, granularity_, 0, 0) != CUDA_SUCCESS) return HEAP_ERR_OOM;
+    t.base = (char*)va;
+    CUmemAccessDesc acc{};
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    acc.location.id = ordinal_;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    CUresult r = d_->cuMemMap_(va, t.bytes, 0, t.mc, 0);
+    if (r == CUDA_SUCCESS) {
+      t.mapped = true;
+      r = d_->cuMemSetAccess_(va, t.bytes, &acc, 1);
+    }
+    if (r != CUDA_SUCCESS) {
+      WARN("NVLS: mapping a team window failed (%s)", cu_error_string(r).c_str());
+      return HEAP_ERR_DRIVER;
+    }
+    *base = t.base;
+    *bytes = t.bytes;
+    INFO(SUB_TEAM, "NVLS window for a team of %zu PEs: %zu bytes at %p", t.members.size(), t.bytes, (void*)t.base);
+    return HEAP_OK;
+  }
+
+  void team_mc_drop(int id) override {
+    if (id < 0 || id >= (int)team_mc_.size() || !team_mc_[id].live) return;
+    TeamMc& t = team_mc_[id];
+    if (t.mapped) d_->cuMemUnmap_((CUdeviceptr)t.base, t.bytes);
+    if (t.base) d_->cuMemAddressFree_((CUdeviceptr)t.base, t.bytes);
+    if (t.bound) d_->cuMulticastUnbind_(t.mc, dev_, 0, t.bound);
+    if (t.mc) d_->cuMemRelease_(t.mc);
+    t = TeamMc{};
+  }
+
+  void release_multicast_local() override {
+    if (!window_base_) return;
+    cudaDeviceSynchronize();
+    for (size_t i = 0; i < team_mc_.size(); ++i) team_mc_drop((int)i);
+    for (auto& c : chunks_) drop_multicast(&c);
+    if (mc_base_) d_->cuMemAddressFree_((CUdeviceptr)mc_base_, stride_);
+    mc_base_ = nullptr;
+    nvls_ = false;
+  }
+
   int zero(void* p, size_t bytes) override {
     return cudaMemset(p, 0, bytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess ? HEAP_OK : HEAP_ERR_DRIVER;
   }
@@ -323,6 +445,7 @@ class VmmHeap final : public SymmetricHeap {
     if (!window_base_) return HEAP_OK;
     cudaDeviceSynchronize();
     // Multicast first: no PE may release memory that is still bound.
+    for (size_t i = 0; i < team_mc_.size(); ++i) team_mc_drop((int)i);
     for (auto& c : chunks_) drop_multicast(&c);
     if (boot_ && npes_ > 1) boot_->barrier(boot_);
     for (auto& c : chunks_) {
@@ -348,6 +471,7 @@ class VmmHeap final : public SymmetricHeap {
   bool want_nvls_ = false, nvls_ = false, retained_ctx_ = false;
   CUmemAllocationProp prop_;
   std::vector<Chunk> chunks_;
+  std::vector<TeamMc> team_mc_;
   FdExchange fdx_;
   uint32_t seq_ = 1;
 

@@ -336,6 +336,8 @@ static void* alloc_common(size_t size, size_t alignment, bool zero, const char* 
   if (r.heap->backed() != before) {  // the heap grew: republish its size
     r.dstate.heap_size = r.heap->backed();
     r.dstate.mc_base = (uint64_t)r.heap->mc_base();
+    r.dstate.nvls_world = r.heap->mc_base() != nullptr;
+    teams_drop_windows(r);
     push_device_state();
   }
   if (options().ENABLE_ERROR_CHECKS && r.heap->check_symmetry() != HEAP_OK) return nullptr;
@@ -366,8 +368,19 @@ void* nvshmem_ptr(const void* dest, int pe) {
 void* nvshmemx_mc_ptr(nvshmem_team_t team, const void* ptr) {
   if (!is_initialized()) return nullptr;
   Team* t = team_get(team);
-  if (!t || !t->nvls) return nullptr;
-  return rt().heap->mc_translate(ptr);
+  Runtime& r = rt();
+  if (!t || !t->nvls || !t->mc_base || !r.heap->contains(ptr)) return nullptr;
+  const size_t off = (size_t)((const char*)ptr - r.heap->base());
+  return off < t->mc_bytes ? t->mc_base + off : nullptr;
+}
+void nvshmemx_b200_release_multicast(void) {
+  if (!is_initialized()) return;
+  Runtime& r = rt();
+  r.heap->release_multicast_local();
+  r.dstate.mc_base = 0;
+  r.dstate.nvls_world = 0;
+  teams_refresh_nvls(r);
+  push_device_state();
 }
 // Local buffer registration matters most to NIC transports; with load/store peers every device buffer is
 // already usable as a local source or target.

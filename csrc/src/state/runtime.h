@@ -63,6 +63,9 @@ struct Team {
   std::vector<int> members;  // world PE of each member (always filled)
   bool strided = true;
   bool nvls = false;
+  int mc_id = -1;               // the heap's handle of this team's own multicast window (-1: the world's, or none)
+  char* mc_base = nullptr;      // multicast address of heap offset 0 for this team (null without NVLS)
+  size_t mc_bytes = 0;          // bytes of the heap that the window covers
   int32_t* pe_of_dev = nullptr;  // device copy of `members` for non-strided teams
   uint64_t uniqueid = 0;
   int num_contexts = 0;
@@ -126,6 +129,7 @@ void watchdog_stop(Runtime& r);
 int teams_init(Runtime& r);
 void teams_finalize(Runtime& r);
 void teams_refresh_nvls(Runtime& r);  // after the heap's multicast window changed
+void teams_drop_windows(Runtime& r);  // after the heap grew: team windows cover the old size only and are given up
 Team* team_get(int handle);
 int team_translate_pe(int src_team, int src_pe, int dst_team);
 int team_split_strided(int parent, int start, int stride, int size, uint64_t uniqueid, int num_contexts, int* new_team);

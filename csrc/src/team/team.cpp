@@ -73,7 +73,7 @@ static int publish_team(Runtime& r, Team* t) {
   d.size = t->size;
   d.team_idx = t->idx;
   d.has_nvls = t->nvls;
-  d.mc_base = t->nvls ? (uint64_t)r.heap->mc_base() : 0;
+  d.mc_base = t->nvls ? (uint64_t)t->mc_base : 0;
   team_sync_ptrs(r, t->idx, &d.sync_base, &d.ll_base, &d.scratch_base);
   d.scratch_bytes = r.scratch_bytes;
   d.ll_bytes = r.ll_bytes;
@@ -95,17 +95,45 @@ static int publish_team(Runtime& r, Team* t) {
 
 // After the heap's multicast window changed (it went away, or moved): rewrites the NVLS fields of every team.
 void teams_refresh_nvls(Runtime& r) {
-  const uint64_t mc = (uint64_t)r.heap->mc_base();
+  char* world_mc = r.heap->mc_base();
   for (auto& up : r.teams) {
     Team* t = up.get();
     if (!t || t->idx < 0) continue;
-    if (!mc) t->nvls = false;
+    if (!world_mc) {  // the heap dropped every multicast object, the teams' own windows included
+      t->nvls = false;
+      t->mc_id = -1;
+      t->mc_base = nullptr;
+      t->mc_bytes = 0;
+    } else if (t->nvls && t->mc_id < 0) {
+      t->mc_base = world_mc;
+      t->mc_bytes = r.heap->backed();
+    }
     bshmemi_team_t& d = r.team_pool_host[t->idx];
-    if (d.has_nvls == (t->nvls ? 1 : 0) && d.mc_base == (t->nvls ? mc : 0)) continue;
+    const uint64_t mc = t->nvls ? (uint64_t)t->mc_base : 0;
+    if (d.has_nvls == (t->nvls ? 1 : 0) && d.mc_base == mc) continue;
     d.has_nvls = t->nvls;
-    d.mc_base = t->nvls ? mc : 0;
+    d.mc_base = mc;
     local_write(r.team_pool_dev + t->idx, &d, sizeof(d));
   }
+}
+
+// A team's own window was made for the heap as it was backed then.  Growth is a step of all PEs, so every
+// member gives its window up here, at the same point of the program; the team goes on with the
+// peer-to-peer algorithms.  Teams that use the world's window follow the heap and are not touched.
+void teams_drop_windows(Runtime& r) {
+  int dropped = 0;
+  for (auto& up : r.teams) {
+    Team* t = up.get();
+    if (!t || t->mc_id < 0) continue;
+    r.heap->team_mc_drop(t->mc_id);
+    t->mc_id = -1;
+    t->nvls = false;
+    t->mc_base = nullptr;
+    t->mc_bytes = 0;
+    ++dropped;
+  }
+  if (dropped) WARN("the symmetric heap grew: %d team multicast window(s) were given up (size the heap with NVSHMEM_SYMMETRIC_SIZE before making teams to keep them)", dropped);
+  teams_refresh_nvls(r);
 }
 
 static Team* install_team(Runtime& r, int idx, int start, int stride, int size, const std::vector<int>* members, int parent) {
@@ -131,6 +159,10 @@ static Team* install_team(Runtime& r, int idx, int start, int stride, int size, 
   // The world multicast window sums over every PE, so only teams that span the
   // world in world order may use it.
   t->nvls = r.heap->mc_base() != nullptr && size == r.npes && t->strided && t->start == 0 && t->stride == 1;
+  if (t->nvls) {
+    t->mc_base = r.heap->mc_base();
+    t->mc_bytes = r.heap->backed();
+  }
   if ((int)r.teams.size() <= idx) r.teams.resize(idx + 1);
   r.teams[idx] = std::move(t);
   bitmap_set(r.team_bitmap, idx, false);
@@ -250,6 +282,47 @@ static int agree_on_index(int parent, int* idx_out) {
   return ST_OUT_OF_MEMORY;
 }
 
+// Gives team `t` (just installed, not yet published) an NVLink multicast window of its own: an object that the
+// team's first member creates, that every member joins with its device and binds its part of the heap to.
+// Every member of `parent` calls this, members of the new team or not, because the three agreements
+// (created / all joined / all bound) run over the parent: after a failure anywhere nobody waits for anybody,
+// everyone undoes its part and the team uses the peer-to-peer algorithms
+// (reference: src/host/team/team_internal.cpp:749-851).
+static int team_window_setup(Runtime& r, int parent, Team* t, int idx, const std::vector<int>& members) {
+  const bool member = t != nullptr;
+  int id = -1;
+  uint64_t ok = ~0ull;
+  if (member) {
+    int live = 0;
+    for (auto& up : r.teams) live += up && up->mc_id >= 0;
+    if (live >= (int)options().NVLS_TEAM_WINDOWS || r.heap->team_mc_create(members, (uint32_t)idx, &id) != HEAP_OK) ok = 0;
+  }
+  int st = team_and_reduce(parent, &ok, 1);
+  if (st != ST_SUCCESS) return st;
+  if (ok && member && r.heap->team_mc_join(id, (int)options().BOOTSTRAP_TIMEOUT_MS) != HEAP_OK) ok = 0;
+  if (ok) {
+    st = team_and_reduce(parent, &ok, 1);
+    if (st != ST_SUCCESS) return st;
+  }
+  char* base = nullptr;
+  size_t bytes = 0;
+  if (ok && member && r.heap->team_mc_bind(id, &base, &bytes) != HEAP_OK) ok = 0;
+  if (ok) {
+    st = team_and_reduce(parent, &ok, 1);
+    if (st != ST_SUCCESS) return st;
+  }
+  if (!member) return ST_SUCCESS;
+  if (!ok) {
+    r.heap->team_mc_drop(id);
+    return ST_SUCCESS;
+  }
+  t->nvls = true;
+  t->mc_id = id;
+  t->mc_base = base;
+  t->mc_bytes = bytes;
+  return ST_SUCCESS;
+}
+
 int team_create_from_members(int parent, const std::vector<int>& world_members, uint64_t uniqueid, int* new_team) {
   Runtime& r = rt();
   *new_team = BSHMEM_TEAM_INVALID;
@@ -257,9 +330,21 @@ int team_create_from_members(int parent, const std::vector<int>& world_members, 
   int st = agree_on_index(parent, &idx);
   if (st != ST_SUCCESS) return st;
   bool member = std::find(world_members.begin(), world_members.end(), r.mype) != world_members.end();
+  Team* t = nullptr;
   if (member) {
-    Team* t = install_team(r, idx, world_members[0], 1, (int)world_members.size(), &world_members, parent);
+    t = install_team(r, idx, world_members[0], 1, (int)world_members.size(), &world_members, parent);
     t->uniqueid = uniqueid;
+  }
+  // A team that spans the world in world order shares the world's window (install_team); any other team of
+  // two or more PEs gets a window of its own where the heap has NVLS.  All inputs of this decision are the
+  // same on every member of the parent.
+  bool spans_world = (int)world_members.size() == r.npes;
+  for (int i = 0; i < (int)world_members.size() && spans_world; ++i) spans_world = world_members[i] == i;
+  if (r.have_gpu && r.heap->mc_base() && world_members.size() >= 2 && !spans_world && options().NVLS_TEAM_WINDOWS > 0) {
+    st = team_window_setup(r, parent, t, idx, world_members);
+    if (st != ST_SUCCESS) return st;
+  }
+  if (member) {
     st = publish_team(r, t);
     if (st != ST_SUCCESS) return st;
     *new_team = idx;
@@ -329,6 +414,7 @@ int team_destroy(int handle) {
     if (r.have_gpu) cudaFree(t->pe_of_dev);
     else delete[] t->pe_of_dev;
   }
+  if (t->mc_id >= 0) r.heap->team_mc_drop(t->mc_id);
   r.teams[handle].reset();
   bitmap_set(r.team_bitmap, handle, true);
   return ST_SUCCESS;

@@ -13,7 +13,7 @@ bool parse_size(const char* text, size_t* out) {
   if (!text || !*text) return false;
   char* end = nullptr;
   double v = strtod(text, &end);
-  if (end == text || v < 0 || std::isnan(v)) return false;
+  if (end == text || v < 0 || std::signbit(v) || std::isnan(v)) return false;  // "-0" is a negative number too
   while (*end == ' ') ++end;
   double mult = 1;
   switch (*end) {

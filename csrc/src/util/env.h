@@ -36,6 +36,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(BOOTSTRAP_UID_SESSION_ID,  std::string, Str, "",            Bootstrap,   "Fixed <address>:<port> of the UID root, replacing the unique-id exchange") \
   X(BOOTSTRAP_TIMEOUT_MS,  long,        Long, 60000,            Bootstrap,   "Milliseconds a bootstrap socket operation may block before it fails") \
   X(DISABLE_NVLS,          bool,        Bool, false,            OpenShmem,   "Do not create NVLink multicast objects even where supported") \
+  X(NVLS_TEAM_WINDOWS,     long,        Long, 16,               OpenShmem,   "NVLink multicast windows a PE may hold for teams that do not span the world (0: such teams never get one)") \
   X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Use the host-memory heap back end instead of CUDA virtual memory management") \
   X(DISABLE_P2P,           bool,        Bool, false,            Hidden,      "Treat peers as not load/store reachable (init then fails: no remote transport is built)") \
   X(DISABLE_CE_COLLECTIVES,bool,        Bool, false,            Collectives, "Never use copy engines for on-stream alltoall/fcollect/broadcast") \

@@ -151,6 +151,7 @@ def load() -> C.CDLL:
     sig("nvshmemx_b200_set_wait_timeout_ms", None, C.c_long)
     sig("nvshmemx_b200_topology", C.c_char_p)
     sig("nvshmemx_b200_heap_info", u64, i32)
+    sig("nvshmemx_b200_release_multicast", None)
     _lib = lib
     return lib
 

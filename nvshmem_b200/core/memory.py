@@ -16,7 +16,10 @@ import warnings
 from ..bindings import host as H
 from .types import BufferKind, NvshmemError, NvshmemInvalid
 
-_tracked: dict[int, dict] = {}  # ptr -> {buffer, ref_count, kind, freed}
+_tracked: dict[int, dict] = {}  # ptr -> {buffer, ref_count, kind, freed}: allocations (NORMAL) and registered ranges (EXTERNAL)
+# Views (peer and multicast aliases) are counted apart from allocations, keyed by (address, kind): the view of
+# the calling PE itself has the allocation's own address and must never touch the allocation's record.
+_views: dict[tuple[int, int], dict] = {}
 
 
 class Buffer:
@@ -66,15 +69,20 @@ def buffer(size: int, alignment: int = 0, zero: bool = False) -> Buffer:
 
 
 def free(buf: Buffer) -> None:
-    """Collective: returns a buffer obtained from :func:`buffer`.  Views (peer, multicast) only drop a reference."""
+    """Collective: returns a buffer obtained from :func:`buffer`.  Freeing a view (peer, multicast) only drops the
+    view's own reference and never touches the allocation it aliases (as in nvshmem4py)."""
+    if buf.kind in (BufferKind.PEER, BufferKind.MULTIMEM):
+        key = (buf.ptr, int(buf.kind))
+        rec = _views.get(key)
+        if rec is None:
+            raise NvshmemInvalid(f"{buf!r} is not a live view")
+        rec["ref_count"] -= 1
+        if rec["ref_count"] <= 0:
+            del _views[key]
+        return
     rec = _tracked.get(buf.ptr)
     if rec is None or rec["freed"]:
         raise NvshmemInvalid(f"{buf!r} is not a live symmetric buffer")
-    if rec["kind"] in (BufferKind.PEER, BufferKind.MULTIMEM):
-        rec["ref_count"] -= 1
-        if rec["ref_count"] <= 0:
-            del _tracked[buf.ptr]
-        return
     rec["ref_count"] -= 1
     if rec["ref_count"] > 0:
         return
@@ -89,6 +97,7 @@ def _free_all_tracked() -> None:
     for ptr in sorted(p for p, r in _tracked.items() if r["kind"] == BufferKind.NORMAL and not r["freed"]):
         H.load().nvshmem_free(C.c_void_p(ptr))
     _tracked.clear()
+    _views.clear()
 
 
 def get_peer_buffer(buf: Buffer, pe: int) -> Buffer:
@@ -97,7 +106,7 @@ def get_peer_buffer(buf: Buffer, pe: int) -> Buffer:
     if not ptr:
         raise NvshmemInvalid(f"{buf!r} is not symmetric or PE {pe} is out of range")
     view = Buffer(ptr, buf.size, BufferKind.PEER, buf.device_memory, owner=buf)
-    rec = _tracked.setdefault(ptr, {"buffer": view, "ref_count": 0, "kind": BufferKind.PEER, "freed": False})
+    rec = _views.setdefault((ptr, int(BufferKind.PEER)), {"buffer": view, "ref_count": 0})
     rec["ref_count"] += 1
     return view
 
@@ -108,7 +117,7 @@ def get_multicast_buffer(team: int, buf: Buffer) -> Buffer:
     if not ptr:
         raise NvshmemInvalid("no multicast mapping: NVLS is unavailable or the team does not span the multicast group")
     view = Buffer(ptr, buf.size, BufferKind.MULTIMEM, True, owner=buf)
-    rec = _tracked.setdefault(ptr, {"buffer": view, "ref_count": 0, "kind": BufferKind.MULTIMEM, "freed": False})
+    rec = _views.setdefault((ptr, int(BufferKind.MULTIMEM)), {"buffer": view, "ref_count": 0})
     rec["ref_count"] += 1
     return view
 

@@ -1,11 +1,13 @@
 """Tensor-parallel GEMMs fused with their collective (``libbshmem_fused.so``).
 
 * :func:`gemm` – plain ``x @ w.T`` on the tcgen05 kernel (what one GPU runs).
-* :class:`GemmReduceScatter` – row-parallel linear: every rank multiplies its K-slice and the
-  kernel's epilogue pushes partial tiles into the owning rank's receive slots and reduces there
-  (``mode="rs"``), or additionally broadcasts the reduced tile to all ranks (``mode="ar"``).
-* :class:`AllGatherGemm` – column-parallel linear: sender CTAs spread the local activation shard
-  to all peers while the GEMM consumes shards as they land.
+* :class:`GemmReduceScatter` – row-parallel linear: every rank multiplies its K-slice; with an NVLink
+  multicast window the partial tiles stay in the producing GPU's staging buffer and the owner of a
+  tile reads their sum through the switch (``multimem.ld_reduce``) inside the same kernel, otherwise
+  the epilogue pushes partial tiles into the owning rank's receive slots and reduces there
+  (``mode="rs"``); ``mode="ar"`` additionally delivers the reduced tile to all ranks.
+* :class:`AllGatherGemm` – column-parallel linear: two spare warps of every CTA spread the local
+  activation shard to all peers while the GEMM consumes shards as they land.
 
 Weights use torch's Linear layout ``[out_features, in_features]``; activations are ``[tokens,
 in_features]``; everything is bf16 with fp32 accumulation.  The collective variants keep their
@@ -32,7 +34,8 @@ class _Args(C.Structure):
     _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("out", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("rank", C.c_int), ("npes", C.c_int),
                 ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
                 ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
-                ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p)]
+                ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p),
+                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p)]
 
 
 _ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
@@ -108,6 +111,7 @@ class GemmReduceScatter:
     ``forward(x, w)``: ``x`` is ``[M, K_local]``, ``w`` ``[N, K_local]``; returns this rank's
     ``[M/npes, N]`` rows of the summed product (``mode="rs"``) or the whole ``[M, N]`` (``"ar"``).
     The output tensor is owned by the object and overwritten by the next call.
+    ``use_multicast=False`` forces the push path even where the heap has a multicast window.
     """
 
     def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0, use_multicast: bool = True):
@@ -123,24 +127,30 @@ class GemmReduceScatter:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.device = dev
         tiles = (self.rows // 128) * (N // 256)
-        if self.npes > 1:
-            # two generations of receive slots: a fast peer may already be pushing call k+1
-            self.recv = core.tensor((2, self.npes, self.rows, N), torch.bfloat16)
-            self.flags = core.tensor((self.npes * max(tiles, 1),), torch.int64, zero=True)
-        else:
-            self.recv = self.flags = None
+        self.recv = self.flags = None
+        self.switch_path = False
+        self._stage_mc = self._out_mc = 0
         if mode == "ar" and self.npes > 1:
             self.out = core.tensor((M, N), torch.bfloat16)
         else:
             self.out = torch.empty(self.rows if mode == "rs" else M, N, dtype=torch.bfloat16, device=dev)
         self._peer = {}
         if self.npes > 1:
+            mc_ptr = H.load().nvshmemx_mc_ptr
+            # Two generations of partial-tile storage by call parity: a fast peer may already be in call k+1.
+            # With a multicast window it is one [M, N] staging buffer per generation that only its owner writes
+            # (the tile owners read the sum of all PEs' copies through the switch); without one, receive slots
+            # [npes, M/npes, N] that the peers push into.
+            probe = core.tensor((2, M, N), torch.bfloat16)
+            if use_multicast:
+                self._stage_mc = int(mc_ptr(0, C.c_void_p(probe.data_ptr())) or 0)
+                if mode == "ar":
+                    self._out_mc = int(mc_ptr(0, C.c_void_p(self.out.data_ptr())) or 0)
+            self.switch_path = bool(self._stage_mc) and (mode == "rs" or bool(self._out_mc))
+            self.recv = probe  # the same bytes serve as staging buffer or as receive slots: 2 * M * N elements either way
+            self.flags = core.tensor((self.npes * max(tiles, 1),), torch.int64, zero=True)
             for q in range(self.npes):
                 self._peer[q] = (core.peer_ptr(self.recv, q), core.peer_ptr(self.flags, q), core.peer_ptr(self.out, q) if mode == "ar" else 0)
-            # All-reduce: the reduced tiles go out through the NVLink-multicast alias of `out` where there is one.
-            self._out_mc = 0
-            if mode == "ar" and use_multicast:
-                self._out_mc = int(H.load().nvshmemx_mc_ptr(0, C.c_void_p(self.out.data_ptr())) or 0)
             core.barrier_all()
             torch.cuda.synchronize()
 
@@ -155,9 +165,13 @@ class GemmReduceScatter:
         a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
         a.error_flag = _error_flag(self.device).data_ptr()
         if self.npes > 1:
-            half = (self.epoch & 1) * self.npes * self.rows * self.N * 2
-            a.recv_local = self.recv.data_ptr() + half
+            half = (self.epoch & 1) * self.M * self.N * 2
             a.flags_local = self.flags.data_ptr()
+            if self.switch_path:
+                a.stage_local = self.recv.data_ptr() + half
+                a.stage_mc = self._stage_mc + half
+            else:
+                a.recv_local = self.recv.data_ptr() + half
             for q in range(self.npes):
                 a.recv_peer[q] = self._peer[q][0] + half
                 a.flags_peer[q] = self._peer[q][1]
@@ -189,13 +203,13 @@ class AllGatherGemm:
     is issued on the stream before each launch so that no peer overwrites a buffer still being read.
     """
 
-    def __init__(self, M: int, K: int, n_comm: int = 16, wait_limit_ms: int = 0):
+    def __init__(self, M: int, K: int, wait_limit_ms: int = 0):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
         if self.npes > MAX_PES:
             raise FusedGemmError(f"at most {MAX_PES} PEs")
-        self.M, self.K, self.n_comm, self.wait_limit_ms = M, K, n_comm, wait_limit_ms
+        self.M, self.K, self.wait_limit_ms = M, K, wait_limit_ms
         self.rows = M // self.npes
         self.epoch = 0
         self.device = torch.device("cuda", torch.cuda.current_device())
@@ -220,7 +234,7 @@ class AllGatherGemm:
         a = _Args()
         a.A, a.B, a.out = self.gathered.data_ptr(), w.data_ptr(), self.out.data_ptr()
         a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, N, self.K, self.rank, self.npes, MODES["ag"]
-        a.epoch, a.wait_limit_ms, a.n_comm = self.epoch, self.wait_limit_ms, self.n_comm
+        a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
         a.error_flag = _error_flag(self.device).data_ptr()
         if self.npes > 1:
             a.ag_flags_local = self.flags.data_ptr()

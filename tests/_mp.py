@@ -33,7 +33,13 @@ def run_workers(func: str, nprocs: int, gpu: bool = False, env: dict | None = No
     deadline = time.time() + timeout
     # Fail fast: once a rank has exited with an error the others can only time out, so give them a
     # short grace period and stop exactly the children started here.
+    # A rank whose heap is bound to an NVLink multicast object is never killed outright: it gets SIGTERM, which the
+    # worker turns into "detach from the multicast objects, then exit", and a grace period longer than the bound
+    # of the device-side waits, so that it leaves by itself.  SIGKILL right away is for runs with NVLS off only.
+    nvls_may_be_on = gpu and (env or {}).get("NVSHMEM_DISABLE_NVLS") != "1"
+    grace = 45 if nvls_may_be_on else 15
     first_failure = None
+    terminated_at = None
     while True:
         codes = [p.poll() for p in procs]
         if all(c is not None for c in codes):
@@ -41,7 +47,12 @@ def run_workers(func: str, nprocs: int, gpu: bool = False, env: dict | None = No
         now = time.time()
         if first_failure is None and any(c not in (None, 0) for c in codes):
             first_failure = now
-        if now > deadline or (first_failure is not None and now - first_failure > 15):
+        if terminated_at is None and (now > deadline or (first_failure is not None and now - first_failure > 15)):
+            terminated_at = now
+            for p in procs:
+                if p.poll() is None:
+                    p.terminate() if nvls_may_be_on else p.kill()
+        if terminated_at is not None and now - terminated_at > grace:
             for p in procs:
                 if p.poll() is None:
                     p.kill()
@@ -53,6 +64,6 @@ def run_workers(func: str, nprocs: int, gpu: bool = False, env: dict | None = No
         outs.append(out)
         codes.append(p.returncode)
     if not expect_fail:
-        order = sorted(range(nprocs), key=lambda i: (codes[i] in (0, -9), i))  # the rank that failed by itself first
+        order = sorted(range(nprocs), key=lambda i: (codes[i] in (0, -9, -15), i))  # the rank that failed by itself first
         assert all(c == 0 for c in codes), "worker failed:\n" + "\n".join(f"--- rank {i} rc={codes[i]}\n{outs[i][-2500:]}" for i in order)
     return codes, outs

@@ -69,6 +69,23 @@ def test_random_sequences_keep_the_heap_consistent(seq):
         lib.bshmem_test_alloc_delete(b)
 
 
+def test_sizes_whose_rounding_overflows_are_refused():
+    """A size within 511 bytes of SIZE_MAX rounds up to zero: it must be refused, not recorded as a zero-length block
+    that the next allocation would alias; the same for sizes beyond what the heap holds."""
+    lib = _lib()
+    a = C.c_void_p(lib.bshmem_test_alloc_new(1 << 20))
+    try:
+        for huge in ((1 << 64) - 100, (1 << 64) - 511, (1 << 64) - 512, (1 << 63), (1 << 20) + 1):
+            assert lib.bshmem_test_alloc_malloc(a, huge, 0) < 0, huge
+            assert lib.bshmem_test_alloc_in_use(a) == 0 and lib.bshmem_test_alloc_check(a) == 0
+        first = lib.bshmem_test_alloc_malloc(a, 512, 0)
+        second = lib.bshmem_test_alloc_malloc(a, 512, 0)
+        assert first == 0 and second == 512
+        assert lib.bshmem_test_alloc_malloc(a, 1 << 20, 0) < 0  # no longer fits
+    finally:
+        lib.bshmem_test_alloc_delete(a)
+
+
 @settings(max_examples=300, deadline=None)
 @given(st.integers(0, 1 << 40), st.sampled_from(["", "k", "K", "m", "M", "g", "G", "t", "T"]))
 def test_size_parser_round_trips_every_suffix(value, suffix):

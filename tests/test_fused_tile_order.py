@@ -68,34 +68,44 @@ def test_cta_pairs_get_two_row_tiles_of_one_column_block(mode, npes, M, N):
             assert a[1] == b[1] and a[2] == b[2] and b[0] == a[0] + 1 and a[3] % 2 == 0, (rank, u, a, b)
 
 
-def test_all_gather_sender_plan_invariants():
-    """The split of a PE's shard over the sender CTAs: units cover the shard exactly, nest with the 128-row blocks
-    (arrival counters are per block), are copied in power-of-two pieces, and come in even numbers for CTA pairs."""
+def test_all_gather_row_slices_cover_every_block_exactly():
+    """The all-gather mode splits a PE's shard by rows over all CTAs of the grid and counts delivered rows per
+    128-row block: the slices must tile the shard, and every block must collect exactly 128 rows."""
     lib = _lib()
-    lib.bshmem_fused_test_ag_plan.argtypes = [C.c_int] * 5 + [C.POINTER(C.c_longlong)]
-    out = (C.c_longlong * 6)()
-    checked = 0
-    for npes in (2, 3, 4, 8):
-        for tmr in (1, 2, 3, 4, 6, 8, 16):
-            for K in (64, 192, 1024, 8192):
-                for req in (0, 1, 2, 3, 5, 8, 16, 24, 32):
-                    for pair in (0, 1):
-                        M = npes * tmr * BM
-                        assert lib.bshmem_fused_test_ag_plan(M, K, npes, req, pair, out) == 0, (npes, tmr, K, req, pair)
-                        n_comm, is_pair, unit, piece, parts, per_unit = [int(v) for v in out]
-                        rows = tmr * BM
-                        shard = rows * K * 2
-                        assert 1 <= n_comm <= (req or 16) and n_comm * unit == shard
-                        assert piece & (piece - 1) == 0 and 16 <= piece <= 16384 and unit % piece == 0
-                        if n_comm >= tmr:
-                            assert n_comm % tmr == 0 and parts == n_comm // tmr and per_unit == 1
-                            assert rows % n_comm == 0 and BM % (rows // n_comm) == 0      # a unit is a whole fraction of one block
-                        else:
-                            assert tmr % n_comm == 0 and parts == 1 and per_unit == tmr // n_comm
-                        if is_pair:
-                            assert pair and tmr % 2 == 0 and n_comm % 2 == 0
-                        checked += 1
-    assert checked > 1000
-    # the benchmark's all-gather shape: 16 senders, half a block each, 16 KB pieces
-    assert lib.bshmem_fused_test_ag_plan(8192, 8192, 8, 0, 1, out) == 0
-    assert [int(v) for v in out] == [16, 1, 1 << 20, 16384, 2, 1]
+    lib.bshmem_fused_test_ag_slice.argtypes = [C.c_int] * 3 + [C.POINTER(C.c_int)]
+    out = (C.c_int * 2)()
+    for rows in (128, 256, 384, 1024, 4096):
+        for grid in (1, 2, 3, 7, 64, 132, 148, 1000):
+            per_block = [0] * (rows // BM)
+            nxt = 0
+            for b in range(grid):
+                assert lib.bshmem_fused_test_ag_slice(rows, grid, b, out) == 0
+                lo, hi = out[0], out[1]
+                assert lo == nxt and hi >= lo
+                nxt = hi
+                for blk in range(lo // BM, (hi - 1) // BM + 1 if hi > lo else lo // BM):
+                    per_block[blk] += min((blk + 1) * BM, hi) - max(blk * BM, lo)
+            assert nxt == rows and per_block == [BM] * (rows // BM), (rows, grid, per_block)
+    assert lib.bshmem_fused_test_ag_slice(128, 4, 4, out) != 0
+
+
+@pytest.mark.parametrize("mode,npes,M,N", [(RS, 2, 1024, 768), (RS, 8, 8192, 1024), (AR, 4, 2048, 512), (RS, 3, 768, 256)])
+def test_switch_path_walks_the_output_in_one_order_on_every_pe(mode, npes, M, N):
+    """Switch path of RS / AR: the order does not depend on the rank, m runs fastest over ALL rows (so the owner changes
+    every M/npes rows and every wave of CTAs holds tiles of every owner), and the flag index is the position of the
+    tile among its owner's tiles in that same order (what the reducing warps count through)."""
+    lib = _lib()
+    SW = 0x100
+    tmr, tiles_n, tiles_m = M // npes // BM, N // BN, M // BM
+    orders = [_order(lib, mode | SW, M, N, rank, npes) for rank in range(npes)]
+    assert all(o == orders[0] for o in orders)
+    tiles = orders[0]
+    assert [(m, n) for m, n, *_ in tiles] == [(t % tiles_m, t // tiles_m) for t in range(len(tiles))]
+    for owner in range(npes):
+        mine = [t for t in tiles if t[2] == owner]
+        assert [t[4] for t in mine] == list(range(tmr * tiles_n))
+        assert all(m == owner * tmr + ml for m, _, _, ml, _ in mine)
+    if tmr % 2 == 0:
+        for u in range(0, len(tiles), 2):
+            a, b = tiles[u], tiles[u + 1]
+            assert a[1] == b[1] and a[2] == b[2] and b[0] == a[0] + 1

@@ -114,6 +114,19 @@ def python_layer_on_host_heap():
     # a peer view aliases the neighbour's memory (process-shared mapping on this back end)
     peer = nv.get_peer_tensor(t, right)
     assert torch.equal(peer, (torch.arange(64, dtype=torch.float32).view(4, 16) + 1000 * me) * 2)
+    # A view never holds the allocation: views of every PE (the caller's own has the allocation's address) are taken
+    # and dropped, and the collective free of the parent still runs on every PE.
+    from nvshmem_b200.core import memory as _mem
+    parent = nv.tensor((32,), torch.float32)
+    views = [nv.get_peer_tensor(parent, p) for p in range(n)]
+    assert views[me].data_ptr() == parent.data_ptr() and _mem._tracked[parent.data_ptr()]["ref_count"] == 1
+    nv.free_tensor(views[me])
+    assert parent.data_ptr() in _mem._tracked
+    nv.free_tensor(parent)
+    assert parent.data_ptr() not in _mem._tracked, "the parent's free was skipped because of a view"
+    for p in range(n):
+        if p != me:
+            nv.free_tensor(views[p])
     # teams through the Python layer
     if n >= 2:
         evens = nv.team_split_strided(nv.Teams.TEAM_WORLD, 0, 2, (n + 1) // 2)
@@ -1127,30 +1140,42 @@ def fused_gemm_collectives():
     from nvshmem_b200.ops import fused_gemm as fg
     n = WORLD
     torch.manual_seed(100)
-    for (M, N, Kl) in ((128 * n, 256, 64), (256 * n, 512, 192), (1024 * n, 768, 256)):
+    paths_seen = []
+    for (M, N, Kl) in ((128 * n, 256, 64), (256 * n, 512, 192), (1024 * n, 768, 256), (384 * n, 2048, 128)):
         xs = [(torch.randn(M, Kl, device="cuda")).to(torch.bfloat16) for _ in range(n)]   # same seed on all ranks: everyone knows all inputs
         ws = [(torch.randn(N, Kl, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
         full = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
         tol = full.abs().max().item() * 2 ** -6 + 1e-2
         rows = M // n
-        rs = fg.GemmReduceScatter(M, N, mode="rs", wait_limit_ms=5000)
-        for it in range(3):  # several calls: epochs and the two receive generations
-            out = rs(xs[RANK], ws[RANK])
-            torch.cuda.synchronize()
-            fg.check_errors()
-            err = (out.float() - full[RANK * rows:(RANK + 1) * rows]).abs().max().item()
-            assert err <= tol, ("rs", M, N, Kl, it, err, tol)
-        rs.close()
-        ar = fg.GemmReduceScatter(M, N, mode="ar", wait_limit_ms=5000)
-        for it in range(2):
-            out = ar(xs[RANK], ws[RANK])
-            nv.barrier_all()
-            torch.cuda.synchronize()
-            fg.check_errors()
-            err = (out.float() - full).abs().max().item()
-            assert err <= tol, ("ar", M, N, Kl, it, err, tol)
-        ar.close()
-    for (M, K, Nl) in ((128 * n, 64, 256), (256 * n, 512, 512), (1024 * n, 1024, 256)):
+        # With a multicast window both paths are checked: partials reduced inside the switch, and pushed partials.
+        for use_mc in (True, False):
+            rs = fg.GemmReduceScatter(M, N, mode="rs", wait_limit_ms=5000, use_multicast=use_mc)
+            if not use_mc and paths_seen and not paths_seen[-1]:
+                rs.close()
+                break  # no multicast window: the first pass already was the push path
+            paths_seen.append(rs.switch_path)
+            for it in range(4):  # several calls: epochs and the two generations of partial-tile storage
+                scale = 1.0 + it
+                out = rs((xs[RANK].float() * scale).to(torch.bfloat16), ws[RANK])
+                torch.cuda.synchronize()
+                fg.check_errors()
+                err = (out.float() - scale * full[RANK * rows:(RANK + 1) * rows]).abs().max().item()
+                assert err <= tol * scale, ("rs", use_mc, M, N, Kl, it, err, tol)
+            rs.close()
+            ar = fg.GemmReduceScatter(M, N, mode="ar", wait_limit_ms=5000, use_multicast=use_mc)
+            assert ar.switch_path == paths_seen[-1]
+            for it in range(3):
+                scale = 1.0 + it
+                out = ar((xs[RANK].float() * scale).to(torch.bfloat16), ws[RANK])
+                nv.barrier_all()
+                torch.cuda.synchronize()
+                fg.check_errors()
+                err = (out.float() - scale * full).abs().max().item()
+                assert err <= tol * scale, ("ar", use_mc, M, N, Kl, it, err, tol)
+            ar.close()
+    if os.environ.get("BSHMEM_EXPECT_SWITCH_PATH") == "1":
+        assert any(paths_seen), "the heap has no multicast window: the switch path did not run"
+    for (M, K, Nl) in ((128 * n, 64, 256), (256 * n, 512, 512), (1024 * n, 1024, 256), (384 * n, 8192, 256)):
         x_full = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         w = (torch.randn(Nl, K, device="cuda") * 0.05).to(torch.bfloat16)
         rows = M // n
@@ -1236,7 +1261,31 @@ def rank_leaves_between_steps():
     teardown(nv)
 
 
+def _leave_multicast():
+    """Detaches this rank from every NVLink multicast object without any collective step."""
+    try:
+        from nvshmem_b200.bindings import host as H
+        H.load().nvshmemx_b200_release_multicast()
+    except Exception:
+        pass
+
+
+def _on_sigterm(signum, frame):
+    raise SystemExit(143)
+
+
 if __name__ == "__main__":
+    import signal
+    import traceback
+    signal.signal(signal.SIGTERM, _on_sigterm)
     name = sys.argv[1]
-    WORKERS[name]()
+    try:
+        WORKERS[name]()
+    except BaseException:
+        # A rank that fails must not vanish while its memory is bound to a multicast object that the other
+        # ranks' GPUs still use: unbind first (local calls only), then let the interpreter exit.
+        traceback.print_exc()
+        sys.stdout.flush()
+        _leave_multicast()
+        os._exit(1)
     print(f"rank {RANK}: {name} ok", flush=True)
