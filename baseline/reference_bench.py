@@ -4,8 +4,10 @@ build in ``baseline/_ref`` (NVIDIA NVSHMEM, built from its own sources with its 
 Per step and rank: cuBLAS bf16 GEMM (``torch.matmul``) writes the partial product into a buffer on the
 reference's symmetric heap, then the reference library's own
 ``nvshmemx_bfloat16_sum_reducescatter_on_stream`` reduces and scatters it on the same stream.  The
-library is driven through its public host API (unique-id init, ``nvshmem_malloc``, the typed on-stream
-collective) with ctypes; none of this repository's kernels, heap or Python layer is on that path.
+end-to-end run is the same stack of tensor-parallel MLP blocks as the other arm's, built from the reference's
+``nvshmemx_bfloat16_fcollect_on_stream`` (all-gather), cuBLAS GEMMs, torch's tanh-GELU and the reference's
+reduce-scatter.  The library is driven through its public host API (unique-id init, ``nvshmem_malloc``, the
+typed on-stream collectives) with ctypes; none of this repository's kernels, heap or Python layer is on that path.
 """
 from __future__ import annotations
 
@@ -66,7 +68,7 @@ def run(args, M, N, K_LOCAL) -> dict:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     os.environ["NVSHMEM_BOOTSTRAP_UID_PLUGIN"] = str(plugin)
-    os.environ.setdefault("NVSHMEM_SYMMETRIC_SIZE", "2G")
+    os.environ.setdefault("NVSHMEM_SYMMETRIC_SIZE", "3G")
     os.environ.setdefault("NVSHMEM_BOOTSTRAP_UID_SOCK_IFNAME", "lo")
     lib = C.CDLL(str(lib_path), mode=C.RTLD_GLOBAL)
     lib.nvshmem_malloc.restype = C.c_void_p
@@ -74,6 +76,8 @@ def run(args, M, N, K_LOCAL) -> dict:
     lib.nvshmem_free.argtypes = [C.c_void_p]
     lib.nvshmemx_bfloat16_sum_reducescatter_on_stream.restype = C.c_int
     lib.nvshmemx_bfloat16_sum_reducescatter_on_stream.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.nvshmemx_bfloat16_fcollect_on_stream.restype = C.c_int
+    lib.nvshmemx_bfloat16_fcollect_on_stream.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
 
     uid = _UniqueId()
     uid.version = (1 << 16) + C.sizeof(_UniqueId)
@@ -110,10 +114,54 @@ def run(args, M, N, K_LOCAL) -> dict:
             raise RuntimeError(f"reference reducescatter returned {rc}")
         return out
 
-    line = timed_runs(step, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=0)
+    class Stack:
+        """L tensor-parallel MLP blocks on the reference's collectives: the token shard lives in a symmetric buffer,
+        fcollect gathers it, cuBLAS multiplies, torch applies the GELU, cuBLAS multiplies again into the symmetric
+        partial buffer and the reference's reduce-scatter writes the next block's token shard."""
+
+        def __init__(self, layers):
+            from bench import HIDDEN
+            self.layers = layers
+            self.kernels_per_forward = 0  # none of this repository's kernels
+            gen = torch.Generator(device=dev)
+            gen.manual_seed(99 + rank)
+            self.w_up = [torch.empty(K_LOCAL, HIDDEN, device=dev, dtype=torch.float32).normal_(0.0, 0.02, generator=gen).to(torch.bfloat16) for _ in range(layers)]
+            self.w_down = [torch.empty(HIDDEN, K_LOCAL, device=dev, dtype=torch.float32).normal_(0.0, 0.02, generator=gen).to(torch.bfloat16) for _ in range(layers)]
+            self.s_ptr = lib.nvshmem_malloc(rows * HIDDEN * 2)
+            self.g_ptr = lib.nvshmem_malloc(M * HIDDEN * 2)
+            self.r_ptrs = [lib.nvshmem_malloc(rows * HIDDEN * 2) for _ in range(2)]
+            if not self.s_ptr or not self.g_ptr or not all(self.r_ptrs):
+                raise RuntimeError("reference nvshmem_malloc failed")
+            self.input_shard = torch.as_tensor(_Sym(self.s_ptr, rows * HIDDEN * 2), device=dev).view(torch.bfloat16).view(rows, HIDDEN)
+            self.gathered = torch.as_tensor(_Sym(self.g_ptr, M * HIDDEN * 2), device=dev).view(torch.bfloat16).view(M, HIDDEN)
+            self.results = [torch.as_tensor(_Sym(q, rows * HIDDEN * 2), device=dev).view(torch.bfloat16).view(rows, HIDDEN) for q in self.r_ptrs]
+            self.h = torch.empty(M, K_LOCAL, device=dev, dtype=torch.bfloat16)
+            self.hidden = HIDDEN
+
+        def forward(self, b):
+            stream = torch.cuda.current_stream().cuda_stream
+            for l in range(self.layers):
+                rc = lib.nvshmemx_bfloat16_fcollect_on_stream(0, self.g_ptr, self.s_ptr, rows * self.hidden, stream)
+                torch.matmul(self.gathered, self.w_up[l].t(), out=self.h)
+                h = torch.nn.functional.gelu(self.h, approximate="tanh")
+                torch.matmul(h, self.w_down[l].t(), out=partial)
+                dst = self.s_ptr if l + 1 < self.layers else self.r_ptrs[b]
+                rc |= lib.nvshmemx_bfloat16_sum_reducescatter_on_stream(0, dst, p_ptr, rows * self.hidden, stream)
+                if rc != 0:
+                    raise RuntimeError(f"a reference collective returned {rc}")
+            return self.results[b]
+
+        def free(self):
+            for q in [self.s_ptr, self.g_ptr] + self.r_ptrs:
+                lib.nvshmem_free(q)
+
+    stack = Stack(args.layers)
+    line = timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=0)
     line["impl"] = "reference"
-    line["config"]["reference_path"] = "torch.matmul (cuBLAS) + libnvshmem_host.so nvshmemx_bfloat16_sum_reducescatter_on_stream"
+    line["path"] = ("torch.matmul (cuBLAS) + libnvshmem_host.so nvshmemx_bfloat16_sum_reducescatter_on_stream; end to end: + "
+                    "nvshmemx_bfloat16_fcollect_on_stream and torch GELU")
     torch.cuda.synchronize()
+    stack.free()
     lib.nvshmem_free(p_ptr)
     lib.nvshmem_free(o_ptr)
     lib.nvshmemx_hostlib_finalize()

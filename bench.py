@@ -5,17 +5,22 @@ Per rank: x[M=8192, K=3584] @ w[N=8192, K=3584]^T in bf16 with fp32 accumulation
 ranks and scattered by rows (weak scaling: the K-slice per rank is fixed, so per-GPU work is
 constant).  The metric is the whole-job TFLOP/s = n_gpus * 2*M*N*K / step time.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--repeats R] [--layers L]
 
 For N > 1 launch with torchrun (one rank per GPU); rank 0 prints one JSON line.
-Timing: CUDA events on the launching stream around exactly K steps, barrier +
-synchronize on both sides, max over ranks.  Inputs rotate through several
-buffer sets whose total size exceeds the 126 MB L2.  SM clocks and throttle
-reasons are sampled with nvidia-smi during the timed region.
 
-The `e2e` number drives the same step through the public Python API with the
-activations of every step coming from pinned host memory (copy overlapped on a
-second stream) and a checksum of the result read back to the host every step.
+Device-timed value: CUDA events on the launching stream around exactly K steps, barrier +
+synchronize on both sides, max over ranks; that region is repeated R times in the same process and
+the median region is reported (all regions are listed under `repeats`), so that the number is a
+steady-state one.  Inputs rotate through several buffer sets whose total size exceeds the 126 MB L2.
+SM clocks and throttle reasons are sampled through NVML over all regions.
+
+End-to-end value (`e2e`): the same GEMM shapes as a unit of model work through the public API, a
+stack of L tensor-parallel MLP blocks (all-gather -> GEMM + GELU, GEMM -> reduce-scatter; hidden
+8192, 3584 FFN columns per rank, 8192 tokens).  Every step copies this rank's token shard from
+pinned host memory to the device, runs the L blocks, and copies the rank's output shard back to
+pinned host memory; copies of neighbouring steps overlap the compute on side streams, and the timed
+region ends when the last result is on the host.  Its TFLOP/s counts the 2 L GEMMs of a step.
 """
 from __future__ import annotations
 
@@ -23,12 +28,12 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
 
 M, N, K_LOCAL = 8192, 8192, 3584
+HIDDEN = N            # MLP stack of the end-to-end run: hidden size = N, FFN columns per rank = K_LOCAL
 BASELINE_VALUE = None  # the reference publishes no number for this metric
 
 
@@ -39,12 +44,15 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sets", type=int, default=3, help="input buffer sets rotated between steps")
+    ap.add_argument("--repeats", type=int, default=10, help="how many times the timed region of --steps steps is run (median reported)")
+    ap.add_argument("--layers", type=int, default=8, help="MLP blocks per step of the end-to-end run")
+    ap.add_argument("--e2e-repeats", type=int, default=3)
     return ap.parse_args()
 
 
 class ClockSampler:
     """Samples SM clock, power and throttle reasons of one GPU through NVML (read-only queries) from a
-    thread while a region runs; falls back to polling nvidia-smi when the NVML module is missing."""
+    thread while a region runs."""
 
     REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
 
@@ -95,8 +103,10 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["NVML unavailable"]}
         self._stop.set()
         self.thread.join(timeout=2)
-        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.sm_max, "samples": len(self.sm),
-                "power_w_max": round(max(self.power), 1) if self.power else None, "reasons": sorted(self.reasons)}
+        # "under load": samples taken while the GPU drew more than half of the highest power seen
+        loaded = [c for c, p in zip(self.sm, self.power) if self.power and p >= 0.5 * max(self.power)]
+        return {"sm_mhz": statistics.median(loaded or self.sm) if self.sm else None, "sm_max_mhz": self.sm_max, "samples": len(self.sm),
+                "samples_under_load": len(loaded), "power_w_max": round(max(self.power), 1) if self.power else None, "reasons": sorted(self.reasons)}
 
 
 def reference_arm(args):
@@ -106,9 +116,10 @@ def reference_arm(args):
     return reference_bench.run(args, M, N, K_LOCAL)
 
 
-def timed_runs(step, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step):
-    """Times `step(x, w) -> out` (a) on device-resident inputs and (b) end to end from pinned host
-    memory with a checksum read back every step.  Returns the JSON line (without `impl`)."""
+def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step):
+    """Times `step(x, w) -> out` on device-resident inputs (R regions of --steps steps), then the end-to-end run of
+    `stack` (an object with `input_shard`, `forward(out_index) -> tensor`, `kernels_per_forward`).  Returns the JSON
+    line (without `impl`).  Both arms of the benchmark go through this function."""
     import torch
     import torch.distributed as dist
 
@@ -124,69 +135,91 @@ def timed_runs(step, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(values):
+        t = torch.tensor(values, device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
     warm = max(3, args.warmup)
     for i in range(warm):
         step(xs[i % sets], ws[i % sets])
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(args.steps):
-        step(xs[i % sets], ws[i % sets])
-    end.record()
-    barrier()
-    ms = start.elapsed_time(end)
-    clocks = sampler.stop()
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
+    regions = []
+    for r in range(max(1, args.repeats)):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            step(xs[i % sets], ws[i % sets])
+        end.record()
+        barrier()
+        regions.append(start.elapsed_time(end))
+    regions = max_over_ranks(regions)               # per region: the slowest rank
+    per_step = sorted(ms / args.steps for ms in regions)
+    ms_per_step = statistics.median(per_step)
     flops_per_rank = 2.0 * M * N * K_LOCAL
     value = world * flops_per_rank / (ms_per_step * 1e-3) / 1e12
+    del xs, ws
 
-    # ---------------- end to end: pinned host input every step, checksum read back every step
-    host_x = [torch.randn(M, K_LOCAL, dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(2)]
-    dev_x = [torch.empty(M, K_LOCAL, device=dev, dtype=torch.bfloat16) for _ in range(2)]
-    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
-    copy_stream = torch.cuda.Stream()
-    main_stream = torch.cuda.current_stream()
-    copied = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
+    # ---------------- end to end: L MLP blocks per step, token shard in from pinned host memory, output shard back out
+    rows = M // world
+    host_in = [torch.randn(rows, HIDDEN, dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_out = [torch.empty(rows, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_in = [torch.empty(rows, HIDDEN, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    in_stream, out_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    h2d_done = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    fwd_done = [torch.cuda.Event() for _ in range(2)]
+    d2h_done = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_steps(n):
-        # Step i+1's input is copied on the copy stream while step i computes.
-        with torch.cuda.stream(copy_stream):
-            dev_x[0].copy_(host_x[0], non_blocking=True)
-            copied[0].record(copy_stream)
         for i in range(n):
-            cur, nxt = i & 1, (i + 1) & 1
-            if i + 1 < n:
-                with torch.cuda.stream(copy_stream):
-                    if i >= 1:
-                        copy_stream.wait_event(consumed[nxt])
-                    dev_x[nxt].copy_(host_x[nxt], non_blocking=True)
-                    copied[nxt].record(copy_stream)
-            main_stream.wait_event(copied[cur])
-            out = step(dev_x[cur], ws[i % sets])
-            consumed[cur].record(main_stream)
-            host_out.copy_(out.float().sum().reshape(1), non_blocking=True)
-            main_stream.synchronize()  # the result of every step reaches the host
-        return float(host_out.item())
+            b = i & 1
+            if i >= 2:
+                d2h_done[b].synchronize()       # at most two steps in flight; step i-2's result is on the host
+            with torch.cuda.stream(in_stream):  # host -> device copy of this step's tokens, ahead of the compute
+                if i >= 2:
+                    in_stream.wait_event(in_free[b])
+                dev_in[b].copy_(host_in[b], non_blocking=True)
+                h2d_done[b].record(in_stream)
+            main.wait_event(h2d_done[b])
+            stack.input_shard.copy_(dev_in[b], non_blocking=True)
+            in_free[b].record(main)
+            if i >= 2:
+                main.wait_event(d2h_done[b])    # the output buffer of step i-2 has been read out
+            out = stack.forward(b)
+            fwd_done[b].record(main)
+            with torch.cuda.stream(out_stream):  # device -> host copy of this step's result shard
+                out_stream.wait_event(fwd_done[b])
+                host_out[b].copy_(out, non_blocking=True)
+                d2h_done[b].record(out_stream)
+        main.wait_event(d2h_done[(n - 1) & 1])
+        if n >= 2:
+            main.wait_event(d2h_done[(n - 2) & 1])
 
-    e2e_steps(3)
+    e2e_steps(max(3, min(args.warmup, 5)))
     barrier()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    e2e_steps(args.steps)
-    t1.record()
-    barrier()
-    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_ms_per_step = float(e2e_ms.item()) / args.steps
-    e2e_value = world * flops_per_rank / (e2e_ms_per_step * 1e-3) / 1e12
+    e2e_regions = []
+    for r in range(max(1, args.e2e_repeats)):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t0.record()
+        in_stream.wait_event(t0)
+        e2e_steps(args.steps)
+        t1.record()   # after the main stream has waited for the last device -> host copies
+        barrier()
+        e2e_regions.append(t0.elapsed_time(t1))
+    clocks = sampler.stop()
+    e2e_regions = max_over_ranks(e2e_regions)
+    e2e_per_step = sorted(ms / args.steps for ms in e2e_regions)
+    e2e_ms_per_step = statistics.median(e2e_per_step)
+    L = stack.layers
+    e2e_value = world * (2 * L * flops_per_rank) / (e2e_ms_per_step * 1e-3) / 1e12
+    checksum = float(host_out[(args.steps - 1) & 1].float().abs().mean())
     return {
         "metric": "fused_gemm_reduce_scatter_tflops",
         "value": round(value, 2),
@@ -201,11 +234,16 @@ def timed_runs(step, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_
         "dtype": "bf16",
         "data": "synthetic (seeded randn activations, N(0,0.02) weights, random init)",
         "config": {"model": "tp_row_parallel_gemm_reduce_scatter", "M": M, "N": N, "K_per_rank": K_LOCAL, "global_batch": M, "seq_len": 1,
-                   "parallelism": f"tp{world}", "l2": f"inputs rotate over {sets} buffer sets ({sets * (M + N) * K_LOCAL * 2 >> 20} MiB > 126 MiB L2)"},
+                   "parallelism": f"tp{world}", "l2": f"inputs rotate over {sets} buffer sets ({sets * (M + N) * K_LOCAL * 2 >> 20} MiB > 126 MiB L2)",
+                   "e2e_model": f"{L} x tp_mlp(hidden {HIDDEN}, ffn {K_LOCAL} per rank, {M} tokens): all-gather->GEMM+GELU, GEMM->reduce-scatter"},
+        "repeats": {"regions": len(per_step), "ms_per_step_min": round(per_step[0], 5), "ms_per_step_median": round(ms_per_step, 5),
+                    "ms_per_step_max": round(per_step[-1], 5)},
         "clocks": clocks,
-        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms_per_step, 5), "h2d_bytes_per_step": M * K_LOCAL * 2,
-                "d2h_bytes_per_step": 4},
-        "gpu_launches": args.steps * launches_per_step,
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms_per_step, 5), "h2d_bytes_per_step": rows * HIDDEN * 2,
+                "d2h_bytes_per_step": rows * HIDDEN * 2, "layers": L, "regions": len(e2e_per_step), "ms_per_step_min": round(e2e_per_step[0], 5),
+                "ms_per_step_max": round(e2e_per_step[-1], 5), "gpu_launches": args.steps * len(e2e_per_step) * stack.kernels_per_forward,
+                "output_abs_mean": round(checksum, 6)},
+        "gpu_launches": args.steps * len(per_step) * launches_per_step,
     }
 
 
@@ -232,7 +270,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    # The benchmark's buffers (two generations of partial tiles, the gathered activations) are backed at start-up.
+    os.environ.setdefault("NVSHMEM_SYMMETRIC_SIZE", "2G")
     import nvshmem_b200.core as nv
+    from nvshmem_b200.models.tp_mlp import TensorParallelMLPStack
     from nvshmem_b200.ops import fused_gemm as fg
 
     if world > 1:
@@ -240,10 +281,28 @@ def main():
     else:
         nv.init(device=local_rank, uid=nv.get_unique_id(), rank=0, nranks=1)
     op = fg.GemmReduceScatter(M, N, mode="rs")
-    # one fused tcgen05 kernel per step (libbshmem_fused.so): GEMM, peer pushes and the reduction
-    line = timed_runs(lambda x, w: op(x, w), args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=1)
+
+    class Stack:
+        """The public model object behind the interface the timing harness wants."""
+
+        def __init__(self):
+            self.model = TensorParallelMLPStack(HIDDEN, K_LOCAL * world, M, args.layers, seed=99 + rank)
+            self.layers = args.layers
+            self.kernels_per_forward = self.model.kernels_per_forward
+            self.outs = [torch.empty_like(self.model.out) for _ in range(2)]
+            self.input_shard = self.model.input_shard
+
+        def forward(self, b):
+            self.model.out = self.outs[b]
+            return self.model.forward()
+
+    stack = Stack()
+    # one fused tcgen05 kernel per step (libbshmem_fused.so): GEMM, partial tiles, flags and the reduction
+    line = timed_runs(lambda x, w: op(x, w), stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=1)
     line["impl"] = "ours"
+    line["path"] = "one fused kernel per step; partial tiles reduced by " + ("the switch (multimem.ld_reduce)" if op.switch_path else ("pushes to the owner" if world > 1 else "nobody (one PE)"))
     fg.check_errors(dev)
+    stack.model.close()
     op.close()
     nv.finalize()
     if world > 1:

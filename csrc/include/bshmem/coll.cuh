@@ -84,11 +84,13 @@ __device__ __forceinline__ int poll_ge(const uint64_t* flag, uint64_t want) {
 // member one hop away); thread and warp scope on teams beyond 32 members fall back to radix-k
 // dissemination.  Returns 0, or 1 if a member did not arrive within the wait bound.
 //
-// QUIET = false (sync): the release fence has GPU scope.  It orders this group's earlier stores to its
-// own memory (which peers read through this GPU's L2) before the flags, and does not wait for stores
-// still in flight to other GPUs, as the sync contract allows.  QUIET = true (barrier): system scope,
-// which also completes the group's earlier stores to peers; it costs a link round trip when such
-// stores are outstanding.
+// The release fence has system scope: the observers of the flags are threads on other GPUs, and only a
+// scope that contains both sides orders the data they read afterwards (peer pulls, multimem.ld_reduce) in
+// the PTX memory model.  It also completes the group's earlier stores to peers, so sync and barrier
+// (QUIET = true) cost the same here.  NVSHMEM_SYNC_GPU_SCOPE_RELEASE=1 selects a GPU-scope fence for sync
+// instead: it orders this group's earlier stores to its own memory, which peers read through this GPU's
+// L2, and skips the wait for stores in flight to other GPUs (a few hundred nanoseconds when there are
+// some); that relies on how the hardware serves peer reads, not on the memory model, hence off by default.
 template <int SCOPE, bool QUIET = false>
 __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) {
   const int size = t->size, me = t->my_pe;
@@ -100,7 +102,7 @@ __device__ __forceinline__ int team_sync(const bshmemi_team_t* t, int slot = 0) 
   uint64_t* flags = (uint64_t*)t->sync_base + (size_t)slot * size;
   int err = 0;
   if (rank == 0) {  // release: the group's earlier stores (ordered before this by the group barrier)
-    if (QUIET) fence_sys();
+    if (QUIET || !bshmemi_state_d.sync_gpu_release) fence_sys();
     else asm volatile("fence.acq_rel.gpu;" ::: "memory");
   }
   group_sync<SCOPE>();

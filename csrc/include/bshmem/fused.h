@@ -13,6 +13,7 @@ extern "C" {
 #define BSHMEM_FUSED_MAX_PES 8
 
 enum { BSHMEM_FUSED_PLAIN = 0, BSHMEM_FUSED_RS = 1, BSHMEM_FUSED_AR = 2, BSHMEM_FUSED_AG = 3 };
+enum { BSHMEM_FUSED_ACT_NONE = 0, BSHMEM_FUSED_ACT_GELU_TANH = 1 };
 enum {
   BSHMEM_FUSED_OK = 0,
   BSHMEM_FUSED_ERR_ARGS = 1,
@@ -57,6 +58,9 @@ typedef struct {
    * recv_local / recv_peer / out_peer are then unused. */
   void* stage_local;
   void* stage_mc;
+  /* Activation applied to the fp32 result before it is rounded to bf16 (BSHMEM_FUSED_ACT_*); PLAIN and AG only
+   * (a partial sum of RS / AR cannot be activated). */
+  int act;
 } bshmem_fused_args_t;
 
 /* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */

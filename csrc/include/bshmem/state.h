@@ -92,6 +92,8 @@ typedef struct {
   int32_t barrier_dissem_kval, barrier_tg_dissem_kval, bcast_tree_kval, debug_checks;
   uint64_t reduce_nvls_threshold, reduce_oneshot_threshold;
   uint64_t fcollect_ll_threshold, fcollect_nvls_threshold, reducescatter_nvls_threshold;
+  int32_t sync_gpu_release;   /* 1: team sync releases with a GPU-scope fence (NVSHMEM_SYNC_GPU_SCOPE_RELEASE) */
+  int32_t reserved0;
 } bshmemi_state_t;
 
 #define BSHMEM_JOB_GPU_LDST_ATOMICS 0 /* every peer reachable by ld/st/atomics (NVSwitch) */

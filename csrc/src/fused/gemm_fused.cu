@@ -226,6 +226,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
             else mbar_arrive(&acc_empty[acc]);
           }
         }
+        if (p.act == BSHMEM_FUSED_ACT_GELU_TANH) {
+          // tanh-approximated GELU on the fp32 accumulators, before the single rounding to bf16.
+#pragma unroll
+          for (int j = 0; j < EPI_COLS; ++j) f[j] = gelu_tanh(f[j]);
+        }
         if (reduce_mode && own) {
           const size_t rows_per_pe = (size_t)p.M / p.npes;
           const size_t grow = (size_t)ti.m_local * BM + row;
@@ -367,6 +372,9 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K; p.rank = a->rank; p.npes = npes; p.mode = mode;
   p.epoch = a->epoch;
+  if (a->act != BSHMEM_FUSED_ACT_NONE && a->act != BSHMEM_FUSED_ACT_GELU_TANH) return BSHMEM_FUSED_ERR_ARGS;
+  if (a->act != BSHMEM_FUSED_ACT_NONE && (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1) return BSHMEM_FUSED_ERR_ARGS;  // partial sums
+  p.act = a->act;
   p.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
   p.error_flag = a->error_flag;
   const int rows_per_pe = a->M / npes;

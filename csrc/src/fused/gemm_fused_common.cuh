@@ -46,6 +46,7 @@ struct alignas(64) FusedParams {
   int* error_flag;
   uint64_t epoch, wait_limit_ns;
   int M, N, K, rank, npes, mode;
+  int act;                                   // BSHMEM_FUSED_ACT_*: applied to the fp32 result in the epilogue (PLAIN / AG)
   int sw_reduce;                             // RS/AR: partial tiles stay local and the owner fetches their sum through the switch
 };
 
@@ -83,6 +84,14 @@ __host__ __device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int
   ti.m_tile = ti.peer * tmr + ti.m_local;
   ti.idx_in_peer = within;
   return ti;
+}
+
+// GELU, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), with the hardware tanh approximation.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
 }
 
 __device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t want, uint64_t limit_ns, volatile int* abort_flag) {
@@ -126,8 +135,8 @@ __device__ void ag_send_rows(const FusedParams& p, int at /*0..63*/, volatile in
   const size_t n16 = (size_t)(hi - lo) * row_bytes / 16;  // K is a multiple of 64: rows are whole 16-byte pieces
   const uint4* src = (const uint4*)(p.ag_src + (size_t)lo * row_bytes);
   constexpr int UNROLL = 8;
+  (void)abort_flag;  // nothing here waits for a peer, and both warps must reach every barrier: no early exit
   for (int o = 1; o < p.npes; ++o) {
-    if (*abort_flag) return;
     const int peer = (p.rank + o) % p.npes;
     uint4* dst = (uint4*)(p.ag_dst[peer] + (size_t)lo * row_bytes);
     size_t i = at;
@@ -174,6 +183,7 @@ __device__ void switch_reduce(const FusedParams& p, int aw /*0..1*/, int lane, v
     {
       uint64_t v;
       asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p.flags_local + (size_t)(lane % p.npes) * per_peer + tile) : "memory");
+      (void)v;
     }
     const size_t row0 = (size_t)m_local * BM + (size_t)g * RED_ROWS;
     const size_t col_bytes = (size_t)n_tile * BN * 2 + (size_t)lane * 16;

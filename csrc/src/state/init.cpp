@@ -311,6 +311,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   d.fcollect_algo = (int)o.FCOLLECT_ALGO;
   d.reducescatter_algo = (int)o.REDUCESCATTER_ALGO;
   d.bcast_algo = (int)o.BCAST_ALGO;
+  d.sync_gpu_release = o.SYNC_GPU_SCOPE_RELEASE ? 1 : 0;
   d.barrier_dissem_kval = (int)std::max<long>(o.BARRIER_DISSEM_KVAL, 2);
   d.barrier_tg_dissem_kval = (int)std::max<long>(o.BARRIER_TG_DISSEM_KVAL, 2);
   d.bcast_tree_kval = (int)std::max<long>(o.BCAST_TREE_KVAL, 2);

@@ -47,6 +47,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(CUMEM_HANDLE_TYPE,     std::string, Str,  "FILE_DESCRIPTOR",Memory,      "Shareable handle type for heap chunks: FILE_DESCRIPTOR")    \
   X(HEAP_BACKEND,          std::string, Str,  "AUTO",           Memory,      "AUTO, VMM (GPU memory) or HOST (process-shared host memory, needs no GPU)") \
   X(MAX_CTAS,              long,        Long, 0,                Collectives, "CTAs used by multi-CTA on-stream collectives (0: chosen per collective)") \
+  X(SYNC_GPU_SCOPE_RELEASE,bool,        Bool, false,            Collectives, "Team sync releases with a GPU-scope fence instead of a system-scope one (faster by a link round trip when puts are in flight; outside the PTX memory model for cross-GPU observers)") \
   X(BARRIER_DISSEM_KVAL,   long,        Long, 2,                Collectives, "Radix of the dissemination barrier for thread and warp scope") \
   X(BARRIER_TG_DISSEM_KVAL,long,        Long, 2,                Collectives, "Radix of the dissemination barrier for block scope when peers are not all load/store reachable") \
   X(REDUCE_ALGO,           long,        Long, 0,                Collectives, "Force an allreduce algorithm: 0 auto, 1 one-shot pull, 2 two-shot, 3 NVLS one-shot, 4 NVLS two-shot, 5 LL one-shot push") \

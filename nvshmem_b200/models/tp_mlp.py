@@ -33,3 +33,63 @@ class TensorParallelMLP(torch.nn.Module):
 
     def close(self):
         self.cache.close()
+
+
+class TensorParallelMLPStack:
+    """``layers`` tensor-parallel MLP blocks applied one after the other to a token shard, forward only
+    (what a serving step of the MLP part of a transformer does).
+
+    Per block: fused all-gather -> GEMM with the tanh-GELU applied in the GEMM's epilogue, then fused
+    GEMM -> reduce-scatter whose result is written straight into this rank's shard of the all-gather
+    buffer, where the next block picks it up: two kernels and one team sync per block, and no copy
+    between blocks.  The blocks share one all-gather buffer and one set of reduce-scatter buffers.
+
+    ``input_shard`` is where the caller puts this rank's ``[tokens/npes, hidden]`` tokens (it may be the
+    target of a host-to-device copy); ``forward()`` returns this rank's ``[tokens/npes, hidden]`` result in a
+    tensor owned by the object.
+    """
+
+    def __init__(self, hidden: int, ffn: int, tokens: int, layers: int, init_std: float = 0.02, seed: int | None = None):
+        from .. import core
+        from ..ops import fused_gemm as fg
+        self.npes, self.rank = core.n_pes(), core.my_pe()
+        assert ffn % self.npes == 0 and tokens % self.npes == 0
+        self.hidden, self.ffn, self.tokens, self.layers = hidden, ffn, tokens, layers
+        dev = torch.device("cuda", torch.cuda.current_device())
+        gen = torch.Generator(device=dev)
+        if seed is not None:
+            gen.manual_seed(seed)
+        fl = ffn // self.npes
+        self.w_up = [torch.empty(fl, hidden, device=dev, dtype=torch.float32).normal_(0.0, init_std, generator=gen).to(torch.bfloat16) for _ in range(layers)]
+        self.w_down = [torch.empty(hidden, fl, device=dev, dtype=torch.float32).normal_(0.0, init_std, generator=gen).to(torch.bfloat16) for _ in range(layers)]
+        self.ag = fg.AllGatherGemm(tokens, hidden)
+        self.rs = fg.GemmReduceScatter(tokens, hidden, mode="rs")
+        self.h = torch.empty(tokens, fl, dtype=torch.bfloat16, device=dev)
+        self.out = torch.empty(tokens // self.npes, hidden, dtype=torch.bfloat16, device=dev)
+        self.kernels_per_forward = layers * (3 if self.npes > 1 else 2)  # GEMM, GEMM (+ the team sync before each all-gather)
+
+    @property
+    def input_shard(self) -> torch.Tensor:
+        return self.ag.shard
+
+    @torch.no_grad()
+    def forward(self) -> torch.Tensor:
+        for l in range(self.layers):
+            self.ag(self.w_up[l], out=self.h, act="gelu_tanh")
+            self.rs(self.h, self.w_down[l], out=self.ag.shard if l + 1 < self.layers else self.out)
+        return self.out
+
+    __call__ = forward
+
+    @torch.no_grad()
+    def reference(self, x_full: torch.Tensor, w_up_full: list, w_down_full: list) -> torch.Tensor:
+        """The same stack in fp32 with plain torch on full weights, rounding to bf16 where the kernels do."""
+        x = x_full.float()
+        for w1, w2 in zip(w_up_full, w_down_full):
+            h = torch.nn.functional.gelu(x @ w1.float().t(), approximate="tanh").to(torch.bfloat16).float()
+            x = (h @ w2.float().t()).to(torch.bfloat16).float()
+        return x
+
+    def close(self):
+        self.ag.close()
+        self.rs.close()

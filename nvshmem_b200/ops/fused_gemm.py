@@ -23,6 +23,7 @@ from ..bindings import host as H
 
 MAX_PES = 8
 MODES = {"plain": 0, "rs": 1, "ar": 2, "ag": 3}
+ACTS = {None: 0, "none": 0, "gelu_tanh": 1}
 _lib = None
 
 
@@ -35,7 +36,7 @@ class _Args(C.Structure):
                 ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
                 ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
                 ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p),
-                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p)]
+                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p), ("act", C.c_int)]
 
 
 _ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
@@ -89,14 +90,23 @@ def _check_operands(x: torch.Tensor, w: torch.Tensor) -> None:
         raise FusedGemmError("operands must be contiguous")
 
 
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
-    """``x[M,K] @ w[N,K].T`` -> bf16 ``[M,N]`` on the tcgen05/TMEM kernel."""
+def _check_out(out: torch.Tensor, rows: int, cols: int) -> None:
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (rows, cols) or not out.is_contiguous() or out.data_ptr() % 16:
+        raise FusedGemmError(f"`out` must be a contiguous, 16-byte aligned bfloat16 tensor of shape {(rows, cols)}")
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0, act: str | None = None) -> torch.Tensor:
+    """``act(x[M,K] @ w[N,K].T)`` -> bf16 ``[M,N]`` on the tcgen05/TMEM kernel; ``act`` is None or ``"gelu_tanh"``
+    (applied to the fp32 accumulators in the epilogue)."""
     _check_operands(x, w)
     M, K = x.shape
     N = w.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    else:
+        _check_out(out, M, N)
     a = _Args()
+    a.act = ACTS[act]
     a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
     a.M, a.N, a.K, a.rank, a.npes, a.mode = M, N, K, 0, 1, MODES["plain"]
     a.epoch, a.max_ctas = 1, max_ctas
@@ -110,8 +120,9 @@ class GemmReduceScatter:
 
     ``forward(x, w)``: ``x`` is ``[M, K_local]``, ``w`` ``[N, K_local]``; returns this rank's
     ``[M/npes, N]`` rows of the summed product (``mode="rs"``) or the whole ``[M, N]`` (``"ar"``).
-    The output tensor is owned by the object and overwritten by the next call.
-    ``use_multicast=False`` forces the push path even where the heap has a multicast window.
+    Without ``out=`` the output tensor is owned by the object and overwritten by the next call; with ``out=``
+    (reduce-scatter only) the result is written there, e.g. straight into the shard of the next layer's
+    all-gather buffer.  ``use_multicast=False`` forces the push path even where the heap has a multicast window.
     """
 
     def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0, use_multicast: bool = True):
@@ -154,13 +165,19 @@ class GemmReduceScatter:
             core.barrier_all()
             torch.cuda.synchronize()
 
-    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         _check_operands(x, w)
         if x.shape[0] != self.M or w.shape[0] != self.N:
             raise FusedGemmError("operand shapes differ from the ones this object was built for")
+        if out is None:
+            out = self.out
+        elif self.mode != "rs":
+            raise FusedGemmError("`out=` is for the reduce-scatter mode (the all-reduce output lives in symmetric memory)")
+        else:
+            _check_out(out, self.rows, self.N)
         self.epoch += 1
         a = _Args()
-        a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), self.out.data_ptr()
+        a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
         a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, self.N, x.shape[1], self.rank, self.npes, MODES[self.mode]
         a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
         a.error_flag = _error_flag(self.device).data_ptr()
@@ -181,7 +198,7 @@ class GemmReduceScatter:
         if self.mode == "ar" and self.npes > 1:
             # Tiles written by the other PEs are complete once everyone's kernel has ended.
             self.core.barrier_all(stream=torch.cuda.current_stream())
-        return self.out
+        return out
 
     __call__ = forward
 
@@ -225,14 +242,21 @@ class AllGatherGemm:
         self.shard = self.gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
         self.out = None
 
-    def forward(self, w: torch.Tensor) -> torch.Tensor:
+    def forward(self, w: torch.Tensor, out: torch.Tensor | None = None, act: str | None = None) -> torch.Tensor:
+        """``act(gathered @ w.T)``.  Without ``out=`` the result tensor is owned by the object and overwritten by the
+        next call; ``act`` is None or ``"gelu_tanh"`` (fused into the epilogue)."""
         _check_operands(self.gathered, w)
         N = w.shape[0]
-        if self.out is None or self.out.shape[1] != N:
-            self.out = torch.empty(self.M, N, dtype=torch.bfloat16, device=self.device)
+        if out is None:
+            if self.out is None or self.out.shape[1] != N:
+                self.out = torch.empty(self.M, N, dtype=torch.bfloat16, device=self.device)
+            out = self.out
+        else:
+            _check_out(out, self.M, N)
         self.epoch += 1
         a = _Args()
-        a.A, a.B, a.out = self.gathered.data_ptr(), w.data_ptr(), self.out.data_ptr()
+        a.act = ACTS[act]
+        a.A, a.B, a.out = self.gathered.data_ptr(), w.data_ptr(), out.data_ptr()
         a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, N, self.K, self.rank, self.npes, MODES["ag"]
         a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
         a.error_flag = _error_flag(self.device).data_ptr()
@@ -243,7 +267,7 @@ class AllGatherGemm:
                 a.ag_flags_peer[q] = self._peer[q][1]
             self.core.sync_all()  # every rank has finished reading the previous gathered buffer
         _launch(a, torch.cuda.current_stream().cuda_stream)
-        return self.out
+        return out
 
     __call__ = forward
 

@@ -9,6 +9,8 @@ Activations are sharded by rows (tokens) between layers, Megatron sequence-paral
 
 The backward passes reuse the same fused kernels with the roles swapped (the gradient of an
 all-gather is a reduce-scatter and vice versa); weight gradients use the plain tcgen05 GEMM.
+Every fused result is written by the kernel straight into a tensor of its own (``out=``): no
+result is copied out of an operator-owned buffer.
 """
 from __future__ import annotations
 
@@ -54,8 +56,9 @@ class _ColumnParallelFn(torch.autograd.Function):
     def forward(ctx, x_shard, weight, cache: _OpCache, M: int, owner):
         K = x_shard.shape[1]
         ag = cache.all_gather(M, K, owner)
-        ag.shard.copy_(x_shard)
-        y = ag(weight).clone()
+        if x_shard.data_ptr() != ag.shard.data_ptr():  # a producer may have written the shard in place
+            ag.shard.copy_(x_shard)
+        y = ag(weight, out=torch.empty(M, weight.shape[0], dtype=torch.bfloat16, device=weight.device))
         ctx.save_for_backward(weight)
         ctx.cache, ctx.M, ctx.K = cache, M, K
         ctx.x_full = ag.gathered  # valid until the next forward of the same shape
@@ -70,7 +73,7 @@ class _ColumnParallelFn(torch.autograd.Function):
         dw = fg.gemm(_t(dy), _t(x_full))
         # dX_shard[M/n, K] = reduce_scatter(dY[M, Nl] @ W[Nl, K])
         rs = ctx.cache.reduce_scatter(ctx.M, ctx.K)
-        dx = rs(dy, _t(weight)).clone()
+        dx = rs(dy, _t(weight), out=torch.empty(rs.rows, ctx.K, dtype=torch.bfloat16, device=dy.device))
         return dx, dw, None, None, None
 
 
@@ -79,7 +82,7 @@ class _RowParallelFn(torch.autograd.Function):
     def forward(ctx, x, weight, cache: _OpCache):
         M, N = x.shape[0], weight.shape[0]
         rs = cache.reduce_scatter(M, N)
-        y = rs(x.contiguous(), weight).clone()
+        y = rs(x.contiguous(), weight, out=torch.empty(rs.rows, N, dtype=torch.bfloat16, device=x.device))
         ctx.save_for_backward(x, weight)
         ctx.cache, ctx.M, ctx.N = cache, M, N
         return y
@@ -90,7 +93,8 @@ class _RowParallelFn(torch.autograd.Function):
         # dX[M, Kl] = all_gather(dY_shard)[M, N] @ W[N, Kl]
         ag = ctx.cache.all_gather(ctx.M, ctx.N)
         ag.shard.copy_(dy_shard)
-        dx = ag(_t(weight)).clone()
+        wt = _t(weight)
+        dx = ag(wt, out=torch.empty(ctx.M, wt.shape[0], dtype=torch.bfloat16, device=dy_shard.device))
         # dW[N, Kl] = dY_full^T @ X
         dw = fg.gemm(_t(ag.gathered), _t(x))
         return dx, dw, None

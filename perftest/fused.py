@@ -3,7 +3,7 @@
   row parallel   : x[M, K/n] @ w[N, K/n]^T -> reduce-scatter      ours: one fused kernel; baseline: matmul + reduce_scatter_tensor
   column parallel: all-gather(x[M/n, K]) @ w[N/n, K]^T            ours: one fused kernel; baseline: all_gather_into_tensor + matmul
 Default shapes are the TP=8 configuration (M=8192, hidden 8192, ffn 28672).  Also reports the fraction of the
-roofline: max(FLOPs / measured cuBLAS peak, bytes over NVLink / 770 GB/s).
+roofline: max(FLOPs / measured cuBLAS peak, bytes over NVLink / 900 GB/s).
 
   torchrun --nproc-per-node 8 -m perftest.fused
 """
@@ -35,7 +35,7 @@ def main():
     except OSError:
         pass
     peak_tflops = peaks.get("bf16_tflops", 1590.0)
-    link_gbs = 770.0
+    link_gbs = 900.0  # per direction and GPU, nominal (a peer copy measures 770 GB/s on these machines)
     M, H = args.M, args.hidden
     ffn_local = args.ffn // 8  # per-GPU work stays that of TP=8 whatever n is (weak scaling)
     sets = 3
@@ -57,14 +57,22 @@ def main():
     link = (n - 1) / n * M * H * 2
     i = [0]
     for mode in ("rs", "ar"):
-        op = fg.GemmReduceScatter(M, H, mode=mode)
-        def step():
-            i[0] += 1
-            op(x[i[0] % sets], w[i[0] % sets])
-        ms = env.time_ms(step, iters=args.iters, warmup=5)
-        fg.check_errors()
-        report(f"gemm_{mode}_fused", ms, flops, link * (2 if mode == "ar" else 1), M=M, N=H, K=K)
-        op.close()
+        for use_mc in (True, False):
+            op = fg.GemmReduceScatter(M, H, mode=mode, use_multicast=use_mc)
+            if not use_mc and n == 1:
+                op.close()
+                continue
+            path = "switch" if op.switch_path else ("push" if n > 1 else "one PE")
+            if use_mc and not op.switch_path and n > 1:
+                op.close()
+                continue  # no multicast window: the second pass measures the push path
+            def step():
+                i[0] += 1
+                op(x[i[0] % sets], w[i[0] % sets])
+            ms = env.time_ms(step, iters=args.iters, warmup=5)
+            fg.check_errors()
+            report(f"gemm_{mode}_fused", ms, flops, link * (2 if mode == "ar" else 1), M=M, N=H, K=K, path=path)
+            op.close()
     if n > 1:
         partial = torch.empty(M, H, dtype=torch.bfloat16, device=env.dev)
         outp = torch.empty(M // n, H, dtype=torch.bfloat16, device=env.dev)
@@ -117,6 +125,16 @@ def main():
         ms = env.time_ms(base_ag, iters=args.iters, warmup=5)
         report("ag_gemm_cublas_nccl", ms, flops, link, M=M, N=Nl, K=H)
     ag.close()
+
+    # ---- the two together: a stack of tensor-parallel MLP blocks (fused GELU, no copies between blocks)
+    from nvshmem_b200.models.tp_mlp import TensorParallelMLPStack
+    L = 4
+    stack = TensorParallelMLPStack(H, ffn_local * n, M, L, seed=5 + env.rank)
+    stack.input_shard.copy_(shard)
+    ms = env.time_ms(lambda: stack(), iters=max(args.iters // 2, 5), warmup=3)
+    fg.check_errors()
+    report("tp_mlp_stack_fused", ms / L, 2 * flops, 2 * link, layers=L, ms_per_block=round(ms / L, 4))
+    stack.close()
     env.finish()
 
 

@@ -1,6 +1,6 @@
-"""Multi-PE tests on real GPUs: one child process per GPU (2 to 4 of them), NCCL only for the test
-harness' own gathers.  NVLS is off unless a test is about it: a rank that died with its memory bound
-to a multicast object has disturbed other GPUs on shared hosts."""
+"""Multi-PE tests on real GPUs: one child process per GPU (as many as the box has, up to 8), NCCL only for the
+test harness' own gathers.  NVLS is off unless a test is about it; the tests about it leave through the
+harness' soft exit (a failing rank detaches from the multicast objects before it goes)."""
 import pytest
 
 from tests._mp import run_workers
@@ -8,7 +8,9 @@ from tests.conftest import gpu_count
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
-NG = min(gpu_count(), 4)
+NG = min(gpu_count(), 8)
+need4 = pytest.mark.skipif(gpu_count() < 4, reason="needs four or more GPUs")
+NVLS_ON = {"NCCL_NVLS_ENABLE": "0"}  # this library's multicast windows on, NCCL's own NVLS off
 need2 = pytest.mark.skipif(gpu_count() < 2, reason="needs two or more GPUs")
 NO_NVLS = {"NVSHMEM_DISABLE_NVLS": "1", "NCCL_NVLS_ENABLE": "0"}
 
@@ -61,6 +63,37 @@ def test_device_collectives_and_tiles():
 @need2
 def test_fused_gemm_collectives():
     run_workers("fused_gemm_collectives", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need2
+def test_fused_gemm_collectives_nvls():
+    """Switch path: partial tiles reduced with multimem.ld_reduce, the all-reduce's multimem.st epilogue."""
+    run_workers("fused_gemm_collectives", NG, gpu=True, env=dict(NVLS_ON, BSHMEM_EXPECT_SWITCH_PATH="1"), timeout=600)
+
+
+@need2
+def test_tp_mlp_stack_nvls():
+    run_workers("tp_mlp_stack_matches_fp32_reference", NG, gpu=True, env=NVLS_ON, timeout=600)
+
+
+@need2
+def test_tp_mlp_stack_push_path():
+    run_workers("tp_mlp_stack_matches_fp32_reference", NG, gpu=True, env=NO_NVLS, timeout=600)
+
+
+@need4
+def test_team_multicast_windows():
+    run_workers("team_multicast_windows", NG - NG % 2, gpu=True, env=NVLS_ON, timeout=600)
+
+
+@need2
+def test_device_collectives_and_tiles_nvls():
+    run_workers("device_collectives_and_tiles", NG, gpu=True, env=NVLS_ON, timeout=600)
+
+
+@need2
+def test_moe_dispatch_combine_nvls():
+    run_workers("moe_dispatch_combine", NG, gpu=True, env=NVLS_ON, timeout=600)
 
 
 @need2

@@ -1232,6 +1232,115 @@ def tp_mlp_matches_single_device():
 
 
 @worker
+def tp_mlp_stack_matches_fp32_reference():
+    """The forward-only stack (fused GELU, reduce-scatter written into the next block's all-gather shard) against plain
+    fp32 torch on the full problem, twice in a row on new inputs (buffers are reused between calls)."""
+    nv = setup()
+    from nvshmem_b200.models.tp_mlp import TensorParallelMLPStack
+    from nvshmem_b200.ops import fused_gemm as fg
+    n = WORLD
+    hidden, ffn, tokens, layers = 512, 256 * n, 256 * n, 3
+    stack = TensorParallelMLPStack(hidden, ffn, tokens, layers, init_std=0.05, seed=11 + RANK)
+    assert stack.kernels_per_forward == layers * (3 if n > 1 else 2)
+    fl, rows = ffn // n, tokens // n
+    w_up = [torch.cat(_gather(w), 0) for w in stack.w_up]           # [ffn, hidden]: rank r holds rows r*fl..
+    w_down = [torch.cat(_gather(w), 1) for w in stack.w_down]       # [hidden, ffn]: rank r holds columns r*fl..
+    for it in range(2):
+        torch.manual_seed(31 + it)
+        x_full = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+        stack.input_shard.copy_(x_full[RANK * rows:(RANK + 1) * rows])
+        y = stack()
+        torch.cuda.synchronize()
+        fg.check_errors()
+        ref = stack.reference(x_full, w_up, w_down)[RANK * rows:(RANK + 1) * rows]
+        err = (y.float() - ref).abs().max().item()
+        assert err <= 0.04 * ref.abs().max().item() + 1e-2, (it, err, ref.abs().max().item())
+    stack.close()
+    teardown(nv)
+
+
+@worker
+def team_multicast_windows():
+    """Teams that do not span the world get an NVLink multicast window of their own: the NVLS algorithms run on a
+    strided split and on both teams of a 2-D split, and nvshmemx_mc_ptr gives a team-specific address."""
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    lib = H.load()
+    n, me = WORLD, RANK
+    assert nv.heap_info()["mc_base"] != 0, "this test needs NVLS"
+    probe = nv.tensor((4096,), torch.float32)
+    world_mc = lib.nvshmemx_mc_ptr(0, C.c_void_p(probe.data_ptr()))
+    assert world_mc
+    teams = []
+    evens = nv.team_split_strided(nv.Teams.TEAM_WORLD, 0, 2, n // 2)
+    if me % 2 == 0:
+        teams.append(("evens", evens, list(range(0, n, 2))))
+    xt, yt = nv.team_split_2d(nv.Teams.TEAM_WORLD, 2)
+    teams.append(("x", xt, [me - me % 2, me - me % 2 + 1]))
+    teams.append(("y", yt, list(range(me % 2, n, 2))))
+    g = torch.Generator(device="cuda").manual_seed(77 + me)
+    count = 8192
+    src = nv.tensor((count,), torch.float32)
+    dst = nv.tensor((count,), torch.float32)
+    big = nv.tensor((count * n,), torch.float32)
+    src.copy_(torch.rand(count, device="cuda", generator=g) * 2 - 1)
+    big.copy_(torch.rand(count * n, device="cuda", generator=g) * 2 - 1)
+    allsrc, allbig = _gather(src), _gather(big)
+    nv.barrier_all()
+    for name, team, members in teams:
+        size = len(members)
+        if size < 2:
+            continue
+        tme = members.index(me)
+        mc = lib.nvshmemx_mc_ptr(int(team), C.c_void_p(probe.data_ptr()))
+        assert mc and mc != world_mc, (name, mc, world_mc)
+        for algo in ("nvls_oneshot", "nvls_twoshot", "auto"):
+            dst.zero_()
+            nv.barrier(team)
+            nv.reduce(team, dst, src, "sum", algo=algo)
+            torch.cuda.synchronize()
+            want = _oracle("sum", [allsrc[m] for m in members])
+            assert _close(dst, want, torch.float32), ("reduce", name, algo, (dst - want).abs().max().item())
+        res = nv.tensor((count,), torch.float32) if False else dst  # reuse: allocation is a world collective
+        res.zero_()
+        nv.barrier(team)
+        nv.reducescatter(team, res, big, "sum", algo="nvls")
+        torch.cuda.synchronize()
+        want = _oracle("sum", [allbig[m][tme * count:(tme + 1) * count] for m in members])
+        assert _close(res, want, torch.float32), ("reducescatter", name)
+        out = big  # gather target: size * count elements fit
+        keep = big.clone()
+        nv.barrier(team)
+        nv.fcollect(team, out, src, algo="nvls")
+        torch.cuda.synchronize()
+        assert torch.equal(out[:size * count], torch.cat([allsrc[m] for m in members])), ("fcollect", name)
+        nv.barrier(team)
+        nv.broadcast(team, dst, src, root=size - 1, algo="nvls")
+        torch.cuda.synchronize()
+        assert torch.equal(dst, allsrc[members[-1]]), ("broadcast", name)
+        big.copy_(keep)
+        torch.cuda.synchronize()
+        nv.barrier(team)
+    assert nv.error_bits() == 0
+    nv.barrier_all()
+    for name, team, members in teams:
+        pass
+    # destruction is collective over the team's members: everyone destroys its own teams in the same order
+    if me % 2 == 0:
+        nv.team_destroy(evens)
+    nv.team_destroy(xt)
+    nv.team_destroy(yt)
+    # the slots (and the multicast windows) can be made again
+    again = nv.team_split_strided(nv.Teams.TEAM_WORLD, 1, 2, n // 2)
+    if me % 2 == 1:
+        assert lib.nvshmemx_mc_ptr(int(again), C.c_void_p(probe.data_ptr()))
+        nv.team_destroy(again)
+    for t in (src, dst, big, probe):
+        nv.free_tensor(t)
+    teardown(nv)
+
+
+@worker
 def rank_leaves_between_steps():
     """Failure detection without faulting a GPU: after a clean step one rank leaves (finalises nothing
     collectively, just stops taking part).  The others learn it on the host through the store before
