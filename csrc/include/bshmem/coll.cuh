@@ -304,6 +304,59 @@ __device__ __forceinline__ int allreduce_ll(const bshmemi_team_t* t, T* dst, con
   return err;
 }
 
+// ------------------------------------------------------------------ reduction inside the switch
+// dst[0, bytes) = reduction over the team of the `bytes` at multicast address mc_src, by the calling group.
+// MC_STORE: dst is a multicast address too and the result is stored to every member (second half of a
+// two-shot).  Four reductions are in flight per thread.  `bytes` is a multiple of NvlsReduce<T, OP>::grain.
+template <class T, int OP, int SCOPE, bool MC_STORE>
+__device__ __forceinline__ void nvls_reduce_bytes(const char* mc_src, char* dst, size_t bytes) {
+  const int rank = group_rank<SCOPE>();
+  const size_t G = group_size<SCOPE>();
+  if (NvlsReduce<T, OP>::vector16) {
+    const size_t nvec = bytes / 16;
+    size_t v = rank;
+    for (; v + 3 * G < nvec; v += 4 * G) {
+      const uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
+      const uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * G) * 16);
+      if (MC_STORE) {
+        multimem_st_v4(dst + v * 16, r0);
+        multimem_st_v4(dst + (v + G) * 16, r1);
+        multimem_st_v4(dst + (v + 2 * G) * 16, r2);
+        multimem_st_v4(dst + (v + 3 * G) * 16, r3);
+      } else {
+        ((uint4*)dst)[v] = r0;
+        ((uint4*)dst)[v + G] = r1;
+        ((uint4*)dst)[v + 2 * G] = r2;
+        ((uint4*)dst)[v + 3 * G] = r3;
+      }
+    }
+    for (; v < nvec; v += G) {
+      const uint4 r = MultimemSum<T>::ld(mc_src + v * 16);
+      if (MC_STORE) multimem_st_v4(dst + v * 16, r);
+      else ((uint4*)dst)[v] = r;
+    }
+  } else {
+    const size_t n = bytes / sizeof(T);
+    const T* s = (const T*)mc_src;
+    T* d = (T*)dst;
+    auto put = [&](size_t i, T r) {
+      if (!MC_STORE) d[i] = r;
+      else if (sizeof(T) == 8) multimem_st_u64(d + i, (uint64_t)r);
+      else multimem_st_u32(d + i, (uint32_t)r);
+    };
+    size_t i = rank;
+    for (; i + 3 * G < n; i += 4 * G) {
+      const T r0 = MultimemInt<T, OP>::ld(s + i), r1 = MultimemInt<T, OP>::ld(s + i + G);
+      const T r2 = MultimemInt<T, OP>::ld(s + i + 2 * G), r3 = MultimemInt<T, OP>::ld(s + i + 3 * G);
+      put(i, r0);
+      put(i + G, r1);
+      put(i + 2 * G, r2);
+      put(i + 3 * G, r3);
+    }
+    for (; i < n; i += G) put(i, MultimemInt<T, OP>::ld(s + i));
+  }
+}
+
 // ------------------------------------------------------------------ allreduce
 // `src` and `dst` are symmetric; in-place is allowed (it then uses two-shot).
 // Works on elements [lo, hi) so that CTA c of a multi-CTA launch can own a slice
@@ -311,16 +364,15 @@ __device__ __forceinline__ int allreduce_ll(const bshmemi_team_t* t, T* dst, con
 template <class T, int OP, int SCOPE>
 __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, const T* src, size_t lo, size_t hi, int slot, int algo) {
   const int size = t->size, me = t->my_pe;
-  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
-  constexpr int N = VecOf<T>::N;
   if (size == 1) {
     if (dst != src) memcpy_group<SCOPE>(dst + lo, src + lo, (hi - lo) * sizeof(T));
     group_sync<SCOPE>();
     return 0;
   }
   const size_t bytes = (hi - lo) * sizeof(T);
-  const bool nvls_ok = OP == OP_SUM && MultimemSum<T>::supported && t->has_nvls && (bytes % 16) == 0 &&
-                       (((uintptr_t)(src + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
+  constexpr int grain = NvlsReduce<T, OP>::grain;
+  const bool nvls_ok = NvlsReduce<T, OP>::supported && t->has_nvls && (bytes % grain) == 0 &&
+                       (((uintptr_t)(src + lo) | (uintptr_t)(dst + lo)) & (grain - 1)) == 0;
   if (algo == RED_AUTO) algo = bshmemi_state_d.reduce_algo;
   // Flag-in-data: whole small messages only (one group owns the team's packet buffer).
   const bool ll_ok = lo == 0 && slot == 0 && bytes > 0 && (bytes & 3) == 0 && ((uintptr_t)src & 3) == 0 && 4 * bytes * size <= t->ll_bytes;
@@ -347,35 +399,14 @@ __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, 
     err |= team_barrier<SCOPE>(t, slot);  // my pushes have landed, theirs too
   } else if (algo == RED_NVLS_ONESHOT) {
     const char* mc_src = (const char*)t->mc_base + ((uint64_t)(src + lo) - bshmemi_state_d.heap_base);
-    const size_t nvec = (hi - lo) / N;
-    uint4* out = (uint4*)(dst + lo);
-    size_t v = rank;
-    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {  // four reductions in flight per thread
-      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
-      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
-      out[v] = r0;
-      out[v + G] = r1;
-      out[v + 2 * (size_t)G] = r2;
-      out[v + 3 * (size_t)G] = r3;
-    }
-    for (; v < nvec; v += G) out[v] = MultimemSum<T>::ld(mc_src + v * 16);
+    nvls_reduce_bytes<T, OP, SCOPE, false>(mc_src, (char*)(dst + lo), bytes);
     err |= team_sync<SCOPE>(t, slot);
   } else {  // NVLS two-shot: reduce my chunk in the switch, multicast the result
     size_t a, b;
     split_range<T>(hi - lo, size, me, &a, &b);
     const char* mc_src = (const char*)t->mc_base + ((uint64_t)(src + lo + a) - bshmemi_state_d.heap_base);
     char* mc_dst = (char*)t->mc_base + ((uint64_t)(dst + lo + a) - bshmemi_state_d.heap_base);
-    const size_t nvec = (b - a) / N;
-    size_t v = rank;
-    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {  // four reductions in flight per thread
-      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
-      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
-      multimem_st_v4(mc_dst + v * 16, r0);
-      multimem_st_v4(mc_dst + (v + G) * 16, r1);
-      multimem_st_v4(mc_dst + (v + 2 * (size_t)G) * 16, r2);
-      multimem_st_v4(mc_dst + (v + 3 * (size_t)G) * 16, r3);
-    }
-    for (; v < nvec; v += G) multimem_st_v4(mc_dst + v * 16, MultimemSum<T>::ld(mc_src + v * 16));
+    nvls_reduce_bytes<T, OP, SCOPE, true>(mc_src, mc_dst, (b - a) * sizeof(T));
     err |= team_barrier<SCOPE>(t, slot);
   }
   return err;
@@ -392,8 +423,6 @@ __device__ __forceinline__ int allreduce(int team, T* dst, const T* src, size_t 
 template <class T, int OP, int SCOPE>
 __device__ __forceinline__ int reducescatter_range(const bshmemi_team_t* t, T* dst, const T* src, size_t nreduce, size_t lo, size_t hi, int slot, int algo) {
   const int size = t->size, me = t->my_pe;
-  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
-  constexpr int N = VecOf<T>::N;
   const T* my_block = src + (size_t)me * nreduce;
   if (size == 1) {
     memcpy_group<SCOPE>(dst + lo, my_block + lo, (hi - lo) * sizeof(T));
@@ -401,25 +430,16 @@ __device__ __forceinline__ int reducescatter_range(const bshmemi_team_t* t, T* d
     return 0;
   }
   const size_t bytes = (hi - lo) * sizeof(T);
-  const bool nvls_ok = OP == OP_SUM && MultimemSum<T>::supported && t->has_nvls && (bytes % 16) == 0 &&
-                       (((uintptr_t)(my_block + lo) | (uintptr_t)(dst + lo)) & 15) == 0;
+  constexpr int grain = NvlsReduce<T, OP>::grain;
+  const bool nvls_ok = NvlsReduce<T, OP>::supported && t->has_nvls && (bytes % grain) == 0 &&
+                       (((uintptr_t)(my_block + lo) | (uintptr_t)(dst + lo)) & (grain - 1)) == 0;
   if (algo == RS_AUTO) algo = bshmemi_state_d.reducescatter_algo;
   if (algo == RS_AUTO) algo = nvls_ok ? RS_NVLS : RS_PULL;
   if (algo == RS_NVLS && !nvls_ok) algo = RS_PULL;
   int err = team_sync<SCOPE>(t, slot);
   if (algo == RS_NVLS) {
     const char* mc_src = (const char*)t->mc_base + ((uint64_t)(my_block + lo) - bshmemi_state_d.heap_base);
-    const size_t nvec = (hi - lo) / N;
-    size_t v = rank;
-    for (; v + 3 * (size_t)G < nvec; v += 4 * (size_t)G) {
-      uint4 r0 = MultimemSum<T>::ld(mc_src + v * 16), r1 = MultimemSum<T>::ld(mc_src + (v + G) * 16);
-      uint4 r2 = MultimemSum<T>::ld(mc_src + (v + 2 * (size_t)G) * 16), r3 = MultimemSum<T>::ld(mc_src + (v + 3 * (size_t)G) * 16);
-      ((uint4*)(dst + lo))[v] = r0;
-      ((uint4*)(dst + lo))[v + G] = r1;
-      ((uint4*)(dst + lo))[v + 2 * (size_t)G] = r2;
-      ((uint4*)(dst + lo))[v + 3 * (size_t)G] = r3;
-    }
-    for (; v < nvec; v += G) ((uint4*)(dst + lo))[v] = MultimemSum<T>::ld(mc_src + v * 16);
+    nvls_reduce_bytes<T, OP, SCOPE, false>(mc_src, (char*)(dst + lo), bytes);
   } else {
     // dst is indexed from 0 while the source block starts at me*nreduce: shift dst.
     pull_reduce_range<T, OP, SCOPE, false>(t, dst - (size_t)me * nreduce, src, (size_t)me * nreduce + lo, (size_t)me * nreduce + hi);

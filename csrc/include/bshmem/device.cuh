@@ -23,15 +23,27 @@
 
 #include "state.h"
 
+// Where the device-side copy of the state lives:
+//   default               one `static __constant__` copy per translation unit, announced to the host library by a
+//                         static registrar (no relocatable device code, nothing for the user to do);
+//   BSHMEM_DEVICE_MODULE  for device code that is compiled on its own (nvcc -cubin / -fatbin / -ptx) and loaded with
+//                         the driver API: the copy gets the unmangled global name `bshmemi_state_d`, which
+//                         nvshmemx_cumodule_init / nvshmemx_culibrary_init look up in the loaded module and fill.
+//                         Define it in ONE translation unit of such a module (with -rdc the others declare it extern).
+#if defined(BSHMEM_DEVICE_MODULE)
+extern "C" {
+__constant__ bshmemi_state_t bshmemi_state_d;
+}
+#else
 #ifndef BSHMEM_STATE_LINKAGE
 #define BSHMEM_STATE_LINKAGE static
 #endif
-
-// One copy per translation unit (no relocatable device code needed).
 BSHMEM_STATE_LINKAGE __constant__ bshmemi_state_t bshmemi_state_d;
+#endif
 
 extern "C" void bshmemi_register_module(void* (*getter)(), const char* name);
 
+#if !defined(BSHMEM_DEVICE_MODULE)
 namespace bshmem_detail {
 static void* state_symbol_address() {
   void* p = nullptr;
@@ -46,6 +58,7 @@ struct ModuleRegistrar {
 };
 static ModuleRegistrar module_registrar_instance;
 }  // namespace bshmem_detail
+#endif
 
 namespace bshmem {
 

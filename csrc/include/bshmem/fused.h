@@ -61,6 +61,10 @@ typedef struct {
   /* Activation applied to the fp32 result before it is rounded to bf16 (BSHMEM_FUSED_ACT_*); PLAIN and AG only
    * (a partial sum of RS / AR cannot be activated). */
   int act;
+  /* AG: 1 = the caller pushes the shards itself (for example with copy engines on another stream) and sets
+   * ag_flags[rank * (M/npes/128)] on each peer to `epoch` once its shard is complete there; the kernel then sends
+   * nothing and waits for one flag per shard.  0 = two warps of every CTA send the shard. */
+  int ag_external;
 } bshmem_fused_args_t;
 
 /* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */

@@ -29,6 +29,11 @@
 //   * Every call on a GPU shares the one array: calls whose kernels could overlap on the
 //     GPU (different streams, no ordering between them) race.  Issue them on one stream
 //     or order them yourself.  Each call clears the words that must start at zero.
+//   * Errors that the kernel meets (BSHMEM_MOE_ERRBIT_*) go to the caller's `error_flag`.  A caller that passes
+//     none does not lose them: they go to a word inside the built-in array, which
+//     bshmem_moe_noalloc_error_bits() reads back (it waits for the stream first).  The next call on the
+//     same GPU clears that word, so read it before calling again.
+//   * T * K must fit a 32-bit row number; larger products are refused with BSHMEM_MOE_ERR_SHAPE.
 //   * No cudaMalloc, cudaFree or allocating library routine is called on this path.
 #pragma once
 #include <cuda_runtime_api.h>
@@ -48,6 +53,11 @@ extern "C" {
  * int that receives BSHMEM_MOE_ERRBIT_* bits (may be null).  Returns a BSHMEM_MOE_* status. */
 int bshmem_moe_dispatch_local_noalloc(const void* x, const int* topk_idx, int T, int H, int K, int E, void* recv_x, int* slot_map, int* expert_offsets,
                                       int* error_flag, cudaStream_t stream);
+
+
+/* For callers that passed no error_flag: waits for `stream`, then copies the error bits that the last call on
+ * the current GPU recorded in the built-in array to *bits (host memory).  Allocates nothing. */
+int bshmem_moe_noalloc_error_bits(cudaStream_t stream, int* bits);
 
 #ifdef __cplusplus
 }

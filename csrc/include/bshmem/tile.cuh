@@ -7,6 +7,12 @@
 // other PEs: completion is `tile_collective_wait` (a team barrier).  This is the
 // interface a GEMM epilogue uses to reduce or gather its output tile by tile.
 //
+// The last argument of every call, `flag`, picks the row of the team's synchronisation flags that the call uses
+// (flag % BSHMEM_SYNC_SLOTS).  One row serves ONE group of threads at a time: two CTAs (or warps) that run tile
+// collectives on the same team at the same time must pass different values, for example blockIdx.x, the same
+// value on every PE for matching calls, and again in the tile_collective_wait that completes them.  With the
+// default of 0 only one group per team may be inside a tile collective at any time.
+//
 // Algorithms (tile_coll_algo_t):
 //   NVLS_ONE_SHOT_PULL_NBI  every PE reduces the tile for itself (multimem.ld_reduce for sum of
 //                           float/half/bf16 on NVLS teams, peer loads otherwise); starts with a team sync
@@ -112,7 +118,7 @@ __device__ __forceinline__ void for_each(const TileGeom& g, const T* src, const 
 }
 
 template <int OP, int SCOPE, class SrcT, class DstT, class Coord>
-__device__ __forceinline__ int tile_reduce_impl(int team, SrcT src, DstT dst, Coord start, Coord bound, int root, bool rooted, bool everyone) {
+__device__ __forceinline__ int tile_reduce_impl(int team, SrcT src, DstT dst, Coord start, Coord bound, int root, bool rooted, bool everyone, uint64_t flag) {
   typedef typename SrcT::value_type T;
   typedef typename bshmem::Acc<T>::type A;
   constexpr int N = 16 / sizeof(T);
@@ -121,7 +127,7 @@ __device__ __forceinline__ int tile_reduce_impl(int team, SrcT src, DstT dst, Co
   const TileGeom g = geometry(src, dst, start, bound);
   const long scs = g.contiguous ? 1 : dim1(src.stride()), dcs = g.contiguous ? 1 : dim1(dst.stride());
   // Every member's source tile must be in place before anyone reads it.
-  int err = bshmem::team_sync<SCOPE>(t, 0);
+  int err = bshmem::team_sync<SCOPE>(t, (int)(flag % BSHMEM_SYNC_SLOTS));
   const bool i_reduce = everyone || t->my_pe == root;
   if (!i_reduce) return err;
   const bool nvls = OP == bshmem::OP_SUM && bshmem::MultimemSum<T>::supported && t->has_nvls;
@@ -195,39 +201,39 @@ __device__ __forceinline__ int tile_copy_impl(int team, SrcT src, DstT dst, Coor
 
 #define BSHMEM_TILE_SCOPE(SUF, SC)                                                                                                        \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_sum_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI); }  \
+  __device__ __forceinline__ int tile_sum_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI, flag); }  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_sum_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, 0, false, true); }                                  \
+  __device__ __forceinline__ int tile_sum_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, 0, false, true, flag); }                                  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_max_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI); }  \
+  __device__ __forceinline__ int tile_max_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI, flag); }  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_max_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, 0, false, true); }                                  \
+  __device__ __forceinline__ int tile_max_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, 0, false, true, flag); }                                  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_min_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI); }  \
+  __device__ __forceinline__ int tile_min_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, root, false, algo == NVLS_ONE_SHOT_PULL_NBI || algo == NVLS_ONE_SHOT_PUSH_NBI, flag); }  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_min_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, 0, false, true); }                                  \
+  __device__ __forceinline__ int tile_min_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, 0, false, true, flag); }                                  \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_sum_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, root, true, false); }                               \
+  __device__ __forceinline__ int tile_sum_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_SUM, SC>(team, src, dst, start, bound, root, true, false, flag); }                               \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_max_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, root, true, false); }                               \
+  __device__ __forceinline__ int tile_max_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MAX, SC>(team, src, dst, start, bound, root, true, false, flag); }                               \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_min_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t) { \
-    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, root, true, false); }                               \
+  __device__ __forceinline__ int tile_min_rooted_reduce##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int root, uint64_t flag) { \
+    return detail::tile_reduce_impl<bshmem::OP_MIN, SC>(team, src, dst, start, bound, root, true, false, flag); }                               \
   /* The caller's tile lands in `dst` (the caller's block of the gathered tensor) on every member. */                                     \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_allgather##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t) { \
+  __device__ __forceinline__ int tile_allgather##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t flag) { \
     return detail::tile_copy_impl<SC>(team, src, dst, start, bound, 0, 2); }                                                               \
   /* Called by the root only: its tile is stored into `dst` on every member. */                                                           \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_coll_algo_t algo>                                        \
-  __device__ __forceinline__ int tile_broadcast##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t) { \
+  __device__ __forceinline__ int tile_broadcast##SUF(nvshmem_team_t team, src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, uint64_t flag) { \
     return detail::tile_copy_impl<SC>(team, src, dst, start, bound, 0, 2); }                                                               \
   template <typename src_tensor_t, typename dst_tensor_t, typename tuple_t, tile_algo_t algo>                                             \
   __device__ __forceinline__ int tile_put##SUF(src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int pe, uint64_t) {      \
@@ -236,9 +242,9 @@ __device__ __forceinline__ int tile_copy_impl(int team, SrcT src, DstT dst, Coor
   __device__ __forceinline__ int tile_get##SUF(src_tensor_t src, dst_tensor_t dst, tuple_t start, tuple_t bound, int pe, uint64_t) {      \
     return detail::tile_copy_impl<SC>(0, src, dst, start, bound, pe, 1); }                                                                 \
   template <tile_coll_algo_t algo>                                                                                                        \
-  __device__ __forceinline__ int tile_collective_wait##SUF(nvshmem_team_t team, uint64_t) {                                               \
+  __device__ __forceinline__ int tile_collective_wait##SUF(nvshmem_team_t team, uint64_t flag) {                                          \
     const bshmemi_team_t* t = bshmem::team_ptr(team);                                                                                     \
-    return t ? bshmem::team_barrier<SC>(t, 0) : 1; }
+    return t ? bshmem::team_barrier<SC>(t, (int)(flag % BSHMEM_SYNC_SLOTS)) : 1; }
 
 BSHMEM_TILE_SCOPE(, bshmem::SCOPE_THREAD)
 BSHMEM_TILE_SCOPE(_warp, bshmem::SCOPE_WARP)

@@ -165,6 +165,19 @@ __global__ void k_tile_allreduce(int team, float* dst, float* src, int R, int C,
   else tile_sum_reduce_block<decltype(s), decltype(d), decltype(start), NVLS_TWO_SHOT_PUSH_NBI>(team, s, d, start, bound, root, 0);
   tile_collective_wait_block<NVLS_ONE_SHOT_PULL_NBI>(team, 0);
 }
+// The same with several CTAs at once: CTA b owns the tile whose first row is r0 + b * rows and synchronises on
+// flag row b of the team, so the CTAs do not share a synchronisation epoch.
+__global__ void k_tile_allreduce_multi(int team, float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int algo, int root) {
+  using namespace nvshmemx;
+  const int rb = r0 + (int)blockIdx.x * rows;
+  auto lay = make_layout(make_shape(rows, cols), make_stride(C, ConstInt<1>{}));
+  Tensor<float, decltype(lay)> s(src + (size_t)rb * C + c0, lay), d(dst + (size_t)rb * C + c0, lay);
+  auto start = make_shape(rb, c0);
+  auto bound = make_shape(R, C);
+  if (algo == 1) tile_sum_reduce_block<decltype(s), decltype(d), decltype(start), NVLS_ONE_SHOT_PULL_NBI>(team, s, d, start, bound, blockIdx.x);
+  else tile_sum_reduce_block<decltype(s), decltype(d), decltype(start), NVLS_TWO_SHOT_PUSH_NBI>(team, s, d, start, bound, root, blockIdx.x);
+  tile_collective_wait_block<NVLS_ONE_SHOT_PULL_NBI>(team, blockIdx.x);
+}
 __global__ void k_tile_put_get(float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int pe, int get) {
   using namespace nvshmemx;
   auto lay = make_layout(make_shape(rows, cols), make_stride(C, 1));
@@ -183,7 +196,7 @@ int devtest_preload(void) {
   cudaFuncAttributes a;
   const void* fns[] = {(const void*)k_put, (const void*)k_get, (const void*)k_typed, (const void*)k_put_signal, (const void*)k_signal_wait_sum, (const void*)k_ring,
                        (const void*)k_wait_never, (const void*)k_amo_fetch_add, (const void*)k_amo_mix, (const void*)k_barrier_rounds, (const void*)k_device_coll,
-                       (const void*)k_tile_allreduce, (const void*)k_tile_put_get};
+                       (const void*)k_tile_allreduce, (const void*)k_tile_allreduce_multi, (const void*)k_tile_put_get};
   int bad = 0;
   for (const void* f : fns) bad |= cudaFuncGetAttributes(&a, f) != cudaSuccess;
   return bad;
@@ -234,6 +247,11 @@ int devtest_device_coll(int kind, int team, void* dst, const void* src, size_t n
 }
 int devtest_tile_allreduce(int team, float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int algo, int root, cudaStream_t s) {
   k_tile_allreduce<<<1, 256, 0, s>>>(team, dst, src, R, C, r0, c0, rows, cols, algo, root);
+  return LAUNCH_OK();
+}
+int devtest_tile_allreduce_multi(int team, float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int algo, int root, int ctas, cudaStream_t s) {
+  if (ctas < 1 || ctas > BSHMEM_SYNC_SLOTS) return 1;
+  k_tile_allreduce_multi<<<ctas, 256, 0, s>>>(team, dst, src, R, C, r0, c0, rows, cols, algo, root);
   return LAUNCH_OK();
 }
 int devtest_tile_put_get(float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int pe, int get, cudaStream_t s) {

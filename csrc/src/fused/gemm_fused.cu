@@ -20,10 +20,11 @@
 //            per tile.  The PE's own rows come last: their epilogue waits for the flags of the tile and adds the
 //            partials to the TMEM accumulator before the single rounding to bf16.
 //   MODE_AR  same; the reduced tile goes to every PE's output (one `multimem.st` through the switch, or per-PE stores).
-//   MODE_AG  all-gather -> column-parallel GEMM.  The auxiliary warps of all CTAs copy this PE's activation shard into
-//            every peer's gathered buffer (nearest peer first) and count rows into a counter per 128-row block;
-//            the producer warp consumes shards in arrival order (own, then rank-1, rank-2, …) and only waits when a
-//            block has not landed.  Remote data is always read from this GPU's own memory.
+//   MODE_AG  all-gather -> column-parallel GEMM.  This PE's activation shard is pushed into every peer's gathered
+//            buffer, nearest peer first, either by copy engines on a second stream (the caller issues the copies and
+//            a flag write per shard; no SM takes part) or by the auxiliary warps of all CTAs (a counter per 128-row
+//            block); the producer warp consumes shards in arrival order (own, then rank-1, rank-2, …) and only waits
+//            when one has not landed.  Remote data is always read from this GPU's own memory.
 //   MODE_PLAIN  no collective (also what 1 PE runs).
 // Every wait (mbarrier, flag) is bounded; on expiry the CTA unwinds, frees its tensor memory and sets `error_flag`.
 // No load uses a cluster-wide broadcast form, so the same binary runs on any number of GPUs.
@@ -120,7 +121,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
         const TileInfo ti = tile_info(p, t);
         if (p.mode == BSHMEM_FUSED_AG && ti.peer != p.rank) {
           // The 128 rows of this tile arrive from `peer`; all of K comes with them.
-          if (!wait_flag_ge(p.ag_flags_local + (size_t)ti.peer * tmr + ti.m_local, p.epoch * (uint64_t)BM, p.wait_limit_ns, abort_flag)) break;
+          // In-kernel sender: a counter per 128-row block.  External sender: one flag per shard, set to the call number.
+          const uint64_t want = p.ag_external ? p.epoch : p.epoch * (uint64_t)ag_units(p.K, (int)gridDim.x).units_per_block;
+          const size_t fidx = (size_t)ti.peer * tmr + (p.ag_external ? 0 : ti.m_local);
+          if (!wait_flag_ge(p.ag_flags_local + fidx, want, p.wait_limit_ns, abort_flag)) break;
           fence_proxy_async_all();  // peer-written data (generic proxy) before my TMA reads (async proxy)
         }
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -180,8 +184,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
     }
   } else if (warp < EPI_WARP0) {
     // ---------------- auxiliary warps 2 and 3
-    if (p.mode == BSHMEM_FUSED_AG && p.npes > 1) ag_send_rows(p, (int)threadIdx.x - AUX_WARP0 * 32, abort_flag);
-    else if (reduce_mode && p.sw_reduce) switch_reduce(p, warp - AUX_WARP0, lane, abort_flag);
+    if (p.mode == BSHMEM_FUSED_AG && p.npes > 1 && !p.ag_external) ag_send_units(p, (int)threadIdx.x - AUX_WARP0 * 32, abort_flag);
+    else if (reduce_mode && p.sw_reduce && p.red_rows == 32) switch_reduce<32>(p, warp - AUX_WARP0, lane, abort_flag);
+    else if (reduce_mode && p.sw_reduce) switch_reduce<16>(p, warp - AUX_WARP0, lane, abort_flag);
   } else {
     // ---------------- epilogue
     const int ew = warp - EPI_WARP0;                 // TMEM lane quarter of this warp
@@ -406,6 +411,11 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
     // Switch path: a staging buffer with a multicast alias (and, for the all-reduce, a multicast alias of the output).
     p.sw_reduce = a->stage_local && a->stage_mc && (mode == BSHMEM_FUSED_RS || a->out_mc);
     if (p.sw_reduce) {
+      static const int red_rows = [] {
+        const char* e = getenv("BSHMEM_FUSED_RED_ROWS");
+        return e && atoi(e) == 16 ? 16 : 32;
+      }();
+      p.red_rows = red_rows;
       if (((uintptr_t)a->stage_mc & 15) || ((uintptr_t)a->out & 15) || ((uintptr_t)a->out_mc & 15)) return BSHMEM_FUSED_ERR_ALIGNMENT;
       p.stage_mc = (const char*)a->stage_mc;
       p.out_local = (char*)a->out;
@@ -436,6 +446,7 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
       p.ag_dst[q] = (char*)a->ag_peer[q] + (size_t)a->rank * shard_bytes;
       p.ag_flags_peer[q] = a->ag_flags_peer[q];
     }
+    p.ag_external = a->ag_external != 0;
   }
   st = make_map(&p.tmB, a->B, a->N, a->K, pair ? BN / 2 : BN);
   if (st) return st;
@@ -476,16 +487,19 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
 
 extern "C" int bshmem_fused_gemm_smem_bytes(void) { return SMEM_BYTES; }
 
-// Test hook (host only): the rows of a shard that CTA `b` of `grid` sends in the all-gather mode.  out = {lo, hi}.
-extern "C" int bshmem_fused_test_ag_slice(int rows, int grid, int b, int* out) {
-  if (rows <= 0 || grid <= 0 || b < 0 || b >= grid) return 1;
-  ag_slice(rows, grid, b, &out[0], &out[1]);
+// Test hook (host only): how the all-gather mode cuts a 128-row block of a shard into units for `grid` CTAs.
+// out = {unit_bytes, units_per_block}.
+extern "C" int bshmem_fused_test_ag_units(int K, int grid, int* out) {
+  if (K <= 0 || K % BK || grid <= 0) return 1;
+  const AgUnits u = ag_units(K, grid);
+  out[0] = u.unit_bytes;
+  out[1] = u.units_per_block;
   return 0;
 }
 
 // Test hook (host only): the tile that position `t` of the tile order names, for the checks of the order's
 // invariants (every tile once, own rows last, pairs share their columns).  out = {m_tile, n_tile, peer, m_local, idx_in_peer}.
-// `mode` may carry BSHMEM_FUSED_TEST_SWITCH_ORDER (0x100) to ask for the order of the switch path of RS / AR.
+// `mode` may carry 0x100 to ask for the order of the switch path of RS / AR.
 extern "C" int bshmem_fused_test_tile_info(int mode, int M, int N, int rank, int npes, int t, int* out) {
   if (npes < 1 || M % (BM * npes) || N % BN || t < 0 || t >= (M / BM) * (N / BN)) return 1;
   FusedParams p;

@@ -24,7 +24,6 @@ constexpr int EPI_COLS = 64, EPI_BUF = BM * EPI_COLS * 2, EPI_BUFS = 2;
 constexpr int TMEM_COLS = 512, ACC_COLS = BN;
 constexpr int NTHREADS = 256, EPI_THREADS = 128, EPI_WARP0 = 4;
 constexpr int AUX_WARP0 = 2, AUX_THREADS = 64;   // warps 2 and 3: switch-side reduction (RS / AR) or shard sender (AG)
-constexpr int RED_ROWS = 16;                      // rows of a tile that one auxiliary warp reduces per work item
 constexpr int SMEM_TILES = 4 * (A_STAGE + BN * BK * 2) + EPI_BUFS * EPI_BUF;  // 4 stages of a 128 x 256 tile = 6 stages of a pair's halves
 constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -46,7 +45,9 @@ struct alignas(64) FusedParams {
   int* error_flag;
   uint64_t epoch, wait_limit_ns;
   int M, N, K, rank, npes, mode;
+  int ag_external;                           // AG: the shards are pushed by the caller (copy engines); flag [peer][0] = epoch when a shard is complete
   int act;                                   // BSHMEM_FUSED_ACT_*: applied to the fp32 result in the epilogue (PLAIN / AG)
+  int red_rows;                              // switch path: rows per work item of the reducing warps (16 or 32)
   int sw_reduce;                             // RS/AR: partial tiles stay local and the owner fetches their sum through the switch
 };
 
@@ -117,56 +118,76 @@ __device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t want
 // ------------------------------------------------------------------ auxiliary warps (warps 2 and 3 of every CTA)
 __device__ __forceinline__ void aux_bar_sync() { named_bar_sync(2, AUX_THREADS); }
 
-// MODE_AG: the 64 auxiliary threads of every CTA copy a slice of this PE's shard (whole rows, split evenly over the
-// grid) into every peer's gathered buffer with 16-byte loads and stores, nearest peer first, and then add the number of
-// rows delivered to the arrival counter of each 128-row block they touched.  No CTA is set aside for sending, so every
-// SM keeps computing; the copies ride in the load/store slots that the tensor-core pipeline leaves idle.
-// Rows [lo, hi) of the shard that CTA `b` of `grid` sends.
-__host__ __device__ __forceinline__ void ag_slice(int rows, int grid, int b, int* lo, int* hi) {
-  *lo = (int)(((long long)b * rows) / grid);
-  *hi = (int)(((long long)(b + 1) * rows) / grid);
+// MODE_AG, in-kernel sender: the 64 auxiliary threads of every CTA copy part of this PE's shard into every peer's
+// gathered buffer with 16-byte loads and stores, nearest peer first.  The shard is cut into units (a row, or a
+// power-of-two fraction of one when there are more CTAs than rows in a block) and the units of every 128-row block
+// are dealt round-robin to the CTAs.  After a peer's copy a CTA makes its stores visible (one barrier of the 64
+// threads, one system-scope fence by one thread: a fence drains the CTA's stores in flight, so it is paid once per
+// peer and not per block) and adds the number of units it delivered to each block's arrival counter on that peer; a
+// block is complete when its counter has grown by `units_per_block`.
+// Loads issued by these warps share the L2-to-SM fabric with the operand traffic of the tensor cores and see long
+// latencies, so this path moves a few hundred GB/s per GPU at best; the default is therefore the external sender
+// (FusedParams::ag_external: copy engines push the shards and set one flag per shard, see the host wrapper), and
+// this path serves callers that cannot use a second stream.
+struct AgUnits {
+  int unit_bytes, units_per_block;
+};
+__host__ __device__ __forceinline__ AgUnits ag_units(int K, int grid) {
+  AgUnits u;
+  u.unit_bytes = K * 2;
+  u.units_per_block = BM;
+  while (u.units_per_block < grid && u.unit_bytes >= 4096) {  // halves stay multiples of 16 bytes (K is a multiple of 64)
+    u.unit_bytes >>= 1;
+    u.units_per_block <<= 1;
+  }
+  return u;
 }
-__device__ void ag_send_rows(const FusedParams& p, int at /*0..63*/, volatile int* abort_flag) {
-  const int rows = p.M / p.npes, tmr = rows / BM;
-  int lo, hi;
-  ag_slice(rows, (int)gridDim.x, (int)blockIdx.x, &lo, &hi);
-  if (lo >= hi) return;
-  const size_t row_bytes = (size_t)p.K * 2;
-  const size_t n16 = (size_t)(hi - lo) * row_bytes / 16;  // K is a multiple of 64: rows are whole 16-byte pieces
-  const uint4* src = (const uint4*)(p.ag_src + (size_t)lo * row_bytes);
-  constexpr int UNROLL = 8;
+__device__ void ag_send_units(const FusedParams& p, int at /*0..63*/, volatile int* abort_flag) {
   (void)abort_flag;  // nothing here waits for a peer, and both warps must reach every barrier: no early exit
+  const int tmr = (p.M / p.npes) / BM;
+  const AgUnits u = ag_units(p.K, (int)gridDim.x);
+  const size_t block_bytes = (size_t)BM * p.K * 2;
+  const int n16 = u.unit_bytes / 16;
+  constexpr int UNROLL = 8;
   for (int o = 1; o < p.npes; ++o) {
     const int peer = (p.rank + o) % p.npes;
-    uint4* dst = (uint4*)(p.ag_dst[peer] + (size_t)lo * row_bytes);
-    size_t i = at;
-    for (; i + (size_t)(UNROLL - 1) * AUX_THREADS < n16; i += (size_t)UNROLL * AUX_THREADS) {
-      uint4 v[UNROLL];
+    for (int blk = 0; blk < tmr; ++blk) {
+      for (int unit = (int)blockIdx.x; unit < u.units_per_block; unit += (int)gridDim.x) {
+        const size_t off = (size_t)blk * block_bytes + (size_t)unit * u.unit_bytes;
+        const uint4* src = (const uint4*)(p.ag_src + off);
+        uint4* dst = (uint4*)(p.ag_dst[peer] + off);
+        int i = at;
+        for (; i + (UNROLL - 1) * AUX_THREADS < n16; i += UNROLL * AUX_THREADS) {
+          uint4 v[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = __ldg(src + i + (size_t)u * AUX_THREADS);
+          for (int k = 0; k < UNROLL; ++k) v[k] = __ldg(src + i + k * AUX_THREADS);
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) dst[i + (size_t)u * AUX_THREADS] = v[u];
+          for (int k = 0; k < UNROLL; ++k) dst[i + k * AUX_THREADS] = v[k];
+        }
+        for (; i < n16; i += AUX_THREADS) dst[i] = __ldg(src + i);
+      }
     }
-    for (; i < n16; i += AUX_THREADS) dst[i] = __ldg(src + i);
     // The stores of all 64 threads are ordered before thread 0's release by the barrier (cumulativity).
     aux_bar_sync();
     if (at == 0) {
       asm volatile("fence.acq_rel.sys;" ::: "memory");
-      for (int b = lo / BM; b <= (hi - 1) / BM; ++b) {
-        const int r0 = b * BM > lo ? b * BM : lo, r1 = (b + 1) * BM < hi ? (b + 1) * BM : hi;
-        uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + b;
-        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)(r1 - r0)) : "memory");
+      // units of a block that this CTA delivered: blockIdx.x, blockIdx.x + grid, … below units_per_block
+      const int sent = (int)blockIdx.x < u.units_per_block ? (u.units_per_block - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+      for (int blk = 0; blk < tmr && sent; ++blk) {
+        uint64_t* f = p.ag_flags_peer[peer] + (size_t)p.rank * tmr + blk;
+        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(f), "l"((uint64_t)sent) : "memory");
       }
     }
   }
 }
 
-// MODE_RS / MODE_AR, switch path: reduction of the tiles this PE owns.  Work items are RED_ROWS-row slices of the
+// MODE_RS / MODE_AR, switch path: reduction of the tiles this PE owns.  Work items are RED_ROWS-row slices (16 or 32) of the
 // owned tiles, numbered in the order the tiles are produced and dealt round-robin to all auxiliary warps of the grid.
 // A warp waits until all PEs have flagged the tile, then fetches each row slice with one `multimem.ld_reduce` per lane
 // (a warp covers one 512-byte row of the tile per instruction): the switch adds the PEs' copies in fp32 and returns one
 // bf16 result, so the owner receives one tile instead of npes - 1 partials and adds nothing itself.
 //   RS: the sum is written to this PE's output.   AR: it is written once through the multicast alias of the output.
+template <int RED_ROWS>
 __device__ void switch_reduce(const FusedParams& p, int aw /*0..1*/, int lane, volatile int* abort_flag) {
   const int tiles_n = p.N / BN, tmr = (p.M / p.npes) / BM, per_peer = tmr * tiles_n;
   constexpr int GROUPS = BM / RED_ROWS;

@@ -465,6 +465,10 @@ extern "C" int bshmem_moe_combine(const bshmem_moe_combine_args_t* a, cudaStream
 // Single-PE dispatch whose scratch is a fixed array inside this library (see bshmem/moe_noalloc.h
 // for who needs that and the rules of use).  In host code the array's name is only a handle; the
 // address a kernel can use comes from cudaGetSymbolAddress, looked up once per GPU.
+#include <limits.h>
+
+#include <atomic>
+
 #include "../../include/bshmem/moe_noalloc.h"
 
 namespace {
@@ -481,7 +485,26 @@ static_assert(sizeof(NoAllocBlock) <= BSHMEM_MOE_NOALLOC_SCRATCH_BYTES, "documen
 static __device__ __align__(256) unsigned char g_noalloc_block[BSHMEM_MOE_NOALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-static NoAllocBlock* g_noalloc_addr[kMaxDevices];  // device address of the array, per GPU ordinal
+static std::atomic<NoAllocBlock*> g_noalloc_addr[kMaxDevices];  // device address of the array, per GPU ordinal (any host thread may fill it)
+
+// Device address of the array on the current GPU, looked up on first use.
+static int noalloc_block(NoAllocBlock** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return BSHMEM_MOE_ERR_DRIVER;
+  NoAllocBlock* blk = g_noalloc_addr[dev].load(std::memory_order_acquire);
+  if (!blk) {  // first call on this GPU (it is the current device): resolve the array's device address
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_block);
+    if (e != cudaSuccess || !p) {
+      fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return BSHMEM_MOE_ERR_DRIVER;
+    }
+    blk = (NoAllocBlock*)p;
+    g_noalloc_addr[dev].store(blk, std::memory_order_release);  // two threads racing here store the same address
+  }
+  *out = blk;
+  return BSHMEM_MOE_OK;
+}
 
 }  // namespace
 
@@ -493,18 +516,13 @@ extern "C" int bshmem_moe_dispatch_local_noalloc(const void* x, const int* topk_
             BSHMEM_MOE_NOALLOC_MAX_EXPERTS, BSHMEM_MOE_MAX_TOPK, BSHMEM_MOE_QUANT_BLOCK);
     return BSHMEM_MOE_ERR_SHAPE;
   }
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return BSHMEM_MOE_ERR_DRIVER;
-  if (!g_noalloc_addr[dev]) {  // first call on this GPU (it is the current device): resolve the array's device address
-    void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_block);
-    if (e != cudaSuccess || !p) {
-      fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
-      return BSHMEM_MOE_ERR_DRIVER;
-    }
-    g_noalloc_addr[dev] = (NoAllocBlock*)p;
+  if ((long long)T * K > INT_MAX) {  // row numbers are 32-bit
+    fprintf(stderr, "bshmem_moe_dispatch_local_noalloc: T * K = %lld rows do not fit 32-bit row numbers\n", (long long)T * K);
+    return BSHMEM_MOE_ERR_SHAPE;
   }
-  NoAllocBlock* blk = g_noalloc_addr[dev];
+  NoAllocBlock* blk = nullptr;
+  int bst = noalloc_block(&blk);
+  if (bst) return bst;
   // The block keeps what the previous call left: clear the counters, the barrier word, the flags and the built-in error word.
   if (cudaMemsetAsync(blk, 0, sizeof(NoAllocBlock), stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;
 
@@ -537,4 +555,13 @@ extern "C" int bshmem_moe_dispatch_local_noalloc(const void* x, const int* topk_
     return BSHMEM_MOE_ERR_DRIVER;
   }
   return BSHMEM_MOE_OK;
+}
+
+extern "C" int bshmem_moe_noalloc_error_bits(cudaStream_t stream, int* bits) {
+  if (!bits) return BSHMEM_MOE_ERR_ARGS;
+  NoAllocBlock* blk = nullptr;
+  int st = noalloc_block(&blk);
+  if (st) return st;
+  if (cudaMemcpyAsync(bits, &blk->error_flag, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return BSHMEM_MOE_ERR_DRIVER;
+  return cudaStreamSynchronize(stream) == cudaSuccess ? BSHMEM_MOE_OK : BSHMEM_MOE_ERR_DRIVER;
 }

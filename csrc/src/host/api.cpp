@@ -288,23 +288,47 @@ void nvshmemx_vendor_get_version_info(int* major, int* minor, int* patch) {
   if (patch) *patch = BSHMEM_PATCH;
 }
 
-// A CUDA module loaded with the driver API carries its own copy of the state
-// under the global name `bshmemi_state_d`; look it up and fill it.
-static int module_init_common(CUdeviceptr addr, size_t bytes) {
+// A CUDA module loaded with the driver API (cuModuleLoad, cuLibraryLoad) carries its own copy of the state under
+// the unmangled global name `bshmemi_state_d`, which the device headers emit when the module's source defines
+// BSHMEM_DEVICE_MODULE before including them.  The copy is filled here and, like the copies of the modules that
+// register themselves, again whenever the state changes (heap growth, multicast window), until the matching
+// finalize call.  (reference: src/host/init/init.cu:1829-1916)
+static int module_init_common(void* handle, CUdeviceptr addr, size_t bytes) {
   Runtime& r = rt();
   if (!is_initialized() || !r.have_gpu) return NVSHMEMX_ERROR_INVALID_VALUE;
-  if (bytes != sizeof(bshmemi_state_t)) return NVSHMEMX_ERROR_SYMMETRY;
-  return cudaMemcpy((void*)addr, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice) == cudaSuccess ? NVSHMEMX_SUCCESS : NVSHMEMX_ERROR_INTERNAL;
+  if (bytes != sizeof(bshmemi_state_t)) {
+    ERROR_PRINT("the module's bshmemi_state_d has %zu bytes, this library's has %zu: it was built against other headers", bytes, sizeof(bshmemi_state_t));
+    return NVSHMEMX_ERROR_SYMMETRY;
+  }
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (cudaMemcpy((void*)addr, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice) != cudaSuccess) return NVSHMEMX_ERROR_INTERNAL;
+  for (auto& m : r.driver_modules)
+    if (m.first == handle) { m.second = (void*)addr; return NVSHMEMX_SUCCESS; }
+  r.driver_modules.emplace_back(handle, (void*)addr);
+  return NVSHMEMX_SUCCESS;
+}
+static int module_finalize_common(void* handle) {
+  Runtime& r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  for (size_t i = 0; i < r.driver_modules.size(); ++i)
+    if (r.driver_modules[i].first == handle) {
+      r.driver_modules.erase(r.driver_modules.begin() + i);
+      return NVSHMEMX_SUCCESS;
+    }
+  return NVSHMEMX_ERROR_INVALID_VALUE;
 }
 int nvshmemx_cumodule_init(void* cumodule) {
   const CuTable* d = cu();
   if (!d || !d->cuModuleGetGlobal_) return NVSHMEMX_ERROR_NOT_SUPPORTED;
   CUdeviceptr addr = 0;
   size_t bytes = 0;
-  if (d->cuModuleGetGlobal_(&addr, &bytes, (CUmodule)cumodule, "bshmemi_state_d") != CUDA_SUCCESS) return NVSHMEMX_ERROR_INVALID_VALUE;
-  return module_init_common(addr, bytes);
+  if (d->cuModuleGetGlobal_(&addr, &bytes, (CUmodule)cumodule, "bshmemi_state_d") != CUDA_SUCCESS) {
+    ERROR_PRINT("nvshmemx_cumodule_init: the module has no global `bshmemi_state_d` (define BSHMEM_DEVICE_MODULE before including the device headers in its source)");
+    return NVSHMEMX_ERROR_INVALID_VALUE;
+  }
+  return module_init_common(cumodule, addr, bytes);
 }
-int nvshmemx_cumodule_finalize(void*) { return NVSHMEMX_SUCCESS; }
+int nvshmemx_cumodule_finalize(void* cumodule) { return module_finalize_common(cumodule); }
 int nvshmemx_culibrary_init(void* culibrary) {
   void* sym = nullptr;
   typedef CUresult (*get_global_t)(CUdeviceptr*, size_t*, void*, const char*);
@@ -312,9 +336,9 @@ int nvshmemx_culibrary_init(void* culibrary) {
   CUdeviceptr addr = 0;
   size_t bytes = 0;
   if (((get_global_t)sym)(&addr, &bytes, culibrary, "bshmemi_state_d") != CUDA_SUCCESS) return NVSHMEMX_ERROR_INVALID_VALUE;
-  return module_init_common(addr, bytes);
+  return module_init_common(culibrary, addr, bytes);
 }
-int nvshmemx_culibrary_finalize(void*) { return NVSHMEMX_SUCCESS; }
+int nvshmemx_culibrary_finalize(void* culibrary) { return module_finalize_common(culibrary); }
 
 // ------------------------------------------------------------------ memory
 static void* alloc_common(size_t size, size_t alignment, bool zero, const char* fn) {

@@ -114,6 +114,13 @@ int push_device_state() {
       return ST_INTERNAL;
     }
   }
+  // Modules loaded through the driver API and announced with nvshmemx_cumodule_init / nvshmemx_culibrary_init.
+  for (auto& m : r.driver_modules) {
+    if (cudaMemcpy(m.second, &r.dstate, sizeof(r.dstate), cudaMemcpyHostToDevice) != cudaSuccess) {
+      ERROR_PRINT("copying the device state into a driver-API module failed");
+      return ST_INTERNAL;
+    }
+  }
   return ST_SUCCESS;
 }
 

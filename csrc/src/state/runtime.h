@@ -98,6 +98,7 @@ struct Runtime {
   int max_teams = 128;
   std::vector<std::pair<StateAddrGetter, std::string>> modules;
   std::atomic<bool> modules_pending{false};  // a module registered after the last state push
+  std::vector<std::pair<void*, void*>> driver_modules;  // (CUmodule / CUlibrary, device address of its state copy), see nvshmemx_cumodule_init
   cudaStream_t stream = nullptr;             // internal stream of blocking calls
   std::vector<cudaStream_t> peer_streams;    // non-blocking host RMA, indexed by distance % size
   std::vector<bool> peer_stream_used;

@@ -6,8 +6,8 @@
   tile reads their sum through the switch (``multimem.ld_reduce``) inside the same kernel, otherwise
   the epilogue pushes partial tiles into the owning rank's receive slots and reduces there
   (``mode="rs"``); ``mode="ar"`` additionally delivers the reduced tile to all ranks.
-* :class:`AllGatherGemm` – column-parallel linear: two spare warps of every CTA spread the local
-  activation shard to all peers while the GEMM consumes shards as they land.
+* :class:`AllGatherGemm` – column-parallel linear: copy engines (or two spare warps of every CTA)
+  spread the local activation shard to all peers while the GEMM consumes shards as they land.
 
 Weights use torch's Linear layout ``[out_features, in_features]``; activations are ``[tokens,
 in_features]``; everything is bf16 with fp32 accumulation.  The collective variants keep their
@@ -36,7 +36,7 @@ class _Args(C.Structure):
                 ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
                 ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
                 ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p),
-                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p), ("act", C.c_int)]
+                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p), ("act", C.c_int), ("ag_external", C.c_int)]
 
 
 _ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
@@ -218,9 +218,15 @@ class AllGatherGemm:
     Write this rank's ``[M/npes, K]`` shard into :attr:`shard` (a view of the symmetric gathered
     buffer), then ``forward(w)`` with ``w`` ``[N_local, K]`` returns ``[M, N_local]``.  A world sync
     is issued on the stream before each launch so that no peer overwrites a buffer still being read.
+
+    ``copy_engine=True`` (default): the shard goes to the peers as one stream-ordered put with signal per
+    peer (``nvshmemx_putmem_signal_on_stream``: a copy-engine copy and a flag write), nearest peer first, on
+    a side stream that runs beside the GEMM kernel; no SM time is spent on the transfer.  The calling stream
+    waits for those copies after the kernel, so the shard may be overwritten as soon as ``forward`` has
+    been issued.  ``copy_engine=False``: two warps of every CTA of the GEMM kernel send the shard.
     """
 
-    def __init__(self, M: int, K: int, wait_limit_ms: int = 0):
+    def __init__(self, M: int, K: int, wait_limit_ms: int = 0, copy_engine: bool = True):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
@@ -234,11 +240,16 @@ class AllGatherGemm:
             self.gathered = core.tensor((M, K), torch.bfloat16)
             self.flags = core.tensor((self.npes * max(self.rows // 128, 1),), torch.int64, zero=True)
             self._peer = {q: (core.peer_ptr(self.gathered, q), core.peer_ptr(self.flags, q)) for q in range(self.npes)}
+            self.copy_engine = copy_engine
+            if copy_engine:
+                self._comm = torch.cuda.Stream(device=self.device)
+                self._ready, self._sent = torch.cuda.Event(), torch.cuda.Event()
             core.barrier_all()
             torch.cuda.synchronize()
         else:
             self.gathered = torch.empty(M, K, dtype=torch.bfloat16, device=self.device)
             self.flags = None
+            self.copy_engine = False
         self.shard = self.gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
         self.out = None
 
@@ -266,7 +277,23 @@ class AllGatherGemm:
                 a.ag_peer[q] = self._peer[q][0]
                 a.ag_flags_peer[q] = self._peer[q][1]
             self.core.sync_all()  # every rank has finished reading the previous gathered buffer
+            if self.copy_engine:
+                a.ag_external = 1
+                main = torch.cuda.current_stream()
+                self._ready.record(main)
+                self._comm.wait_event(self._ready)
+                lib = H.load()
+                tmr = max(self.rows // 128, 1)
+                shard_ptr, shard_bytes = self.shard.data_ptr(), self.rows * self.K * 2
+                flag_ptr = self.flags.data_ptr() + 8 * self.rank * tmr
+                for o in range(1, self.npes):
+                    # the same symmetric addresses on the peer: its slot for my shard, its flag for my shard
+                    lib.nvshmemx_putmem_signal_on_stream(C.c_void_p(shard_ptr), C.c_void_p(shard_ptr), shard_bytes, C.c_void_p(flag_ptr), self.epoch, 9,
+                                                         (self.rank + o) % self.npes, C.c_void_p(self._comm.cuda_stream))
+                self._sent.record(self._comm)
         _launch(a, torch.cuda.current_stream().cuda_stream)
+        if self.npes > 1 and self.copy_engine:
+            torch.cuda.current_stream().wait_event(self._sent)  # the shard may be rewritten once the copies have read it
         return out
 
     __call__ = forward

@@ -107,14 +107,19 @@ def main():
     shard = torch.randn(M // n, H, device=env.dev).to(torch.bfloat16)
     flops = 2.0 * M * Nl * H
     link = (n - 1) / n * M * H * 2
+    for ce in (True, False):
+        if n == 1 and not ce:
+            continue
+        ag = fg.AllGatherGemm(M, H, copy_engine=ce)
+        ag.shard.copy_(shard)
+        def step_ag():
+            i[0] += 1
+            ag(ws[i[0] % sets])
+        ms = env.time_ms(step_ag, iters=args.iters, warmup=5)
+        fg.check_errors()
+        report("ag_gemm_fused", ms, flops, link, M=M, N=Nl, K=H, path=("copy engines" if ce else "warps of the GEMM kernel") if n > 1 else "one PE")
+        ag.close()
     ag = fg.AllGatherGemm(M, H)
-    ag.shard.copy_(shard)
-    def step_ag():
-        i[0] += 1
-        ag(ws[i[0] % sets])
-    ms = env.time_ms(step_ag, iters=args.iters, warmup=5)
-    fg.check_errors()
-    report("ag_gemm_fused", ms, flops, link, M=M, N=Nl, K=H)
     if n > 1:
         gathered = torch.empty(M, H, dtype=torch.bfloat16, device=env.dev)
         out2 = torch.empty(M, Nl, dtype=torch.bfloat16, device=env.dev)

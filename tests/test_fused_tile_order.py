@@ -68,25 +68,24 @@ def test_cta_pairs_get_two_row_tiles_of_one_column_block(mode, npes, M, N):
             assert a[1] == b[1] and a[2] == b[2] and b[0] == a[0] + 1 and a[3] % 2 == 0, (rank, u, a, b)
 
 
-def test_all_gather_row_slices_cover_every_block_exactly():
-    """The all-gather mode splits a PE's shard by rows over all CTAs of the grid and counts delivered rows per
-    128-row block: the slices must tile the shard, and every block must collect exactly 128 rows."""
+def test_all_gather_units_tile_a_block_and_are_dealt_to_every_cta():
+    """The all-gather mode cuts each 128-row block into units and deals them round-robin to the CTAs; the arrival
+    counter of a block must grow by exactly `units_per_block`, units must be whole 16-byte pieces that tile the block,
+    and a row is only split while there are more CTAs than units."""
     lib = _lib()
-    lib.bshmem_fused_test_ag_slice.argtypes = [C.c_int] * 3 + [C.POINTER(C.c_int)]
+    lib.bshmem_fused_test_ag_units.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_int)]
     out = (C.c_int * 2)()
-    for rows in (128, 256, 384, 1024, 4096):
-        for grid in (1, 2, 3, 7, 64, 132, 148, 1000):
-            per_block = [0] * (rows // BM)
-            nxt = 0
-            for b in range(grid):
-                assert lib.bshmem_fused_test_ag_slice(rows, grid, b, out) == 0
-                lo, hi = out[0], out[1]
-                assert lo == nxt and hi >= lo
-                nxt = hi
-                for blk in range(lo // BM, (hi - 1) // BM + 1 if hi > lo else lo // BM):
-                    per_block[blk] += min((blk + 1) * BM, hi) - max(blk * BM, lo)
-            assert nxt == rows and per_block == [BM] * (rows // BM), (rows, grid, per_block)
-    assert lib.bshmem_fused_test_ag_slice(128, 4, 4, out) != 0
+    for K in (64, 128, 1024, 2048, 3584, 8192, 28672):
+        for grid in (1, 2, 3, 64, 128, 132, 148, 296):
+            assert lib.bshmem_fused_test_ag_units(K, grid, out) == 0
+            unit, per_block = out[0], out[1]
+            assert unit % 16 == 0 and unit * per_block == BM * K * 2
+            assert per_block >= BM and (per_block == BM or unit >= 2048)
+            assert per_block >= grid or unit < 4096       # every CTA gets a unit of each block unless units are small already
+            delivered = sum(len(range(b, per_block, grid)) for b in range(grid))
+            assert delivered == per_block
+    assert lib.bshmem_fused_test_ag_units(100, 148, out) != 0
+    assert lib.bshmem_fused_test_ag_units(8192, 148, out) == 0 and (out[0], out[1]) == (8192, 256)
 
 
 @pytest.mark.parametrize("mode,npes,M,N", [(RS, 2, 1024, 768), (RS, 8, 8192, 1024), (AR, 4, 2048, 512), (RS, 3, 768, 256)])

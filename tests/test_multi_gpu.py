@@ -107,5 +107,10 @@ def test_tp_mlp_matches_single_device():
 
 
 @need2
+def test_device_module_via_driver_api():
+    run_workers("device_module_via_driver_api", NG, gpu=True, env=NO_NVLS, timeout=300)
+
+
+@need2
 def test_rank_leaves_between_steps():
     run_workers("rank_leaves_between_steps", NG, gpu=True, env=NO_NVLS)

@@ -172,3 +172,10 @@ def test_copy_engine_collectives_on_one_pe(nv):
     assert nv.error_bits() == 0
     nv.free_tensor(src)
     nv.free_tensor(dst)
+
+
+def test_device_code_in_a_separately_loaded_module():
+    """A cubin built from tests/data/device_module_kernel.cu is loaded with the driver API, given the library state with
+    nvshmemx_cumodule_init and puts to PE 0 (itself).  Runs as a child process with its own initialisation."""
+    from tests._mp import run_workers
+    run_workers("device_module_via_driver_api", 1, gpu=True, env={"NVSHMEM_DISABLE_NVLS": "1"}, timeout=300)

@@ -25,6 +25,8 @@ def _load():
     lib = _lib()
     lib.bshmem_moe_dispatch_local_noalloc.restype = C.c_int
     lib.bshmem_moe_dispatch_local_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.bshmem_moe_noalloc_error_bits.restype = C.c_int
+    lib.bshmem_moe_noalloc_error_bits.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
     return lib
 
 
@@ -52,18 +54,26 @@ def _reference(lib, x, idx, E):
     return recv, slot, offs
 
 
-def _noalloc(lib, x, idx, E):
+def _noalloc(lib, x, idx, E, own_error_word=True):
+    """`own_error_word=False` passes no error flag: the kernel's error bits then go to the word inside the built-in
+    array and are read back with bshmem_moe_noalloc_error_bits."""
     T, H = x.shape
     K = idx.shape[1]
     recv = torch.zeros(T * K, H, dtype=torch.bfloat16, device=x.device)
     slot = torch.full((T, K), -7, dtype=torch.int32, device=x.device)
     offs = torch.zeros(E + 1, dtype=torch.int32, device=x.device)
     err = torch.zeros(1, dtype=torch.int32, device=x.device)
-    st = lib.bshmem_moe_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), T, H, K, E, recv.data_ptr(), slot.data_ptr(), offs.data_ptr(), err.data_ptr(),
-                                               torch.cuda.current_stream().cuda_stream)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    st = lib.bshmem_moe_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), T, H, K, E, recv.data_ptr(), slot.data_ptr(), offs.data_ptr(),
+                                               err.data_ptr() if own_error_word else None, stream)
     assert st == 0
-    torch.cuda.synchronize()
-    assert int(err) == 0
+    if own_error_word:
+        torch.cuda.synchronize(x.device)
+        assert int(err) == 0
+    else:
+        bits = C.c_int(-1)
+        assert lib.bshmem_moe_noalloc_error_bits(stream, C.byref(bits)) == 0
+        assert bits.value == 0
     return recv, slot, offs
 
 
@@ -83,21 +93,37 @@ def _canonical(x, idx, recv, slot, offs, E):
     return e_of[order], tt[order]
 
 
-def test_noalloc_dispatch_matches_the_ordinary_entry_point_twice():
-    lib = _load()
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+def _compare_on(lib, device_index, own_error_word):
+    torch.cuda.set_device(device_index)
+    dev = torch.device("cuda", device_index)
     g = torch.Generator(device=dev).manual_seed(99)
     for call, (T, H, K, E) in enumerate([(300, 512, 4, 24), (257, 1024, 8, 64)]):  # two calls in a row, different sizes
         x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
         idx = torch.rand(T, E, device=dev, generator=g).topk(K, dim=-1).indices.to(torch.int32).contiguous()
         idx[call, 0] = -1
         ref = _reference(lib, x, idx, E)
-        got = _noalloc(lib, x, idx, E)
+        got = _noalloc(lib, x, idx, E, own_error_word)
         assert torch.equal(got[2], ref[2]), "segment boundaries differ"
         ce_ref, ct_ref = _canonical(x, idx, *ref, E)
         ce_got, ct_got = _canonical(x, idx, *got, E)
         assert torch.equal(ce_ref, ce_got) and torch.equal(ct_ref, ct_got)
+
+
+def test_noalloc_dispatch_matches_the_ordinary_entry_point_twice():
+    _compare_on(_load(), 0, own_error_word=True)
+
+
+def test_noalloc_dispatch_without_an_error_flag_keeps_its_error_bits_readable():
+    _compare_on(_load(), 0, own_error_word=False)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_noalloc_dispatch_on_a_second_gpu_uses_that_gpus_array():
+    """The array exists once per GPU and its address is looked up per GPU: the same two calls on device 1."""
+    try:
+        _compare_on(_load(), 1, own_error_word=True)
+    finally:
+        torch.cuda.set_device(0)
 
 
 def test_noalloc_dispatch_refuses_sizes_beyond_its_scratch():
@@ -111,3 +137,7 @@ def test_noalloc_dispatch_refuses_sizes_beyond_its_scratch():
     st = lib.bshmem_moe_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), 8, 128, 1, 1025, out.data_ptr(), slot.data_ptr(), offs.data_ptr(), None,
                                                torch.cuda.current_stream().cuda_stream)
     assert st == 2  # BSHMEM_MOE_ERR_SHAPE
+    # a product T * K beyond 32-bit row numbers is a shape error too, not a kernel full of overflow flags
+    st = lib.bshmem_moe_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), 1 << 28, 128, 16, 8, out.data_ptr(), slot.data_ptr(), offs.data_ptr(), None,
+                                               torch.cuda.current_stream().cuda_stream)
+    assert st == 2

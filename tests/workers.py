@@ -877,7 +877,7 @@ def collectives_on_stream():
             src.copy_(make(count))
             allsrc = _gather(src)
             want = _oracle(op, allsrc)
-            for algo in (red_algos if op == "sum" else red_algos[:4]):
+            for algo in red_algos:  # the NVLS algorithms cover float sums and 4- / 8-byte integer operators; other cases fall back
                 dst.zero_()
                 nv.barrier_all()
                 nv.reduce(0, dst, src, op, algo=algo)
@@ -1046,6 +1046,15 @@ def device_collectives_and_tiles():
         r1, c1 = min(r0 + rows, R), min(c0 + cols, Cc)
         want[r0:r1, c0:c1] = (torch.arange(R * Cc, dtype=torch.float32).reshape(R, Cc) * (n * (n + 1) // 2))[r0:r1, c0:c1]
         assert torch.equal(t_dst.cpu(), want), (algo, r0, c0)
+    # several CTAs at once, each with its own tile and its own row of sync flags
+    for algo in (1, 2):
+        t_dst.zero_()
+        nv.barrier_all()
+        assert dt.devtest_tile_allreduce_multi(0, C.c_void_p(t_dst.data_ptr()), C.c_void_p(t_src.data_ptr()), R, Cc, 4, 16, 24, 64, algo, 0, 4, _stream()) == 0
+        torch.cuda.synchronize()
+        want = torch.zeros(R, Cc)
+        want[4:100, 16:80] = (torch.arange(R * Cc, dtype=torch.float32).reshape(R, Cc) * (n * (n + 1) // 2))[4:100, 16:80]
+        assert torch.equal(t_dst.cpu(), want), ("multi-CTA tile reduce", algo)
     right = (RANK + 1) % n
     t_dst.zero_()
     nv.barrier_all()
@@ -1179,18 +1188,19 @@ def fused_gemm_collectives():
         x_full = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         w = (torch.randn(Nl, K, device="cuda") * 0.05).to(torch.bfloat16)
         rows = M // n
-        ag = fg.AllGatherGemm(M, K, wait_limit_ms=5000)
-        for it in range(3):
-            xi = (x_full.float() * (it + 1)).to(torch.bfloat16)
-            ag.shard.copy_(xi[RANK * rows:(RANK + 1) * rows])
-            out = ag(w)
-            torch.cuda.synchronize()
-            fg.check_errors()
-            ref = xi.float() @ w.float().t()
-            err = (out.float() - ref).abs().max().item()
-            assert err <= ref.abs().max().item() * 2 ** -7 + 1e-3, ("ag", M, K, Nl, it, err)
-            assert torch.equal(ag.gathered, xi), "gathered activations differ"
-        ag.close()
+        for ce in (True, False):  # shard pushed by copy engines on a side stream, and by two warps of every CTA
+            ag = fg.AllGatherGemm(M, K, wait_limit_ms=5000, copy_engine=ce)
+            for it in range(3):
+                xi = (x_full.float() * (it + 1)).to(torch.bfloat16)
+                ag.shard.copy_(xi[RANK * rows:(RANK + 1) * rows])
+                out = ag(w)
+                torch.cuda.synchronize()
+                fg.check_errors()
+                ref = xi.float() @ w.float().t()
+                err = (out.float() - ref).abs().max().item()
+                assert err <= ref.abs().max().item() * 2 ** -7 + 1e-3, ("ag", ce, M, K, Nl, it, err)
+                assert torch.equal(ag.gathered, xi), "gathered activations differ"
+            ag.close()
     teardown(nv)
 
 
@@ -1336,6 +1346,55 @@ def team_multicast_windows():
         assert lib.nvshmemx_mc_ptr(int(again), C.c_void_p(probe.data_ptr()))
         nv.team_destroy(again)
     for t in (src, dst, big, probe):
+        nv.free_tensor(t)
+    teardown(nv)
+
+
+@worker
+def device_module_via_driver_api():
+    """Device code in a separately loaded module: a kernel is compiled to a cubin with nvcc, loaded with cuModuleLoadData,
+    handed the library state with nvshmemx_cumodule_init, and puts to the next PE."""
+    import subprocess
+    import tempfile
+    nv = setup()
+    from nvshmem_b200.bindings import host as H
+    from nvshmem_b200.utils.build import CSRC, nvcc
+    lib = H.load()
+    n, me = WORLD, RANK
+    src_file = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "device_module_kernel.cu")
+    with tempfile.TemporaryDirectory() as tmp:
+        cubin = os.path.join(tmp, f"module_{me}.cubin")
+        subprocess.run([nvcc(), "-cubin", "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(CSRC / "include"), "-o", cubin, src_file], check=True)
+        image = open(cubin, "rb").read()
+    cu = C.CDLL("libcuda.so.1")
+    mod, fn = C.c_void_p(), C.c_void_p()
+    torch.cuda.synchronize()  # the primary context is current on this thread
+    assert cu.cuModuleLoadData(C.byref(mod), image) == 0
+    assert cu.cuModuleGetFunction(C.byref(fn), mod, b"module_put") == 0
+    lib.nvshmemx_cumodule_init.argtypes = [C.c_void_p]
+    lib.nvshmemx_cumodule_finalize.argtypes = [C.c_void_p]
+    assert lib.nvshmemx_cumodule_init(mod) == 0
+    count = 1000
+    dst, src = nv.tensor((count,), torch.int32, zero=True), nv.tensor((count,), torch.int32)
+    sig = nv.tensor((1,), torch.int64, zero=True)
+    facts = torch.zeros(2, dtype=torch.int32, device="cuda")
+    src.copy_(torch.arange(count, device="cuda", dtype=torch.int32) + 1000 * me)
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    right, left = (me + 1) % n, (me - 1) % n
+    args = [C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), C.c_int(count), C.c_void_p(sig.data_ptr()), C.c_int(right), C.c_void_p(facts.data_ptr())]
+    argv = (C.c_void_p * len(args))(*[C.cast(C.pointer(a), C.c_void_p) for a in args])
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert cu.cuLaunchKernel(fn, 1, 1, 1, 256, 1, 1, 0, stream, argv, None) == 0
+    nv.signal_wait(sig, count, nv.ComparisonType.CMP_EQ)   # the left neighbour's data has landed
+    torch.cuda.synchronize()
+    assert facts.tolist() == [me, n]
+    assert torch.equal(dst.cpu(), torch.arange(count, dtype=torch.int32) + 1000 * left)
+    assert nv.error_bits() == 0
+    nv.barrier_all()
+    assert lib.nvshmemx_cumodule_finalize(mod) == 0 and lib.nvshmemx_cumodule_finalize(mod) != 0
+    assert cu.cuModuleUnload(mod) == 0
+    for t in (dst, src, sig):
         nv.free_tensor(t)
     teardown(nv)
 
