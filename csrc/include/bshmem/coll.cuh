@@ -10,8 +10,10 @@
 //   allreduce   one-shot pull (latency), two-shot = pull-reduce my chunk + push it to all
 //               (bandwidth), NVLS one-shot / two-shot with multimem.ld_reduce / multimem.st
 //   reducescatter  pull-reduce my block, or multimem.ld_reduce of it
-//   fcollect / broadcast  push (vector stores) or multimem.st, then barrier; flag-in-data
-//               (LL) variant for small fcollect
+//   fcollect / broadcast  push (vector stores) or multimem.st, then barrier; flag-in-data variants
+//               without any barrier: 8-byte packets (LL) for the smallest fcollect / allreduce, 128-byte
+//               packets (LL128: 120 bytes of data + an 8-byte flag) for fcollect, allreduce and broadcast
+//               up to NVSHMEM_LL128_THRESHOLD bytes per PE
 //   alltoall    push block p to PE p, then barrier
 // 16-bit floating types accumulate in fp32 across PEs and round once.
 // (reference behaviour: src/include/non_abi/device/coll/{barrier,reduce,reducescatter,fcollect,alltoall,broadcast}.cuh)
@@ -22,8 +24,8 @@
 namespace bshmem {
 
 enum ReduceOp { OP_AND = 0, OP_OR = 1, OP_XOR = 2, OP_MIN = 3, OP_MAX = 4, OP_SUM = 5, OP_PROD = 6 };
-enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4, RED_LL = 5 };
-enum FcollectAlgo { FC_AUTO = 0, FC_PUSH = 1, FC_LL = 2, FC_NVLS = 3 };
+enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4, RED_LL = 5, RED_LL128 = 6 };
+enum FcollectAlgo { FC_AUTO = 0, FC_PUSH = 1, FC_LL = 2, FC_NVLS = 3, FC_LL128 = 4 };
 enum RsAlgo { RS_AUTO = 0, RS_PULL = 1, RS_NVLS = 2 };
 enum BcastAlgo { BC_AUTO = 0, BC_PUSH = 1, BC_LL = 2, BC_NVLS = 3, BC_PULL = 4 };
 
@@ -242,6 +244,216 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int which, size
   *hi = b < n ? b : n;
 }
 
+// ------------------------------------------------------------------ LL128: 128-byte packets, flag in the data
+// A packet is one 128-byte line: 120 bytes of payload followed by an 8-byte flag that carries the generation of
+// the call.  Eight consecutive lanes of a warp write (or read) one packet with ONE 16-byte access each, issued by the
+// same instruction, so the line travels and lands as a unit: a reader that finds the flag of the generation it
+// waits for has the 120 bytes that were written with it, and no barrier or separate signal is needed.  A warp moves
+// four packets per instruction.  Messages must be 8-byte aligned multiples of 8 bytes; scopes must be made of whole
+// warps (warp, warpgroup, block).  The packets of a team live in its LL128 area:
+//   [ two generations x size x max_packets  : fcollect / allreduce, slot `my_pe` of every member ]
+//   [ two generations x max_packets         : broadcast ]
+//   [ size x 8 bytes                        : broadcast acknowledgements ]
+// (reference: src/include/non_abi/device/common/nvshmemi_common_device.cuh:699-920, packLL128 / recvLL128;
+//  src/include/non_abi/device/coll/fcollect.cuh:100-314; src/include/non_abi/device/coll/broadcast.cuh:151-334)
+constexpr int LL128_DATA = 120, LL128_LINE = 128;
+__device__ __forceinline__ size_t ll128_packets(size_t bytes) { return (bytes + LL128_DATA - 1) / LL128_DATA; }
+struct Ll128Layout {
+  size_t max_packets;   // per message
+  char* exchange;       // [2][size][max_packets] lines
+  char* bcast;          // [2][max_packets] lines
+  uint64_t* acks;       // [size]
+};
+__device__ __forceinline__ Ll128Layout ll128_layout(const bshmemi_team_t* t) {
+  Ll128Layout l;
+  const size_t size = (size_t)t->size;
+  // area = 2*size*P*128 + 2*P*128 + size*8 (rounded up by the host)  =>  P = (bytes - size*8) / (256*(size+1))
+  l.max_packets = t->ll128_bytes > size * 8 ? (t->ll128_bytes - size * 8) / (2 * LL128_LINE * (size + 1)) : 0;
+  l.exchange = (char*)t->ll128_base;
+  l.bcast = l.exchange + 2 * size * l.max_packets * LL128_LINE;
+  l.acks = (uint64_t*)(l.bcast + 2 * l.max_packets * LL128_LINE);
+  return l;
+}
+// The 16 bytes that lane `j` (0..7) of a packet group contributes to packet `k` of a message: payload bytes
+// [k*120 + 16j, +16) for j < 7; 8 payload bytes and the flag for j == 7.  Bytes past the end of the message are zero.
+__device__ __forceinline__ uint4 ll128_piece(const char* msg, size_t bytes, size_t k, int j, uint64_t flag) {
+  const size_t off = k * LL128_DATA + (size_t)j * 16;
+  uint64_t lo = 0, hi = 0;
+  if (off < bytes) lo = *(const uint64_t*)(msg + off);
+  if (j == 7) hi = flag;
+  else if (off + 8 < bytes) hi = *(const uint64_t*)(msg + off + 8);
+  return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+}
+__device__ __forceinline__ void ll128_store_line(char* line, int j, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(line + j * 16), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ll128_load_line(const char* line, int j) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(line + j * 16) : "memory");
+  return v;
+}
+// Whole-warp call: lane group g = lane/8 reads packet `line` (null for a group with nothing to read) until its flag is
+// `flag`; returns this lane's 16 bytes.  `*err` is set if the bound of all device waits runs out.
+__device__ __forceinline__ uint4 ll128_wait_line(const char* line, int lane, uint64_t flag, uint64_t start, int* err) {
+  const int j = lane & 7, leader = (lane & ~7) + 7;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  uint32_t spins = 0;
+  for (;;) {
+    if (line) v = ll128_load_line(line, j);
+    const uint64_t seen = ((uint64_t)__shfl_sync(0xffffffffu, v.w, leader) << 32) | __shfl_sync(0xffffffffu, v.z, leader);
+    const bool ok = !line || seen == flag;
+    if (__all_sync(0xffffffffu, ok)) return v;
+    if ((++spins & 0xff) == 0 && global_timer_ns() - start > bshmemi_state_d.wait_timeout_ns) {
+      if (!ok && j == 7) record_timeout(line + LL128_DATA, flag, seen, BSHMEM_WHERE_COLL);
+      *err = 1;
+      return v;
+    }
+  }
+}
+// Writes this lane's payload bytes of packet `k` to the message at `msg` (bytes past the end are dropped).
+__device__ __forceinline__ void ll128_unpack(char* msg, size_t bytes, size_t k, int j, uint4 v) {
+  const size_t off = k * LL128_DATA + (size_t)j * 16;
+  if (off < bytes) *(uint64_t*)(msg + off) = ((uint64_t)v.y << 32) | v.x;
+  if (j != 7 && off + 8 < bytes) *(uint64_t*)(msg + off + 8) = ((uint64_t)v.w << 32) | v.z;
+}
+template <int SCOPE>
+__device__ __forceinline__ bool ll128_scope_ok() {
+  return SCOPE != SCOPE_THREAD && (group_size<SCOPE>() & 31) == 0;
+}
+
+// fcollect: every member's `bytes` land at dst + m * bytes on every member.
+template <int SCOPE>
+__device__ __forceinline__ int fcollect_ll128(const bshmemi_team_t* t, void* dst, const void* src, size_t bytes, int slot) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const int lane = rank & 31, warp = rank >> 5, nwarps = G >> 5, j = lane & 7;
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[slot] + 1;
+  const Ll128Layout L = ll128_layout(t);
+  const size_t npk = ll128_packets(bytes);
+  char* buf = L.exchange + (gen & 1) * ((size_t)size * L.max_packets * LL128_LINE);
+  // send: packet k of my message into slot `me` of every member
+  for (size_t q = warp; q * 4 < npk; q += nwarps) {
+    const size_t k = q * 4 + (lane >> 3);
+    if (k >= npk) continue;
+    const uint4 v = ll128_piece((const char*)src, bytes, k, j, gen);
+    for (int sft = 0; sft < size; ++sft) {
+      const int p = (me + 1 + sft) % size;
+      ll128_store_line(translate(buf + ((size_t)me * L.max_packets + k) * LL128_LINE, team_world_pe(t, p)), j, v);
+    }
+  }
+  // receive: the packets of every member, in my own buffer
+  int err = 0;
+  const uint64_t start = global_timer_ns();
+  const size_t total = (size_t)size * npk;
+  for (size_t q = warp; q * 4 < total && !err; q += nwarps) {
+    const size_t i = q * 4 + (lane >> 3);
+    const bool mine = i < total;
+    const size_t m = mine ? i / npk : 0, k = mine ? i % npk : 0;
+    const uint4 v = ll128_wait_line(mine ? buf + (m * L.max_packets + k) * LL128_LINE : nullptr, lane, gen, start, &err);
+    if (mine && !err) ll128_unpack((char*)dst + m * bytes, bytes, k, j, v);
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[slot] = gen;
+  return err;
+}
+
+// allreduce: every member pushes its whole vector to every member; each member reduces the `size` copies locally.
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int allreduce_ll128(const bshmemi_team_t* t, T* dst, const T* src, size_t n, int slot) {
+  typedef typename Acc<T>::type A;
+  constexpr int PER8 = 8 / (int)sizeof(T);  // elements per 8-byte word
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const int lane = rank & 31, warp = rank >> 5, nwarps = G >> 5, j = lane & 7;
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[slot] + 1;
+  const Ll128Layout L = ll128_layout(t);
+  const size_t bytes = n * sizeof(T), npk = ll128_packets(bytes);
+  char* buf = L.exchange + (gen & 1) * ((size_t)size * L.max_packets * LL128_LINE);
+  for (size_t q = warp; q * 4 < npk; q += nwarps) {
+    const size_t k = q * 4 + (lane >> 3);
+    if (k >= npk) continue;
+    const uint4 v = ll128_piece((const char*)src, bytes, k, j, gen);
+    for (int sft = 0; sft < size; ++sft) {
+      const int p = (me + 1 + sft) % size;
+      ll128_store_line(translate(buf + ((size_t)me * L.max_packets + k) * LL128_LINE, team_world_pe(t, p)), j, v);
+    }
+  }
+  group_sync<SCOPE>();  // in place: all of src has been sent before any of dst is written
+  int err = 0;
+  const uint64_t start = global_timer_ns();
+  for (size_t q = warp; q * 4 < npk && !err; q += nwarps) {
+    const size_t k = q * 4 + (lane >> 3);
+    const bool mine = k < npk;
+    A acc[2 * PER8];
+    for (int m = 0; m < size; ++m) {
+      const uint4 v = ll128_wait_line(mine ? buf + ((size_t)m * L.max_packets + k) * LL128_LINE : nullptr, lane, gen, start, &err);
+      T e[2 * PER8];
+      memcpy(e, &v, 16);
+#pragma unroll
+      for (int x = 0; x < 2 * PER8; ++x) acc[x] = m == 0 ? to_acc<T>(e[x]) : combine<A, OP>(acc[x], to_acc<T>(e[x]));
+    }
+    if (mine && !err) {
+      T e[2 * PER8];
+#pragma unroll
+      for (int x = 0; x < 2 * PER8; ++x) e[x] = from_acc<T>(acc[x]);
+      uint4 v;
+      memcpy(&v, e, 16);
+      ll128_unpack((char*)dst, bytes, k, j, v);  // lane 7's upper half held the flag: unpack drops it
+    }
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[slot] = gen;
+  return err;
+}
+
+// broadcast: the root pushes its message to every member; the others poll their own buffer.  Data flows one way, so
+// a root that runs ahead could overwrite a buffer half that a slow member still reads: every member therefore
+// acknowledges each broadcast to all members (an 8-byte store, nobody waits for it), and a root starts generation g
+// only once all members have acknowledged g - 2, which is normally long past.  Broadcasts have their own generation
+// counter (the collective-epoch word of slot 1, which no flag-in-data collective uses) and their own packet area.
+template <int SCOPE>
+__device__ __forceinline__ int broadcast_ll128(const bshmemi_team_t* t, void* dst, const void* src, size_t bytes, int root) {
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  const int lane = rank & 31, warp = rank >> 5, nwarps = G >> 5, j = lane & 7;
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS + 1;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[0] + 1;
+  const Ll128Layout L = ll128_layout(t);
+  const size_t npk = ll128_packets(bytes);
+  char* buf = L.bcast + (gen & 1) * (L.max_packets * LL128_LINE);
+  int err = 0;
+  const uint64_t start = global_timer_ns();
+  if (me == root) {
+    if (gen > 2) {
+      for (int m = rank; m < size; m += G) err |= poll_ge<false>(L.acks + m, gen - 2);
+      group_sync<SCOPE>();
+    }
+    for (size_t q = warp; q * 4 < npk; q += nwarps) {
+      const size_t k = q * 4 + (lane >> 3);
+      if (k >= npk) continue;
+      const uint4 v = ll128_piece((const char*)src, bytes, k, j, gen);
+      for (int sft = 1; sft < size; ++sft) ll128_store_line(translate(buf + k * LL128_LINE, team_world_pe(t, (me + sft) % size)), j, v);
+      if (dst != src) ll128_unpack((char*)dst, bytes, k, j, v);
+    }
+  } else {
+    for (size_t q = warp; q * 4 < npk && !err; q += nwarps) {
+      const size_t k = q * 4 + (lane >> 3);
+      const bool mine = k < npk;
+      const uint4 v = ll128_wait_line(mine ? buf + k * LL128_LINE : nullptr, lane, gen, start, &err);
+      if (mine && !err) ll128_unpack((char*)dst, bytes, k, j, v);
+    }
+  }
+  group_sync<SCOPE>();  // every thread of the group is done with the buffer half
+  for (int m = rank; m < size; m += G) st_relaxed_sys(translate(L.acks + me, team_world_pe(t, m)), gen);
+  if (rank == 0) epochs[0] = gen;
+  return err;
+}
+
 // ------------------------------------------------------------------ allreduce, flag-in-data (small messages)
 // Every member pushes its `n` elements as 8-byte packets (4 bytes of payload + the 4-byte generation of
 // this call) into slot `my_pe` of every member's packet buffer; each member then polls the packets of all
@@ -377,8 +589,15 @@ __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, 
   // Flag-in-data: whole small messages only (one group owns the team's packet buffer).
   const bool ll_ok = lo == 0 && slot == 0 && bytes > 0 && (bytes & 3) == 0 && ((uintptr_t)src & 3) == 0 && 4 * bytes * size <= t->ll_bytes;
   if (algo == RED_AUTO && ll_ok && bytes <= bshmemi_state_d.fcollect_ll_threshold) algo = RED_LL;
+  const bool ll128_ok = lo == 0 && slot == 0 && bytes > 0 && (bytes & 7) == 0 && (((uintptr_t)src | (uintptr_t)dst) & 7) == 0 && ll128_scope_ok<SCOPE>() &&
+                        ll128_packets(bytes) <= ll128_layout(t).max_packets;
+  if (algo == RED_AUTO && ll128_ok && bytes <= bshmemi_state_d.ll128_threshold) algo = RED_LL128;
   if (algo == RED_LL) {
     if (ll_ok) return allreduce_ll<T, OP, SCOPE>(t, dst, src, hi, slot);
+    algo = RED_AUTO;
+  }
+  if (algo == RED_LL128) {
+    if (ll128_ok) return allreduce_ll128<T, OP, SCOPE>(t, dst, src, hi, slot);
     algo = RED_AUTO;
   }
   if (algo == RED_AUTO) {
@@ -514,14 +733,19 @@ __device__ __forceinline__ int fcollect_bytes(const bshmemi_team_t* t, void* dst
   const bool ll_ok = lo == 0 && hi == block_bytes && (bytes & 3) == 0 && ((uintptr_t)src & 3) == 0 && ((uintptr_t)dst & 3) == 0 &&
                      2 * bytes * size <= t->ll_bytes / 2;
   const bool nvls_ok = t->has_nvls && aligned16;
+  const bool ll128_ok = lo == 0 && hi == block_bytes && slot == 0 && bytes > 0 && (bytes & 7) == 0 && (((uintptr_t)src | (uintptr_t)dst) & 7) == 0 && ll128_scope_ok<SCOPE>() &&
+                        ll128_packets(bytes) <= ll128_layout(t).max_packets;
+  if (algo == FC_LL128 && !ll128_ok) algo = FC_AUTO;
   if (algo == FC_AUTO) {
     if (ll_ok && bytes <= bshmemi_state_d.fcollect_ll_threshold) algo = FC_LL;
+    else if (ll128_ok && bytes <= bshmemi_state_d.ll128_threshold) algo = FC_LL128;
     else if (nvls_ok && bytes * size <= bshmemi_state_d.fcollect_nvls_threshold) algo = FC_NVLS;
     else algo = FC_PUSH;
   }
   if (algo == FC_LL && !ll_ok) algo = FC_PUSH;
   if (algo == FC_NVLS && !nvls_ok) algo = FC_PUSH;
   if (algo == FC_LL) return fcollect_ll<SCOPE>(t, dst, src, bytes, slot);
+  if (algo == FC_LL128) return fcollect_ll128<SCOPE>(t, dst, src, bytes, slot);
   char* my_slot = (char*)dst + (size_t)me * block_bytes + lo;
   if (algo == FC_NVLS) {
     char* mc = (char*)t->mc_base + ((uint64_t)my_slot - bshmemi_state_d.heap_base);
@@ -568,6 +792,10 @@ __device__ __forceinline__ int broadcast_bytes(const bshmemi_team_t* t, void* ds
   const size_t bytes = hi - lo;
   if (algo == BC_AUTO) algo = bshmemi_state_d.bcast_algo;
   const bool nvls_ok = t->has_nvls && ((((uintptr_t)dst + lo) | ((uintptr_t)src + lo) | bytes) & 15) == 0;
+  // Flag-in-data (128-byte packets): whole messages of one group only, no barrier at all.
+  const bool ll128_ok = lo == 0 && slot == 0 && size > 1 && bytes > 0 && (bytes & 7) == 0 && (((uintptr_t)src | (uintptr_t)dst) & 7) == 0 && ll128_scope_ok<SCOPE>() &&
+                        ll128_packets(bytes) <= ll128_layout(t).max_packets;
+  if (ll128_ok && (algo == BC_LL || (algo == BC_AUTO && bytes <= bshmemi_state_d.ll128_threshold))) return broadcast_ll128<SCOPE>(t, dst, src, bytes, root);
   if (algo == BC_AUTO || algo == BC_LL) algo = nvls_ok ? BC_NVLS : BC_PUSH;
   if (algo == BC_NVLS && !nvls_ok) algo = BC_PUSH;
   if (algo == BC_PULL) {

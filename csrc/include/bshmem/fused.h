@@ -12,8 +12,11 @@ extern "C" {
 
 #define BSHMEM_FUSED_MAX_PES 8
 
-enum { BSHMEM_FUSED_PLAIN = 0, BSHMEM_FUSED_RS = 1, BSHMEM_FUSED_AR = 2, BSHMEM_FUSED_AG = 3 };
-enum { BSHMEM_FUSED_ACT_NONE = 0, BSHMEM_FUSED_ACT_GELU_TANH = 1 };
+enum { BSHMEM_FUSED_PLAIN = 0, BSHMEM_FUSED_RS = 1, BSHMEM_FUSED_AR = 2, BSHMEM_FUSED_AG = 3, BSHMEM_FUSED_GROUPED = 4 };
+#define BSHMEM_FUSED_MAX_GROUPS 256
+/* SWIGLU (GROUPED only): every 64 output columns are 32 gate columns followed by their 32 up columns (the caller orders
+ * the rows of B that way); the kernel writes silu(gate) * up, so `out` has N / 2 columns. */
+enum { BSHMEM_FUSED_ACT_NONE = 0, BSHMEM_FUSED_ACT_GELU_TANH = 1, BSHMEM_FUSED_ACT_SWIGLU = 2 };
 enum {
   BSHMEM_FUSED_OK = 0,
   BSHMEM_FUSED_ERR_ARGS = 1,
@@ -27,6 +30,10 @@ typedef struct {
    * PLAIN: A, B, out local.
    * RS   : every PE holds a K-slice; out is this PE's [M/npes, N] block of the sum over PEs.
    * AR   : as RS, but out is the full [M, N] sum on every PE (out_peer[] = each PE's out).
+   * GROUPED: one PE; the rows of A fall into `groups` consecutive groups with boundaries group_offsets[0..groups] (a
+   *        device array, read by the kernel: no host synchronisation), B holds one [N, K] matrix per group back to
+   *        back, and rows r of group g give out[r, :] = A[r, :] * B_g^T.  M is the number of rows A and out are
+   *        allocated for (any positive number); rows at or beyond group_offsets[groups] are not written.
    * AG   : A is this PE's gathered [M, K] buffer (symmetric); rows [rank*M/npes, …) hold this PE's shard on
    *        entry and the kernel fills the peers' copies (ag_peer[] = each PE's gathered buffer). */
   const void* A;
@@ -65,6 +72,9 @@ typedef struct {
    * ag_flags[rank * (M/npes/128)] on each peer to `epoch` once its shard is complete there; the kernel then sends
    * nothing and waits for one flag per shard.  0 = two warps of every CTA send the shard. */
   int ag_external;
+  /* GROUPED */
+  const int* group_offsets;  /* device int32 [groups + 1], non-decreasing, group_offsets[groups] <= M */
+  int groups;                /* 1 .. BSHMEM_FUSED_MAX_GROUPS */
 } bshmem_fused_args_t;
 
 /* Launches the kernel on `stream`.  Returns a BSHMEM_FUSED_* code. */

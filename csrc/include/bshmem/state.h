@@ -67,8 +67,10 @@ typedef struct {
   uint64_t scratch_bytes;
   uint64_t epochs;      /* local device memory: uint64 [BSHMEM_SYNC_SLOTS] barrier epochs + [BSHMEM_SYNC_SLOTS] collective epochs */
   uint64_t pe_of;       /* local device memory: int32 [size] world PE of each member (non-strided teams), else 0 */
-  uint64_t ll_base;     /* symmetric flag-in-data buffer for small fcollect/broadcast */
+  uint64_t ll_base;     /* symmetric flag-in-data buffer (8-byte packets) for small fcollect / allreduce */
   uint64_t ll_bytes;
+  uint64_t ll128_base;  /* symmetric area of 128-byte packets: exchange halves, broadcast halves, acknowledgements */
+  uint64_t ll128_bytes;
 } bshmemi_team_t;
 
 typedef struct {
@@ -94,6 +96,7 @@ typedef struct {
   uint64_t fcollect_ll_threshold, fcollect_nvls_threshold, reducescatter_nvls_threshold;
   int32_t sync_gpu_release;   /* 1: team sync releases with a GPU-scope fence (NVSHMEM_SYNC_GPU_SCOPE_RELEASE) */
   int32_t reserved0;
+  uint64_t ll128_threshold;   /* bytes per PE up to which fcollect / allreduce / broadcast use 128-byte flag-in-data packets */
 } bshmemi_state_t;
 
 #define BSHMEM_JOB_GPU_LDST_ATOMICS 0 /* every peer reachable by ld/st/atomics (NVSwitch) */

@@ -72,11 +72,12 @@ int timeout_ms() { return (int)options().BOOTSTRAP_TIMEOUT_MS; }
 struct RootArgs {
   int listen_fd;
   uint64_t magic;
+  int timeout_ms;  // read by the creating thread: the root thread never touches the option table (it may be reloaded meanwhile)
 };
 
 void root_main(RootArgs args) {
   pthread_setname_np(pthread_self(), "bshmem-uidroot");
-  const int tmo = timeout_ms();
+  const int tmo = args.timeout_ms;
   std::vector<int> fds;
   std::vector<SockAddr> table;
   std::vector<bool> seen;
@@ -135,7 +136,7 @@ void root_main(RootArgs args) {
 int start_root(SockAddr* addr, uint64_t magic) {
   int fd = -1;
   if (sock_listen(addr, &fd) != SOCK_OK) return BOOT_ERR_SOCKET;
-  std::thread(root_main, RootArgs{fd, magic}).detach();
+  std::thread(root_main, RootArgs{fd, magic, timeout_ms()}).detach();
   return BOOT_OK;
 }
 

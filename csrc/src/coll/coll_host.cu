@@ -316,7 +316,7 @@ int coll_barrier_on_stream(int team, cudaStream_t stream, bool with_quiet) {
 // ------------------------------------------------------------------ host-side barrier entry points
 static int device_errors_to_status() {
   Runtime& r = rt();
-  if (r.status_host && (r.status_host->error_bits & BSHMEM_ERR_WAIT_TIMEOUT)) return ST_INTERNAL;
+  if (r.status_host && (status_load(&r.status_host->error_bits) & BSHMEM_ERR_WAIT_TIMEOUT)) return ST_INTERNAL;
   return ST_SUCCESS;
 }
 

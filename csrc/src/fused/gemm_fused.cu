@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   uint64_t* acc_empty = acc_full + 2;       // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* g_prefix = (int*)(smem + SMEM_TILES + 256);  // GROUPED: [groups + 1] tiles before each group
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0;
@@ -95,6 +96,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
     tmem_alloc<PAIR ? 2 : 1>(tmem_slot, TMEM_COLS);
     tmem_relinquish<PAIR ? 2 : 1>();
   }
+  const bool grouped = p.mode == BSHMEM_FUSED_GROUPED;
+  if (grouped && warp == 3 && lane == 0) {
+    // Tiles per group from the group boundaries in device memory: no host round trip decides the work list.
+    int acc = 0;
+    for (int g = 0; g < p.groups; ++g) {
+      g_prefix[g] = acc;
+      const int rows = p.group_offsets[g + 1] - p.group_offsets[g];
+      acc += ((rows > 0 ? rows : 0) + BM - 1) / BM * (p.group_n / BN);
+    }
+    g_prefix[p.groups] = acc;
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
@@ -102,7 +114,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_n = p.N / BN;
-  const int total_tiles = (p.M / BM) * tiles_n;
+  const int total_tiles = grouped ? g_prefix[p.groups] : (p.M / BM) * tiles_n;
   const int kblocks = p.K / BK;
   // Pair: worker u = pair index takes tiles 2u + r, 2(u + workers) + r, …
   const int first = PAIR ? ((int)blockIdx.x & ~1) + (int)cta_rank : (int)blockIdx.x;
@@ -118,7 +130,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       for (int t = first; t < total_tiles && !*abort_flag; t += step) {
-        const TileInfo ti = tile_info(p, t);
+        const TileInfo ti = grouped ? grouped_tile_info(p, g_prefix, t) : tile_info(p, t);
         if (p.mode == BSHMEM_FUSED_AG && ti.peer != p.rank) {
           // The 128 rows of this tile arrive from `peer`; all of K comes with them.
           // In-kernel sender: a counter per 128-row block.  External sender: one flag per shard, set to the call number.
@@ -132,12 +144,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
           if (PAIR) {
             const uint32_t lead = mapa_u32(smem_u32(&full[stage]), 0);
             mbar_expect_tx_cluster(lead, A_STAGE + B_STAGE);
-            tma_load_2d_pair(sA + stage * A_STAGE, &p.tmA, lead, kb * BK, ti.m_tile * BM);
-            tma_load_2d_pair(sB + stage * B_STAGE, &p.tmB, lead, kb * BK, ti.n_tile * BN + (int)cta_rank * B_ROWS);
+            tma_load_2d_pair(sA + stage * A_STAGE, &p.tmA, lead, kb * BK, ti.a_row);
+            tma_load_2d_pair(sB + stage * B_STAGE, &p.tmB, lead, kb * BK, ti.b_row + (int)cta_rank * B_ROWS);
           } else {
             mbar_expect_tx(&full[stage], A_STAGE + B_STAGE);
-            tma_load_2d(sA + stage * A_STAGE, &p.tmA, &full[stage], kb * BK, ti.m_tile * BM);
-            tma_load_2d(sB + stage * B_STAGE, &p.tmB, &full[stage], kb * BK, ti.n_tile * BN);
+            tma_load_2d(sA + stage * A_STAGE, &p.tmA, &full[stage], kb * BK, ti.a_row);
+            tma_load_2d(sB + stage * B_STAGE, &p.tmB, &full[stage], kb * BK, ti.b_row);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -197,7 +209,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
     uint32_t acc_phase = 0, chunk_counter = 0;
     uint64_t* pending_flag = nullptr;  // flag of the previous remote tile, published once its stores have completed
     for (int t = first; t < total_tiles; t += step) {
-      const TileInfo ti = tile_info(p, t);
+      const TileInfo ti = grouped ? grouped_tile_info(p, g_prefix, t) : tile_info(p, t);
       const bool own = !reduce_mode || (!sw && ti.peer == p.rank);
       uint32_t ok = mbar_wait(&acc_full[acc], acc_phase, p.wait_limit_ns, abort_flag) ? 1u : 0u;
       if (issuer && pending_flag) {
@@ -269,6 +281,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_fused_kernel(const __grid_co
             add8(v0);
             if (two) add8(v1);
           }
+        }
+        if (grouped) {
+          // Ragged tiles: every thread writes its own row straight from registers (128 contiguous bytes per chunk),
+          // rows past the end of the group are dropped.  No shared-memory staging, no bulk store.
+          if (p.act == BSHMEM_FUSED_ACT_SWIGLU) {
+            // Gated activation: the 64 columns of a chunk are 32 gate columns followed by their 32 up columns (the
+            // caller interleaves the weight rows that way); the output has half as many columns.
+#pragma unroll
+            for (int j = 0; j < EPI_COLS / 2; ++j) f[j] = f[j] / (1.0f + __expf(-f[j])) * f[EPI_COLS / 2 + j];
+          }
+          const int out_cols = p.act == BSHMEM_FUSED_ACT_SWIGLU ? EPI_COLS / 2 : EPI_COLS;
+          const size_t pitch = p.act == BSHMEM_FUSED_ACT_SWIGLU ? (size_t)p.group_n / 2 : (size_t)p.group_n;
+          if (row < ti.valid_rows) {
+            uint4* o = (uint4*)(p.out_local + ((size_t)(ti.a_row + row) * pitch + ((size_t)ti.n_tile * (BN / EPI_COLS) + (size_t)c) * out_cols) * 2);
+#pragma unroll
+            for (int j = 0; j < EPI_COLS / 8; ++j) {
+              if (j * 8 >= out_cols) break;
+              uint4 v;
+              __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[j * 8 + 2 * e], f[j * 8 + 2 * e + 1]);
+              o[j] = v;
+            }
+          }
+          continue;
         }
         // Staging buffer (chunk_counter & 1) must have been drained by the TMA store issued two chunks ago.
         uint8_t* buf = sE + (chunk_counter & 1) * EPI_BUF;
@@ -372,12 +409,14 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   if (!a || !a->A || !a->B || !a->out || !a->error_flag) return BSHMEM_FUSED_ERR_ARGS;
   const int npes = a->npes, mode = a->mode;
   if (npes < 1 || npes > BSHMEM_FUSED_MAX_PES || a->rank < 0 || a->rank >= npes) return BSHMEM_FUSED_ERR_ARGS;
-  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->M % (BM * npes) || a->N % BN || a->K % BK) return BSHMEM_FUSED_ERR_SHAPE;
+  const bool grouped = mode == BSHMEM_FUSED_GROUPED;
+  if (grouped && (npes != 1 || !a->group_offsets || a->groups < 1 || a->groups > MAX_GROUPS)) return BSHMEM_FUSED_ERR_ARGS;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || (!grouped && a->M % (BM * npes)) || a->N % BN || a->K % BK) return BSHMEM_FUSED_ERR_SHAPE;
   FusedParams p;
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K; p.rank = a->rank; p.npes = npes; p.mode = mode;
   p.epoch = a->epoch;
-  if (a->act != BSHMEM_FUSED_ACT_NONE && a->act != BSHMEM_FUSED_ACT_GELU_TANH) return BSHMEM_FUSED_ERR_ARGS;
+  if (a->act != BSHMEM_FUSED_ACT_NONE && a->act != BSHMEM_FUSED_ACT_GELU_TANH && !(a->act == BSHMEM_FUSED_ACT_SWIGLU && mode == BSHMEM_FUSED_GROUPED)) return BSHMEM_FUSED_ERR_ARGS;
   if (a->act != BSHMEM_FUSED_ACT_NONE && (mode == BSHMEM_FUSED_RS || mode == BSHMEM_FUSED_AR) && npes > 1) return BSHMEM_FUSED_ERR_ARGS;  // partial sums
   p.act = a->act;
   p.wait_limit_ns = a->wait_limit_ms ? (uint64_t)a->wait_limit_ms * 1000000ull : 10000000000ull;
@@ -389,7 +428,7 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   int grid = a->max_ctas > 0 && a->max_ctas < sms ? a->max_ctas : sms;
   // A pair takes two consecutive 128-row tiles of one PE's block of rows.
-  bool pair = pair_wanted() && rows_per_pe % (2 * BM) == 0 && grid >= 2;
+  bool pair = pair_wanted() && rows_per_pe % (2 * BM) == 0 && grid >= 2 && !grouped;  // ragged groups do not pair up
   if (pair) grid &= ~1;
   int st = make_map(&p.tmA, a->A, a->M, a->K, BM);
   if (st) return st;
@@ -448,7 +487,14 @@ extern "C" int bshmem_fused_gemm(const bshmem_fused_args_t* a, cudaStream_t stre
     }
     p.ag_external = a->ag_external != 0;
   }
-  st = make_map(&p.tmB, a->B, a->N, a->K, pair ? BN / 2 : BN);
+  if (grouped) {
+    if ((uintptr_t)a->out & 15) return BSHMEM_FUSED_ERR_ALIGNMENT;
+    p.group_offsets = a->group_offsets;
+    p.groups = a->groups;
+    p.group_n = a->N;
+    p.out_local = (char*)a->out;
+  }
+  st = make_map(&p.tmB, a->B, grouped ? (uint64_t)a->groups * a->N : (uint64_t)a->N, a->K, pair ? BN / 2 : BN);
   if (st) return st;
   if (g_attr_set_for_device != device) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);

@@ -25,7 +25,8 @@ constexpr int TMEM_COLS = 512, ACC_COLS = BN;
 constexpr int NTHREADS = 256, EPI_THREADS = 128, EPI_WARP0 = 4;
 constexpr int AUX_WARP0 = 2, AUX_THREADS = 64;   // warps 2 and 3: switch-side reduction (RS / AR) or shard sender (AG)
 constexpr int SMEM_TILES = 4 * (A_STAGE + BN * BK * 2) + EPI_BUFS * EPI_BUF;  // 4 stages of a 128 x 256 tile = 6 stages of a pair's halves
-constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int MAX_GROUPS = 256;                   // grouped mode: experts (row groups) per call
+constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/ + (MAX_GROUPS + 4) * 4 /*grouped mode: tile prefix sums*/;
 
 struct alignas(64) FusedParams {
   CUtensorMap tmA, tmB;
@@ -47,11 +48,15 @@ struct alignas(64) FusedParams {
   int M, N, K, rank, npes, mode;
   int ag_external;                           // AG: the shards are pushed by the caller (copy engines); flag [peer][0] = epoch when a shard is complete
   int act;                                   // BSHMEM_FUSED_ACT_*: applied to the fp32 result in the epilogue (PLAIN / AG)
+  const int* group_offsets;                  // GROUPED: device array [groups + 1], rows of group g are [offsets[g], offsets[g + 1])
+  int groups, group_n;                       // GROUPED: number of groups; rows of B (output columns) per group
   int red_rows;                              // switch path: rows per work item of the reducing warps (16 or 32)
   int sw_reduce;                             // RS/AR: partial tiles stay local and the owner fetches their sum through the switch
 };
 
 struct TileInfo {
+  int a_row, b_row;     // row coordinates of the tile's operands: first row of A, first row of B (the CTA pair adds its half)
+  int valid_rows;       // rows of the tile that exist (BM except in the last tile of a group, GROUPED mode)
   int m_tile, n_tile;   // position in the full output
   int peer;             // RS/AR: PE that owns the rows; AG: PE whose shard holds the rows
   int m_local;          // m-tile index inside that PE's block of rows
@@ -63,7 +68,40 @@ struct TileInfo {
 // Switch path of RS/AR: every PE walks the output in the same order (m fastest over all rows, then n), so that the
 // partials of a tile are produced at about the same time everywhere and its owner can reduce it right away; owners
 // alternate every M/npes rows, so the reduction traffic is spread evenly over the PEs and over the run.
+__host__ __device__ __forceinline__ TileInfo tile_info_base(const FusedParams& p, int t);
 __host__ __device__ __forceinline__ TileInfo tile_info(const FusedParams& p, int t) {
+  TileInfo ti = tile_info_base(p, t);
+  ti.a_row = ti.m_tile * BM;
+  ti.b_row = ti.n_tile * BN;
+  ti.valid_rows = BM;
+  return ti;
+}
+// GROUPED mode (C rows of group g = A rows of group g times B_g^T, group boundaries in device memory): `prefix[g]` is
+// the number of tiles of the groups before g (built once per CTA in shared memory).  Inside a group the 128-row
+// blocks run fastest, then the column blocks.  The last block of a group may be short: its operand tile still loads
+// 128 rows (whatever follows the group; rows past the end of A read as zero) and only `valid_rows` rows are stored.
+__device__ __forceinline__ TileInfo grouped_tile_info(const FusedParams& p, const int* prefix, int t) {
+  int lo = 0, hi = p.groups;  // find g with prefix[g] <= t < prefix[g + 1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= t) lo = mid;
+    else hi = mid;
+  }
+  const int g = lo, local = t - prefix[g];
+  const int r0 = p.group_offsets[g], r1 = p.group_offsets[g + 1];
+  const int mblocks = (r1 - r0 + BM - 1) / BM;
+  TileInfo ti;
+  ti.peer = g;
+  ti.m_local = local % mblocks;
+  ti.n_tile = local / mblocks;
+  ti.m_tile = 0;
+  ti.idx_in_peer = local;
+  ti.a_row = r0 + ti.m_local * BM;
+  ti.b_row = g * p.group_n + ti.n_tile * BN;
+  ti.valid_rows = r1 - ti.a_row < BM ? r1 - ti.a_row : BM;
+  return ti;
+}
+__host__ __device__ __forceinline__ TileInfo tile_info_base(const FusedParams& p, int t) {
   const int tiles_n = p.N / BN;
   const int tmr = (p.M / p.npes) / BM;
   const int per_peer = tmr * tiles_n;

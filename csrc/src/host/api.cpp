@@ -150,7 +150,7 @@ void wait_on_stream(const void* ivar, int cmp, uint64_t value, int width, bool i
         timespec t1;
         clock_gettime(CLOCK_MONOTONIC, &t1);
         if ((t1.tv_sec - t0.tv_sec) * 1000 + (t1.tv_nsec - t0.tv_nsec) / 1000000 > limit_ms) {
-          if (r.status_host) r.status_host->error_bits |= BSHMEM_ERR_WAIT_TIMEOUT;
+          if (r.status_host) status_or(&r.status_host->error_bits, BSHMEM_ERR_WAIT_TIMEOUT);
           ERROR_PRINT("wait on %p timed out after %ld ms", ivar, limit_ms);
           return;
         }
@@ -172,7 +172,7 @@ int coll_finish(int st, cudaStream_t s) {  // blocking flavour of a collective l
   Runtime& r = rt();
   if (!r.have_gpu) return ST_SUCCESS;  // the CPU versions of the collectives have already run
   if (cudaStreamSynchronize(s) != cudaSuccess) return ST_INTERNAL;
-  return r.status_host && (r.status_host->error_bits & BSHMEM_ERR_WAIT_TIMEOUT) ? ST_INTERNAL : ST_SUCCESS;
+  return r.status_host && (status_load(&r.status_host->error_bits) & BSHMEM_ERR_WAIT_TIMEOUT) ? ST_INTERNAL : ST_SUCCESS;
 }
 
 int do_init(unsigned int flags, nvshmemx_init_attr_t* attr, bool hostlib_only) {
@@ -855,20 +855,20 @@ void nvshmemx_b200_module_sync(void) {
 }
 uint32_t nvshmemx_b200_error_bits(void) {
   Runtime& r = rt();
-  return r.status_host ? r.status_host->error_bits : 0;
+  return r.status_host ? status_load(&r.status_host->error_bits) : 0;
 }
 void nvshmemx_b200_clear_errors(void) {
   Runtime& r = rt();
   if (!r.status_host) return;
-  r.status_host->error_bits = 0;
-  r.status_host->timeout_count = 0;
+  status_store(&r.status_host->error_bits, 0);
+  status_store(&r.status_host->timeout_count, 0);
   r.reported_errors.store(0);
 }
 uint32_t nvshmemx_b200_timeout_info(bshmemi_status_t* out) {
   Runtime& r = rt();
   if (!r.status_host) return 0;
   if (out) memcpy(out, (const void*)r.status_host, sizeof(*out));
-  return r.status_host->timeout_count;
+  return status_load(&r.status_host->timeout_count);
 }
 void nvshmemx_b200_set_wait_timeout_ms(long ms) {
   Runtime& r = rt();

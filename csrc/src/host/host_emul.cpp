@@ -43,7 +43,7 @@ int emul_team_sync(int team) {
     while (__atomic_load_n(flags + i, __ATOMIC_ACQUIRE) < epoch) {
       if (now_ms() > deadline) {
         ERROR_PRINT("PE %d: team %d sync timed out waiting for member %d", r.mype, team, i);
-        r.status_host->error_bits |= BSHMEM_ERR_WAIT_TIMEOUT;
+        status_or(&r.status_host->error_bits, BSHMEM_ERR_WAIT_TIMEOUT);
         return ST_INTERNAL;
       }
       std::this_thread::yield();

@@ -135,7 +135,7 @@ static void watchdog_main(Runtime* r) {
   while (!r->watchdog_stop.load()) {
     bshmemi_status_t* s = r->status_host;
     if (s) {
-      uint32_t bits = s->error_bits;
+      uint32_t bits = status_load(&s->error_bits);
       uint32_t fresh = bits & ~r->reported_errors.load();
       if (fresh) {
         r->reported_errors.fetch_or(fresh);
@@ -150,7 +150,7 @@ static void watchdog_main(Runtime* r) {
           _exit(-1);
         }
       }
-      if (s->global_exit_req) {
+      if (status_load(&s->global_exit_req)) {
         int code = s->global_exit_code;
         INFO(SUB_INIT, "PE %d: device code called nvshmem_global_exit(%d)", r->mype, code);
         if (r->boot_live && r->boot.global_exit) r->boot.global_exit(code, &r->boot);
@@ -220,7 +220,15 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   bool gpu = cu() != nullptr && cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0;
   std::string be = o.HEAP_BACKEND;
   std::transform(be.begin(), be.end(), be.begin(), ::toupper);
-  bool use_vmm = be == "VMM" || (be == "AUTO" && gpu && !o.DISABLE_CUDA_VMM);
+  if (o.DISABLE_CUDA_VMM && gpu && be != "HOST") {
+    // The reference's alternative to VMM is one cudaMalloc per PE shared through CUDA IPC.  IPC mappings land at
+    // addresses the driver picks, while this library's address translation relies on all PEs' heaps sitting at fixed
+    // offsets of one reservation, so that heap is not built; a job that asks for it gets an error, not host memory.
+    ERROR_PRINT("NVSHMEM_DISABLE_CUDA_VMM is set, but the GPU heap of this library needs CUDA virtual memory management (every sm_100 GPU has it); "
+                "unset the variable, or set NVSHMEM_HEAP_BACKEND=HOST for a heap in host memory");
+    return ST_NOT_SUPPORTED;
+  }
+  bool use_vmm = be == "VMM" || (be == "AUTO" && gpu);
   if (use_vmm && !gpu) {
     ERROR_PRINT("NVSHMEM_HEAP_BACKEND=VMM needs a CUDA device");
     return ST_GPU_NOT_SELECTED;
@@ -327,6 +335,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   d.reduce_nvls_threshold = o.REDUCE_NVLS_THRESHOLD;
   d.reduce_oneshot_threshold = o.REDUCE_ONESHOT_THRESHOLD;
   d.fcollect_ll_threshold = o.FCOLLECT_LL_THRESHOLD;
+  d.ll128_threshold = o.LL128_THRESHOLD;
   d.fcollect_nvls_threshold = o.FCOLLECT_NVLS_THRESHOLD;
   d.reducescatter_nvls_threshold = o.REDUCESCATTER_NVLS_THRESHOLD;
 

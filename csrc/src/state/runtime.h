@@ -92,7 +92,7 @@ struct Runtime {
   std::vector<bshmemi_team_t> team_pool_host;
   uint64_t* epochs_dev = nullptr;            // [max_teams][2*BSHMEM_SYNC_SLOTS]
   char* team_area = nullptr;                 // symmetric: per-team sync + LL + scratch
-  size_t team_area_bytes = 0, sync_bytes = 0, ll_bytes = 0, scratch_bytes = 0;
+  size_t team_area_bytes = 0, sync_bytes = 0, ll_bytes = 0, scratch_bytes = 0, ll128_bytes = 0;
   std::vector<std::unique_ptr<Team>> teams;  // index = team handle
   std::vector<uint64_t> team_bitmap;         // 1 = free
   int max_teams = 128;
@@ -116,6 +116,12 @@ struct Runtime {
 
 Runtime& rt();
 
+// The status block is written by device code (or, with the host-memory heap, by host code standing in for it) and
+// by API calls, and polled by the watchdog thread: host code touches its words through these relaxed atomics.
+inline uint32_t status_load(const volatile uint32_t* p) { return __atomic_load_n((const uint32_t*)p, __ATOMIC_RELAXED); }
+inline void status_store(volatile uint32_t* p, uint32_t v) { __atomic_store_n((uint32_t*)p, v, __ATOMIC_RELAXED); }
+inline void status_or(volatile uint32_t* p, uint32_t v) { __atomic_fetch_or((uint32_t*)p, v, __ATOMIC_RELAXED); }
+
 // ---- init / finalize (init.cpp)
 int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_hint, bool hostlib_only, int boot_mode);
 int runtime_finalize();
@@ -137,7 +143,7 @@ int team_split_strided(int parent, int start, int stride, int size, uint64_t uni
 int team_split_2d(int parent, int xrange, int* xteam, int* yteam);
 int team_create_from_members(int parent, const std::vector<int>& world_members, uint64_t uniqueid, int* new_team);
 int team_destroy(int handle);
-void team_sync_ptrs(const Runtime& r, int idx, uint64_t* sync, uint64_t* ll, uint64_t* scratch);
+void team_sync_ptrs(const Runtime& r, int idx, uint64_t* sync, uint64_t* ll, uint64_t* scratch, uint64_t* ll128 = nullptr);
 
 // ---- barriers used by the host paths (coll_host.cu / host_emul.cpp)
 int host_barrier_team(int team, cudaStream_t stream, bool blocking);  // quiet + device barrier kernel (GPU) or CPU flags (host mode)

@@ -50,12 +50,13 @@ Team* team_get(int handle) {
   return r.teams[handle].get();
 }
 
-void team_sync_ptrs(const Runtime& r, int idx, uint64_t* sync, uint64_t* ll, uint64_t* scratch) {
-  size_t per = r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes;
+void team_sync_ptrs(const Runtime& r, int idx, uint64_t* sync, uint64_t* ll, uint64_t* scratch, uint64_t* ll128) {
+  size_t per = r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes + r.ll128_bytes;
   char* base = r.team_area + (size_t)idx * per;
   *sync = (uint64_t)base;
   *ll = (uint64_t)(base + r.sync_bytes);
   *scratch = (uint64_t)(base + r.sync_bytes + r.ll_bytes);
+  if (ll128) *ll128 = (uint64_t)(base + r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes);
 }
 
 static bool bitmap_test(const std::vector<uint64_t>& b, int i) { return (b[i / 64] >> (i % 64)) & 1; }
@@ -74,9 +75,10 @@ static int publish_team(Runtime& r, Team* t) {
   d.team_idx = t->idx;
   d.has_nvls = t->nvls;
   d.mc_base = t->nvls ? (uint64_t)t->mc_base : 0;
-  team_sync_ptrs(r, t->idx, &d.sync_base, &d.ll_base, &d.scratch_base);
+  team_sync_ptrs(r, t->idx, &d.sync_base, &d.ll_base, &d.scratch_base, &d.ll128_base);
   d.scratch_bytes = r.scratch_bytes;
   d.ll_bytes = r.ll_bytes;
+  d.ll128_bytes = r.ll128_bytes;
   d.epochs = (uint64_t)(r.epochs_dev + (size_t)t->idx * 2 * BSHMEM_SYNC_SLOTS);
   d.pe_of = 0;
   if (!t->strided) {
@@ -175,7 +177,11 @@ int teams_init(Runtime& r) {
   // Flag-in-data packets double the payload; two generations avoid a reset barrier.
   r.ll_bytes = round_up(2 * 2 * std::max<size_t>(o.FCOLLECT_LL_THRESHOLD, 2048) * r.npes, 512);
   r.scratch_bytes = round_up(std::max<size_t>(o.REDUCE_SCRATCH_SIZE, 4096), 512);
-  size_t per = r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes;
+  // 128-byte packets: two generations of [npes][P] lines for fcollect / allreduce, two of [P] lines for broadcast and
+  // npes acknowledgement words, P = packets of the largest message (120 payload bytes per line).
+  const size_t p128 = (o.LL128_THRESHOLD + 119) / 120;
+  r.ll128_bytes = p128 ? round_up(2 * 128 * p128 * ((size_t)r.npes + 1) + 8 * (size_t)r.npes, 512) : 0;
+  size_t per = r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes + r.ll128_bytes;
   const int words = (r.max_teams + 63) / 64;
   r.team_area_bytes = per * r.max_teams;
   int hst = 0;
@@ -231,7 +237,7 @@ int teams_init(Runtime& r) {
     t = install_team(r, TEAM_SHARED + i, (*sets[i])[0], 1, (int)sets[i]->size(), sets[i], TEAM_WORLD);
     if (publish_team(r, t)) return ST_INTERNAL;
   }
-  INFO(SUB_TEAM, "team area: %d slots x %zu bytes (sync %zu, LL %zu, scratch 2x%zu)", r.max_teams, per, r.sync_bytes, r.ll_bytes, r.scratch_bytes);
+  INFO(SUB_TEAM, "team area: %d slots x %zu bytes (sync %zu, LL %zu, scratch 2x%zu, LL128 %zu)", r.max_teams, per, r.sync_bytes, r.ll_bytes, r.scratch_bytes, r.ll128_bytes);
   return ST_SUCCESS;
 }
 
@@ -401,9 +407,10 @@ int team_destroy(int handle) {
   int st = host_barrier_team(handle, r.stream, true);
   if (st != ST_SUCCESS) return st;
   for (int c : t->children) team_destroy(c);
-  uint64_t sync, ll, scratch;
-  team_sync_ptrs(r, handle, &sync, &ll, &scratch);
+  uint64_t sync, ll, scratch, ll128;
+  team_sync_ptrs(r, handle, &sync, &ll, &scratch, &ll128);
   local_zero((void*)sync, r.sync_bytes + r.ll_bytes);
+  if (r.ll128_bytes) local_zero((void*)ll128, r.ll128_bytes);
   local_zero(r.epochs_dev + (size_t)handle * 2 * BSHMEM_SYNC_SLOTS, sizeof(uint64_t) * 2 * BSHMEM_SYNC_SLOTS);
   bshmemi_team_t blank{};
   blank.my_pe = -1;

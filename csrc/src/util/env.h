@@ -37,7 +37,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(BOOTSTRAP_TIMEOUT_MS,  long,        Long, 60000,            Bootstrap,   "Milliseconds a bootstrap socket operation may block before it fails") \
   X(DISABLE_NVLS,          bool,        Bool, false,            OpenShmem,   "Do not create NVLink multicast objects even where supported") \
   X(NVLS_TEAM_WINDOWS,     long,        Long, 16,               OpenShmem,   "NVLink multicast windows a PE may hold for teams that do not span the world (0: such teams never get one)") \
-  X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Use the host-memory heap back end instead of CUDA virtual memory management") \
+  X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Refused on a GPU: the GPU heap needs CUDA virtual memory management (the cudaMalloc + IPC heap of the reference is not built); see NVSHMEM_HEAP_BACKEND") \
   X(DISABLE_P2P,           bool,        Bool, false,            Hidden,      "Treat peers as not load/store reachable (init then fails: no remote transport is built)") \
   X(DISABLE_CE_COLLECTIVES,bool,        Bool, false,            Collectives, "Never use copy engines for on-stream alltoall/fcollect/broadcast") \
   X(CE_COLLECTIVES_MIN_BYTES, size_t,   Size, 0,                Collectives, "On-stream alltoall/fcollect/broadcast of at least this many bytes go through copy engines (0: never)") \
@@ -56,6 +56,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(REDUCE_SCRATCH_SIZE,   size_t,      Size, (size_t)512 << 10, Collectives, "Bytes of per-team scratch for push-based reductions")      \
   X(REDUCE_NTHREADS,       long,        Long, 512,              Collectives, "Threads per CTA for on-stream reductions")                 \
   X(FCOLLECT_ALGO,         long,        Long, 0,                Collectives, "Force an fcollect algorithm: 0 auto, 1 one-shot push, 2 LL, 3 NVLS push") \
+  X(LL128_THRESHOLD,       size_t,      Size, 32768,            Collectives, "Bytes per PE up to which fcollect, allreduce and broadcast use 128-byte flag-in-data packets (0: never)") \
   X(FCOLLECT_LL_THRESHOLD, size_t,      Size, 2048,             Collectives, "Bytes up to which fcollect uses the flag-in-data protocol")  \
   X(FCOLLECT_NVLS_THRESHOLD, size_t,    Size, (size_t)16 << 20, Collectives, "Bytes up to which fcollect uses multicast stores when available") \
   X(FCOLLECT_NTHREADS,     long,        Long, 512,              Collectives, "Threads per CTA for on-stream fcollect")                   \

@@ -12,7 +12,8 @@ import ctypes as C
 import os
 from pathlib import Path
 
-LIB_DIR = Path(__file__).resolve().parents[1] / "lib"
+# BSHMEM_LIB_DIR selects another build of the native libraries (for example a sanitizer build, see utils/build.py).
+LIB_DIR = Path(os.environ["BSHMEM_LIB_DIR"]) if os.environ.get("BSHMEM_LIB_DIR") else Path(__file__).resolve().parents[1] / "lib"
 _lib = None
 
 UNIQUEID_BYTES = 128

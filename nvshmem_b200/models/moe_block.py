@@ -3,7 +3,11 @@
 Each rank holds ``E / npes`` experts (a gated MLP each).  ``forward(x)``:
 router logits -> softmax -> top-k -> ``MoeDispatchCombine.dispatch`` (tokens travel to the ranks of
 their experts, grouped by expert) -> the local experts' MLPs over their row groups -> ``combine``
-(the weighted sum comes back to the token's rank).  Inference path: no autograd through the exchange.
+(the weighted sum comes back to the token's rank).  The experts run as two grouped GEMMs on the
+tcgen05 kernel (``ops.fused_gemm.grouped_gemm``): the group boundaries stay on the device, the gated
+activation is applied in the first GEMM's epilogue, and the second GEMM writes straight into the
+buffer that ``combine`` reads; nothing is synchronised with the host between dispatch and combine.
+Inference path: no autograd through the exchange.
 (the reference's counterpart is the data movement of examples/moe_shuffle.cu; the experts and the
 router are this framework's)
 """
@@ -11,6 +15,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import fused_gemm as fg
 from ..ops.moe import MoeDispatchCombine
 
 
@@ -31,9 +36,21 @@ class ExpertParallelMoE(torch.nn.Module):
         self.w_in = torch.nn.Parameter(w_in[mine].to(dev, torch.bfloat16).contiguous(), requires_grad=False)    # [EL, 2F, H]: gate and up projections
         self.w_out = torch.nn.Parameter(w_out[mine].to(dev, torch.bfloat16).contiguous(), requires_grad=False)  # [EL, H, F]
         self.exchange = MoeDispatchCombine(tokens, hidden, topk, experts, payload=payload, wait_limit_ms=wait_limit_ms)
+        # The grouped tcgen05 GEMM needs 256-column output tiles and 64-deep K steps; other shapes use torch matmuls.
+        self.grouped = (2 * ffn) % 256 == 0 and hidden % 256 == 0 and ffn % 64 == 0 and self.EL <= fg.MAX_GROUPS and not self.fp8_payload(payload)
+        if self.grouped:
+            self.w_in_gated = fg.interleave_gate_up(self.w_in.data)   # rows reordered for the fused gated activation
+            self.act_buf = torch.empty(self.exchange.cap_rows, ffn, dtype=torch.bfloat16, device=dev)
+
+    @staticmethod
+    def fp8_payload(payload: str) -> bool:
+        return payload == "fp8"
 
     def route(self, x: torch.Tensor):
-        logits = (x @ self.router.t()).float()
+        if self.T % 128 == 0 and self.E % 256 == 0 and self.H % 64 == 0:
+            logits = fg.gemm(x, self.router).float()   # the router is a GEMM like any other
+        else:
+            logits = (x @ self.router.t()).float()
         weight, idx = logits.softmax(-1).topk(self.K, dim=-1)
         weight = weight / weight.sum(-1, keepdim=True)
         return idx.to(torch.int32).contiguous(), weight.contiguous()
@@ -53,9 +70,14 @@ class ExpertParallelMoE(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         idx, weight = self.route(x)
         recv, offsets = self.exchange.dispatch(x, idx)
-        offs = offsets.tolist()  # group boundaries are needed on the host to slice the grouped GEMMs
-        rows = self.exchange.dequantized(offs[-1]).to(torch.bfloat16) if self.exchange.fp8 else recv
-        self.experts_forward(rows, offs)
+        if self.grouped:
+            # two grouped GEMMs over the expert segments; `offsets` never leaves the device
+            fg.grouped_gemm(recv, self.w_in_gated, offsets, out=self.act_buf, act="swiglu")
+            fg.grouped_gemm(self.act_buf, self.w_out, offsets, out=self.exchange.expert_out)
+        else:
+            offs = offsets.tolist()  # group boundaries on the host to slice per-expert matmuls
+            rows = self.exchange.dequantized(offs[-1]).to(torch.bfloat16) if self.exchange.fp8 else recv
+            self.experts_forward(rows, offs)
         return self.exchange.combine(idx, weight)
 
     def close(self) -> None:

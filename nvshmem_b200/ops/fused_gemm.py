@@ -16,14 +16,16 @@ buffers in the symmetric heap; a call counter (epoch) replaces flag resets.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
 from ..bindings import host as H
 
 MAX_PES = 8
-MODES = {"plain": 0, "rs": 1, "ar": 2, "ag": 3}
-ACTS = {None: 0, "none": 0, "gelu_tanh": 1}
+MODES = {"plain": 0, "rs": 1, "ar": 2, "ag": 3, "grouped": 4}
+ACTS = {None: 0, "none": 0, "gelu_tanh": 1, "swiglu": 2}
+MAX_GROUPS = 256
 _lib = None
 
 
@@ -36,7 +38,7 @@ class _Args(C.Structure):
                 ("mode", C.c_int), ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("n_comm", C.c_int), ("error_flag", C.c_void_p),
                 ("recv_local", C.c_void_p), ("recv_peer", C.c_void_p * MAX_PES), ("flags_local", C.c_void_p), ("flags_peer", C.c_void_p * MAX_PES),
                 ("out_peer", C.c_void_p * MAX_PES), ("ag_peer", C.c_void_p * MAX_PES), ("ag_flags_local", C.c_void_p), ("ag_flags_peer", C.c_void_p * MAX_PES), ("out_mc", C.c_void_p),
-                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p), ("act", C.c_int), ("ag_external", C.c_int)]
+                ("stage_local", C.c_void_p), ("stage_mc", C.c_void_p), ("act", C.c_int), ("ag_external", C.c_int), ("group_offsets", C.c_void_p), ("groups", C.c_int)]
 
 
 _ERRORS = {1: "bad arguments", 2: "shape: M must be a multiple of 128*npes, N of 256, K of 64", 3: "operands must be 16-byte aligned", 4: "CUDA driver/runtime error"}
@@ -115,6 +117,53 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, max_
     return out
 
 
+def grouped_gemm(x: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor | None = None, act: str | None = None) -> torch.Tensor:
+    """Grouped GEMM on the tcgen05 kernel: the rows of ``x[R, K]`` fall into ``G`` consecutive groups with boundaries
+    ``group_offsets`` (int32 ``[G + 1]`` ON THE DEVICE: the kernel reads them, nothing is synchronised with the
+    host), ``w`` is ``[G, N, K]``, and rows of group ``g`` are multiplied by ``w[g].T``.  Rows at or beyond
+    ``group_offsets[G]`` are not written.  This is the contraction of a mixture-of-experts layer after dispatch.
+
+    ``act="swiglu"``: each 64 rows of ``w[g]`` are 32 gate rows followed by their 32 up rows
+    (:func:`interleave_gate_up` builds that order); the result is ``silu(gate) * up`` with ``N / 2`` columns.
+    """
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 3 or x.shape[1] != w.shape[2]:
+        raise FusedGemmError(f"grouped_gemm: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+    if not x.is_contiguous() or not w.is_contiguous():
+        raise FusedGemmError("operands must be contiguous")
+    G, N, K = w.shape
+    if group_offsets.dtype != torch.int32 or group_offsets.numel() != G + 1 or not group_offsets.is_cuda or not group_offsets.is_contiguous():
+        raise FusedGemmError("group_offsets must be a contiguous int32 device tensor with one entry more than there are groups")
+    if G > MAX_GROUPS:
+        raise FusedGemmError(f"at most {MAX_GROUPS} groups per call")
+    R = x.shape[0]
+    out_cols = N // 2 if act == "swiglu" else N
+    if out is None:
+        out = torch.empty(R, out_cols, dtype=torch.bfloat16, device=x.device)
+    else:
+        _check_out(out, R, out_cols)
+    a = _Args()
+    a.act = ACTS[act]
+    a.A, a.B, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.M, a.N, a.K, a.rank, a.npes, a.mode = R, N, K, 0, 1, MODES["grouped"]
+    a.epoch = 1
+    a.group_offsets, a.groups = group_offsets.data_ptr(), G
+    a.error_flag = _error_flag(x.device).data_ptr()
+    _launch(a, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def interleave_gate_up(w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``[..., 2F, K]`` with the F gate rows first and the F up rows after them -> the row order that
+    ``grouped_gemm(..., act="swiglu")`` expects: blocks of 32 gate rows followed by the matching 32 up rows."""
+    *lead, two_f, K = w_gate_up.shape
+    F = two_f // 2
+    if two_f % 64:
+        raise FusedGemmError("the gate and up projections must each have a multiple of 32 rows")
+    gate = w_gate_up[..., :F, :].reshape(*lead, F // 32, 32, K)
+    up = w_gate_up[..., F:, :].reshape(*lead, F // 32, 32, K)
+    return torch.stack((gate, up), dim=-3).reshape(*lead, two_f, K).contiguous()
+
+
 class GemmReduceScatter:
     """Row-parallel GEMM fused with reduce-scatter (or all-reduce) over the world team.
 
@@ -122,10 +171,17 @@ class GemmReduceScatter:
     ``[M/npes, N]`` rows of the summed product (``mode="rs"``) or the whole ``[M, N]`` (``"ar"``).
     Without ``out=`` the output tensor is owned by the object and overwritten by the next call; with ``out=``
     (reduce-scatter only) the result is written there, e.g. straight into the shard of the next layer's
-    all-gather buffer.  ``use_multicast=False`` forces the push path even where the heap has a multicast window.
+    all-gather buffer.
+
+    ``use_multicast``: True = the switch path wherever the heap has a multicast window, False = the push path,
+    None (default) = by team size: the switch path from four PEs on, the push path below.  With two or three PEs an
+    owner adds only one or two partial tiles, which the push path's epilogue does faster than a trip through the
+    switch (measured at 2 PEs: 0.33 ms push, 0.36 ms switch per 8192 x 8192 x 3584 GEMM); from four PEs on the owner's
+    ingress and its epilogue work grow with the PE count on the push path and stay constant on the switch path.
+    ``BSHMEM_FUSED_REDUCE_PATH=switch|push`` overrides the automatic choice.
     """
 
-    def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0, use_multicast: bool = True):
+    def __init__(self, M: int, N: int, mode: str = "rs", wait_limit_ms: int = 0, use_multicast: bool | None = None):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
@@ -146,6 +202,9 @@ class GemmReduceScatter:
         else:
             self.out = torch.empty(self.rows if mode == "rs" else M, N, dtype=torch.bfloat16, device=dev)
         self._peer = {}
+        if use_multicast is None:
+            forced = os.environ.get("BSHMEM_FUSED_REDUCE_PATH", "").lower()
+            use_multicast = forced == "switch" or (forced != "push" and self.npes >= 4)
         if self.npes > 1:
             mc_ptr = H.load().nvshmemx_mc_ptr
             # Two generations of partial-tile storage by call parity: a fast peer may already be in call k+1.

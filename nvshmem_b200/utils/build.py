@@ -9,6 +9,12 @@ Targets (all land in ``nvshmem_b200/lib``):
 
 Objects are rebuilt when a source or any header is newer.  ``python -m
 nvshmem_b200.utils.build`` builds everything; ``--verbose`` adds ``-Xptxas -v``.
+
+``--sanitize=address|undefined|thread`` (or a comma list such as ``address,undefined``) builds an
+instrumented copy of the HOST library and the bootstrap plugin into ``nvshmem_b200/lib-<name>``
+(objects under ``build/obj-<name>``); the Python layer loads that copy when ``BSHMEM_LIB_DIR`` names
+the directory, and the interpreter needs the sanitizer runtime preloaded (``sanitizer_env`` returns
+the environment for a child process).  The CPU test-suite runs a part of itself that way.
 """
 from __future__ import annotations
 
@@ -44,9 +50,43 @@ def _headers_mtime() -> float:
     return newest
 
 
-def _compile(src: Path, extra: list[str], verbose: bool, hdr_mtime: float) -> Path:
+def sanitizer_dirs(sanitize: str) -> tuple[Path, Path]:
+    tag = sanitize.replace(",", "-")
+    return ROOT / "nvshmem_b200" / f"lib-{tag}", ROOT / "build" / f"obj-{tag}"
+
+
+def sanitizer_env(sanitize: str, log_dir: str | None = None) -> dict[str, str]:
+    """Environment for a Python child process that loads the instrumented host library.
+
+    ThreadSanitizer also watches the interpreter, torch and gloo, which are not instrumented, and reports their
+    internal locking as errors; those processes therefore exit normally (exitcode=0) and write their reports to
+    `log_dir`, where the caller looks for reports that name this library (`tsan_reports_about_us`)."""
+    import subprocess as sp
+    libs = []
+    for s in sanitize.split(","):
+        name = {"address": "libasan.so", "undefined": "libubsan.so", "thread": "libtsan.so"}[s]
+        libs.append(sp.run(["gcc", f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip())
+    env = {"LD_PRELOAD": ":".join(libs), "BSHMEM_LIB_DIR": str(sanitizer_dirs(sanitize)[0]),
+           "ASAN_OPTIONS": "detect_leaks=0:abort_on_error=1:protect_shadow_gap=0", "UBSAN_OPTIONS": "halt_on_error=1:print_stacktrace=1",
+           "TSAN_OPTIONS": f"halt_on_error=0:exitcode=0:report_signal_unsafe=0:suppressions={ROOT / 'tests' / 'data' / 'tsan.supp'}"
+                           + (f":log_path={log_dir}/tsan" if log_dir else "")}
+    return env
+
+
+def tsan_reports_about_us(log_dir: str) -> list[str]:
+    """The ThreadSanitizer reports under `log_dir` that have a frame of this repository's host library."""
+    found = []
+    for p in sorted(Path(log_dir).glob("tsan.*")):
+        text = p.read_text(errors="replace")
+        for report in text.split("=================="):
+            if "WARNING: ThreadSanitizer" in report and "libbshmem" in report:
+                found.append(report.strip())
+    return found
+
+
+def _compile(src: Path, extra: list[str], verbose: bool, hdr_mtime: float, obj_dir: Path | None = None) -> Path:
     rel = src.relative_to(CSRC) if CSRC in src.parents else src.relative_to(ROOT)
-    obj = OBJ / (str(rel).replace("/", "__") + ".o")
+    obj = (obj_dir or OBJ) / (str(rel).replace("/", "__") + ".o")
     obj.parent.mkdir(parents=True, exist_ok=True)
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
         return obj
@@ -85,6 +125,25 @@ def _sources(*dirs: str) -> list[Path]:
     for d in dirs:
         out += sorted((CSRC / "src" / d).glob("*.cpp")) + sorted((CSRC / "src" / d).glob("*.cu"))
     return out
+
+
+def build_sanitized(sanitize: str, jobs: int | None = None) -> dict[str, Path]:
+    """Builds the host library and the bootstrap plugin with -fsanitize=<sanitize> into their own directories."""
+    hdr = _headers_mtime()
+    jobs = jobs or min(8, os.cpu_count() or 4)
+    lib_dir, obj_dir = sanitizer_dirs(sanitize)
+    san = [f for s in sanitize.split(",") for f in ("-Xcompiler", f"-fsanitize={s}")]  # nvcc splits -Xcompiler values at commas
+    flags = san + ["-Xcompiler", "-fno-omit-frame-pointer", "-g"]
+    built = {}
+    for name, srcs, out, libs in (
+            ("host", _sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), lib_dir / "libbshmem_host.so",
+             ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
+            ("plugins", _sources("bootstrap_plugins"), lib_dir / "libbshmem_bootstrap_file.so", [])):
+        with ThreadPoolExecutor(jobs) as ex:
+            objs = list(ex.map(lambda s: _compile(s, flags, False, hdr, obj_dir), srcs))
+        _link(objs, out, True, libs + san)
+        built[name] = out
+    return built
 
 
 def build_all(verbose: bool = False, jobs: int | None = None, only: str | None = None) -> dict[str, Path]:
@@ -134,6 +193,10 @@ def main() -> None:
     for a in sys.argv[1:]:
         if a.startswith("--only="):
             only = a.split("=", 1)[1]
+        if a.startswith("--sanitize="):
+            for name, path in build_sanitized(a.split("=", 1)[1]).items():
+                print(f"{name} ({a[2:]}): {path}")
+            return
     for name, path in build_all(verbose=verbose, only=only).items():
         print(f"{name}: {path}")
 

@@ -112,6 +112,46 @@ class Env:
             dist.destroy_process_group()
 
 
+def parse_size(s) -> int:
+    """8, 4K, 32M, 1G (binary multiples), as the reference's perftests take them."""
+    s = str(s)
+    mult = {"k": 1 << 10, "m": 1 << 20, "g": 1 << 30}
+    return int(float(s[:-1]) * mult[s[-1].lower()]) if s[-1].lower() in mult else int(s)
+
+
+def add_reference_args(ap, min_size, max_size, iters, warmup, ctas=32, threads=1024, step=2):
+    """The argument set shared by the reference's perftests (perftest/common/utils.cu:889-1010), with this driver's
+    defaults: -b/-e/-f message sizes, -n/-w iterations, -c/-t launch geometry, -d datatype, -o reduce op, -s scope,
+    -a atomic op, --bidir, --cudagraph, --issue."""
+    ap.add_argument("-b", "--min_size", "--min-bytes", dest="min_size", default=min_size, help="smallest message (bytes; k/m/g suffixes)")
+    ap.add_argument("-e", "--max_size", "--max-bytes", dest="max_size", default=max_size, help="largest message")
+    ap.add_argument("-f", "--step", type=int, default=step, help="factor between consecutive message sizes")
+    ap.add_argument("-n", "--iters", type=int, default=iters, help="timed iterations per size")
+    ap.add_argument("-w", "--warmup_iters", type=int, default=warmup, help="untimed iterations before them")
+    ap.add_argument("-c", "--ctas", type=int, default=ctas)
+    ap.add_argument("-t", "--threads_per_cta", "--threads", dest="threads", type=int, default=threads)
+    ap.add_argument("-d", "--datatype", default=None, help="element type(s), comma separated (collectives: float, bfloat16, half, int ...)")
+    ap.add_argument("-o", "--reduce_op", default="sum")
+    ap.add_argument("-s", "--scope", default="all", help="thread, warp, block or all")
+    ap.add_argument("-a", "--atomic_op", default="all")
+    ap.add_argument("--bidir", action="store_true", help="both PEs of a pair send at the same time")
+    ap.add_argument("--cudagraph", action="store_true", help="replay the on-stream calls from a CUDA graph instead of issuing them eagerly")
+    ap.add_argument("--issue", default="on_stream", help="on_stream (default) or host: how host-initiated operations are issued")
+    return ap
+
+
+def sizes_geometric(lo: int, hi: int, step: int = 2):
+    s = max(1, lo)
+    while s <= hi:
+        yield s
+        s *= max(2, step)
+
+
+def scopes_of(arg: str):
+    names = {"thread": 0, "warp": 1, "block": 2}
+    return [(names[a], a) for a in (["block", "warp", "thread"] if arg == "all" else arg.split(","))]
+
+
 def busbw_factor(coll: str, n: int) -> float:
     if n <= 1:
         return 1.0

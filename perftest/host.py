@@ -13,7 +13,7 @@ import time
 import torch
 
 from .common import Env, ok, sizes_pow2, stream_ptr
-from .rma import parse_size
+from .common import parse_size
 
 
 def main():

@@ -7,6 +7,11 @@ the 126 MB L2 where DRAM figures matter, a few hundred MB on the device at most,
   python -m perftest.kernel_case --kernel moe_dispatch_fp8
   python -m perftest.kernel_case --kernel moe_combine
   python -m perftest.kernel_case --kernel allreduce       # one-PE on-stream allreduce kernel (copy path)
+  python -m perftest.kernel_case --kernel reducescatter | fcollect | alltoall | broadcast   # the other on-stream kernels, one PE
+  python -m perftest.kernel_case --kernel put_bw          # block-scope put loop of the RMA perftest onto this PE's own heap
+  python -m perftest.kernel_case --kernel get_bw
+  python -m perftest.kernel_case --kernel grouped_gemm    # grouped tcgen05 GEMM with the gated activation, 32 ragged groups
+  BSHMEM_FUSED_2CTA=0 python -m perftest.kernel_case --kernel gemm   # the one-CTA-per-tile variant of the GEMM kernel
 Prints the CUDA-event time of the last launch.
 """
 from __future__ import annotations
@@ -52,6 +57,21 @@ def main():
         print(f"{args.kernel}: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
         fg.check_errors()
         return
+    if args.kernel == "grouped_gemm":
+        G, N, K, R = 32, 4096, 7168, 16384   # 32 experts, gate + up of 2048 each, 16384 routed rows in ragged groups
+        sizes = torch.full((G,), R // G, dtype=torch.int64)
+        sizes[::2] += 37
+        sizes[1::2] -= 37
+        offs = torch.zeros(G + 1, dtype=torch.int32)
+        offs[1:] = sizes.cumsum(0).to(torch.int32)
+        x = torch.randn(R, K, device=dev).to(torch.bfloat16)
+        w = fg.interleave_gate_up((torch.randn(G, N, K, device=dev) * 0.02).to(torch.bfloat16))
+        out = torch.empty(R, N // 2, device=dev, dtype=torch.bfloat16)
+        offs_d = offs.to(dev)
+        ms = timed(lambda: fg.grouped_gemm(x, w, offs_d, out=out, act="swiglu"), args.launches)
+        print(f"grouped_gemm: {ms:.4f} ms, {2 * R * N * K / ms / 1e9:.1f} TFLOP/s ({G} groups, rows {int(sizes.min())}-{int(sizes.max())})")
+        fg.check_errors()
+        return
     import nvshmem_b200.core as nv
     nv.init(device=0, uid=nv.get_unique_id(), rank=0, nranks=1)
     try:
@@ -78,6 +98,26 @@ def main():
             src.fill_(1.0)
             ms = timed(lambda: nv.reduce(0, dst, src, "sum"), args.launches)
             print(f"allreduce (1 PE, copy path): {ms * 1e3:.1f} us, {2 * n * 4 / ms / 1e6:.0f} GB/s")
+        elif args.kernel in ("reducescatter", "fcollect", "alltoall", "broadcast"):
+            n = 64 << 20
+            src, dst = nv.tensor((n,), torch.float32), nv.tensor((n,), torch.float32)
+            src.fill_(1.0)
+            ms = timed(lambda: nv.collective_on_buffer(args.kernel, 0, dst, src, op="sum"), args.launches)
+            print(f"{args.kernel} (1 PE, copy path): {ms * 1e3:.1f} us, {2 * n * 4 / ms / 1e6:.0f} GB/s")
+        elif args.kernel in ("put_bw", "get_bw"):
+            import ctypes as C
+            from nvshmem_b200.bindings import host as H
+            lib = C.CDLL(str(H.lib_path("libbshmem_devtest.so")))
+            H.load().nvshmemx_b200_module_sync()
+            size, iters = 256 << 20, 4
+            sym = nv.tensor((size,), torch.uint8)
+            local = torch.empty(size, dtype=torch.uint8, device=dev)
+            counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            call = lambda: lib.perf_bw(C.c_void_p(sym.data_ptr()), C.c_void_p(local.data_ptr()), C.c_size_t(size), 0, iters, 2, int(args.kernel == "get_bw"), 32, 1024,
+                                       C.c_void_p(counter.data_ptr()), stream)
+            ms = timed(call, args.launches)
+            print(f"{args.kernel} (block scope, 32 CTAs x 1024 threads, own heap): {ms * 1e3 / iters:.1f} us per {size >> 20} MB, {2 * size * iters / ms / 1e6:.0f} GB/s read+write")
         else:
             raise SystemExit(f"unknown kernel {args.kernel}")
     finally:

@@ -112,5 +112,21 @@ def test_device_module_via_driver_api():
 
 
 @need2
+@pytest.mark.parametrize("script", ["torch_interop.py", "triton_interop.py", "tp_and_ep_blocks.py", "external_memory.py"])
+def test_python_examples_run_on_gpus(script):
+    """The example programs under examples/python, each as a torchrun job on two GPUs; they check their own results."""
+    import os
+    import subprocess
+    import sys
+    from tests._mp import ROOT, free_port
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NVSHMEM_WAIT_TIMEOUT_MS="5000", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(ROOT, "examples", "python", script)]
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "WRONG" not in res.stdout
+
+
+@need2
 def test_rank_leaves_between_steps():
     run_workers("rank_leaves_between_steps", NG, gpu=True, env=NO_NVLS)

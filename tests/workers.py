@@ -860,10 +860,10 @@ def collectives_on_stream():
     n = WORLD
     nvls = nv.heap_info()["mc_base"] != 0
     g = torch.Generator(device="cuda").manual_seed(5 + RANK)
-    sizes = [1, 3, 8, 255, 1024, 4097, 65536, 1 << 20]
+    sizes = [1, 3, 8, 30, 255, 1022, 1024, 4097, 8190, 65536, 1 << 20]  # 30 floats: one 120-byte packet; 1022, 8190: a partly filled last packet
     cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.int32, "min"), (torch.int64, "xor"), (torch.float64, "prod"), (torch.uint8, "and"),
              (torch.int16, "or")]
-    red_algos = ["auto", "oneshot", "twoshot", "ll"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
+    red_algos = ["auto", "oneshot", "twoshot", "ll", "ll128"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
     for dtype, op in cases:
         for count in sizes:
             if dtype.is_floating_point:
@@ -894,7 +894,7 @@ def collectives_on_stream():
                 nv.free_tensor(t)
     # reducescatter / fcollect / alltoall / broadcast
     for dtype in (torch.float32, torch.bfloat16, torch.int32):
-        for count in (1, 5, 256, 4099, 1 << 18):
+        for count in (1, 5, 30, 256, 2046, 4099, 1 << 18):
             make = (lambda m: (torch.rand(m, device="cuda", generator=g) * 2 - 1).to(dtype)) if dtype.is_floating_point else (lambda m: torch.randint(0, 1000, (m,), device="cuda", generator=g).to(dtype))
             big = nv.tensor((count * n,), dtype)
             small = nv.tensor((count,), dtype)
@@ -911,7 +911,7 @@ def collectives_on_stream():
                 want = _oracle("sum", [b[RANK * count:(RANK + 1) * count] for b in allbig])
                 assert _close(res, want, dtype), ("reducescatter", dtype, count, algo)
                 nv.free_tensor(res)
-            for algo in ["auto", "push", "ll"] + (["nvls"] if nvls else []):
+            for algo in ["auto", "push", "ll", "ll128"] + (["nvls"] if nvls else []):
                 out_big.zero_()
                 nv.barrier_all()
                 nv.fcollect(0, out_big, small, algo=algo)
@@ -924,7 +924,7 @@ def collectives_on_stream():
             want = torch.cat([b[RANK * count:(RANK + 1) * count] for b in allbig])
             assert torch.equal(out_big, want), ("alltoall", dtype, count)
             for root in {0, n - 1}:
-                for algo in ["auto", "push", "pull"] + (["nvls"] if nvls else []):
+                for algo in ["auto", "push", "pull", "ll", "ll"] + (["nvls"] if nvls else []):  # "ll" twice: generations alternate halves
                     res = nv.tensor((count,), dtype, zero=True)
                     nv.barrier_all()
                     nv.broadcast(0, res, small, root=root, algo=algo)
