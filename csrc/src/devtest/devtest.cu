@@ -189,6 +189,49 @@ __global__ void k_tile_put_get(float* dst, float* src, int R, int C, int r0, int
   nvshmemx_quiet_block();
 }
 
+// One call of each family of thin wrappers: queue-pair forms (the handle is accepted and ignored: load/store peers have
+// no queue pairs), sized puts / gets, byte collectives at the three scopes.  `buf` is a symmetric int64 array of at
+// least 64 + 8 * npes words, `sig` a symmetric signal word; results are checked on the host.
+__global__ void k_api_wrappers(long long* buf, uint64_t* sig, int pe, int* status) {
+  const nvshmemx_qp_handle_t qp = 0;
+  nvshmemx_qp_handle_t qps[1] = {0};
+  int rc = 0;
+  if (threadIdx.x == 0) {
+    nvshmemx_qp_longlong_p(buf + 0, 101LL, pe, qp);
+    long long two[2] = {202LL, 203LL};
+    nvshmemx_qp_longlong_put(buf + 1, two, 2, pe, qp);
+    nvshmemx_qp_longlong_put_nbi(buf + 3, two, 2, pe, qp);
+    nvshmemx_qp_quiet(0, qps, 1);
+    nvshmemx_qp_fence(0, qps, 1);
+    nvshmem_put64(buf + 5, two, 2, pe);
+    nvshmem_put32(buf + 7, two, 2, pe);            // two 32-bit elements: the low word of two[0] and its high word
+    nvshmem_put8(buf + 8, two, 8, pe);
+    nvshmem_quiet();
+  }
+  __syncthreads();
+  nvshmemx_qp_longlong_put_block(buf + 16, buf + 40, 8, pe, qp);   // whatever the source holds: compared with the source on the host
+  nvshmemx_qp_quiet_block(0, qps, 1);
+  if (threadIdx.x < 32) {
+    nvshmemx_qp_longlong_put_signal_warp(buf + 24, buf + 40, 8, sig, 5ULL, NVSHMEM_SIGNAL_ADD, pe, qp);
+    nvshmemx_qp_quiet_warp(0, qps, 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    nvshmemx_qp_signal_op(sig, 2ULL, NVSHMEM_SIGNAL_ADD, pe, qp);
+    nvshmem_quiet();
+  }
+  // byte collectives: every PE contributes 8 bytes (its word 48), gathered into words 64 .. 64 + npes
+  nvshmemx_barrier_all_block();
+  rc |= nvshmemx_fcollectmem_block(NVSHMEM_TEAM_WORLD, buf + 64, buf + 48, 8);
+  if (threadIdx.x < 32) rc |= nvshmemx_broadcastmem_warp(NVSHMEM_TEAM_WORLD, buf + 49, buf + 48, 8, 0);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    rc |= nvshmem_alltoallmem(NVSHMEM_TEAM_WORLD, buf + 64 + nvshmem_n_pes(), buf + 64, 8);
+    status[0] = rc;
+    status[1] = (int)nvshmemx_qp_longlong_g(buf + 48, pe, qp);
+  }
+}
+
 extern "C" {
 // With lazy module loading the first launch of a kernel may have to wait for running kernels to
 // finish.  Tests that start a waiting kernel before the kernel that satisfies it call this first.
@@ -196,7 +239,7 @@ int devtest_preload(void) {
   cudaFuncAttributes a;
   const void* fns[] = {(const void*)k_put, (const void*)k_get, (const void*)k_typed, (const void*)k_put_signal, (const void*)k_signal_wait_sum, (const void*)k_ring,
                        (const void*)k_wait_never, (const void*)k_amo_fetch_add, (const void*)k_amo_mix, (const void*)k_barrier_rounds, (const void*)k_device_coll,
-                       (const void*)k_tile_allreduce, (const void*)k_tile_allreduce_multi, (const void*)k_tile_put_get};
+                       (const void*)k_tile_allreduce, (const void*)k_tile_allreduce_multi, (const void*)k_tile_put_get, (const void*)k_api_wrappers};
   int bad = 0;
   for (const void* f : fns) bad |= cudaFuncGetAttributes(&a, f) != cudaSuccess;
   return bad;
@@ -252,6 +295,10 @@ int devtest_tile_allreduce(int team, float* dst, float* src, int R, int C, int r
 int devtest_tile_allreduce_multi(int team, float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int algo, int root, int ctas, cudaStream_t s) {
   if (ctas < 1 || ctas > BSHMEM_SYNC_SLOTS) return 1;
   k_tile_allreduce_multi<<<ctas, 256, 0, s>>>(team, dst, src, R, C, r0, c0, rows, cols, algo, root);
+  return LAUNCH_OK();
+}
+int devtest_api_wrappers(long long* buf, uint64_t* sig, int pe, int* status, cudaStream_t s) {
+  k_api_wrappers<<<1, 128, 0, s>>>(buf, sig, pe, status);
   return LAUNCH_OK();
 }
 int devtest_tile_put_get(float* dst, float* src, int R, int C, int r0, int c0, int rows, int cols, int pe, int get, cudaStream_t s) {

@@ -128,3 +128,31 @@ void bshmem_test_boot_finalize(void* h) {
 void bshmem_test_boot_drop_rank(int rank) { bootstrap_uid_test_drop_rank(rank); }
 const char* bshmem_test_boot_strerror(int st) { return bootstrap_strerror(st); }
 }
+
+// ---- transport seam: capability bits of the built-in load/store transport for a synthetic peer, and the error path
+// of the plugin loader (no GPU is touched for peers on another host or on the same device).
+#include "../state/runtime.h"
+#include "../transport/transport.h"
+extern "C" int bshmem_test_transport_caps(int same_host, int same_gpu, unsigned* caps, unsigned* attr) {
+  using namespace bshmem;
+  bshmem_transport* t = nullptr;
+  if (transport_p2p_init(&t) != 0) return 1;
+  PeInfo me{}, peer{};
+  me.host_hash = 42;
+  peer.host_hash = same_host ? 42 : 43;
+  memset(me.uuid, 7, 16);
+  memset(peer.uuid, same_gpu ? 7 : 9, 16);
+  snprintf(peer.pci_bus_id, sizeof(peer.pci_bus_id), "0000:ff:1f.0");
+  uint32_t c = 0;
+  int st = t->ops.can_reach_peer(t, &me, &peer, 0, &c);
+  *caps = c;
+  *attr = t->attr;
+  transport_destroy(t);
+  return st;
+}
+extern "C" int bshmem_test_transport_load(const char* name) {
+  bshmem::bshmem_transport* t = nullptr;
+  int st = bshmem::transport_load_plugin(name, &t);
+  if (st == 0) bshmem::transport_destroy(t);
+  return st;
+}

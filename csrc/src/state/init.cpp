@@ -10,6 +10,7 @@
 #include "../util/log.h"
 #include "../util/nvtx.h"
 #include "runtime.h"
+#include "../transport/transport.h"
 
 namespace bshmem {
 
@@ -63,31 +64,53 @@ int probe_topology(Runtime& r) {
   return ST_SUCCESS;
 }
 
-// Fills `reach` for every PE from the all-gathered PeInfo: which peers this GPU
-// can load/store to and do native atomics on
-// (reference: src/host/transport/p2p/p2p.cpp, nvshmemt_p2p_can_reach_peer).
+// Asks every transport which peers it reaches (the built-in P2P transport first, then a plugin named by
+// NVSHMEM_REMOTE_TRANSPORT), records per PE the first transport that reaches it, and fills the reach bits that the
+// rest of bring-up reads: bit 0 load/store, bit 1 native atomics, bit 2 same device
+// (reference: src/host/transport/transport.cpp nvshmemi_transport_init + nvshmemi_setup_connections,
+//  src/host/transport/p2p/p2p.cpp nvshmemt_p2p_can_reach_peer).
 static int build_reach_map(Runtime& r) {
   TopoRecord& t = r.topo;
   t.reach.assign(r.npes, 0);
-  const bool no_p2p = options().DISABLE_P2P;
-  for (int pe = 0; pe < r.npes; ++pe) {
-    const PeInfo& p = r.pe_info[pe];
-    uint8_t bits = 0;
-    if (p.host_hash == r.pe_info[r.mype].host_hash) {
-      if (memcmp(p.uuid, r.pe_info[r.mype].uuid, 16) == 0) {
-        bits = 7;  // the same GPU: plain addresses work
-      } else if (!no_p2p) {
-        // Find the local ordinal of the peer's GPU by PCI bus id.
-        int peer_dev = -1;
-        if (cudaDeviceGetByPCIBusId(&peer_dev, p.pci_bus_id) == cudaSuccess && peer_dev >= 0) {
-          int can = 0, atom = 0;
-          cudaDeviceCanAccessPeer(&can, r.device, peer_dev);
-          cudaDeviceGetP2PAttribute(&atom, cudaDevP2PAttrNativeAtomicSupported, r.device, peer_dev);
-          if (can) bits |= 1;
-          if (can && atom) bits |= 2;
-        }
-      }
+  if (r.transports.empty()) {
+    bshmem_transport* p2p = nullptr;
+    if (transport_p2p_init(&p2p) != 0) return ST_INTERNAL;
+    r.transports.push_back(p2p);
+    const std::string remote = options().REMOTE_TRANSPORT;
+    if (!remote.empty() && remote != "none" && remote != "NONE") {
+      bshmem_transport* extra = nullptr;
+      if (transport_load_plugin(remote, &extra) != 0) return ST_NOT_SUPPORTED;
+      r.transports.push_back(extra);
     }
+  }
+  r.transport_of_pe.assign(r.npes, -1);
+  for (size_t ti = 0; ti < r.transports.size(); ++ti) {
+    bshmem_transport* tr = r.transports[ti];
+    tr->cap.assign(r.npes, 0);
+    for (int pe = 0; pe < r.npes; ++pe) {
+      uint32_t caps = 0;
+      if (tr->ops.can_reach_peer(tr, &r.pe_info[r.mype], &r.pe_info[pe], r.device, &caps) != 0) caps = 0;
+      tr->cap[pe] = caps;
+      if (caps && r.transport_of_pe[pe] < 0) r.transport_of_pe[pe] = (int)ti;
+    }
+    if (tr->ops.connect_endpoints && !(tr->attr & TRANSPORT_ATTR_NO_ENDPOINTS)) {
+      std::vector<int> mine;
+      for (int pe = 0; pe < r.npes; ++pe)
+        if (r.transport_of_pe[pe] == (int)ti) mine.push_back(pe);
+      if (!mine.empty() && tr->ops.connect_endpoints(tr, mine.data(), (int)mine.size()) != 0) return ST_INTERNAL;
+    }
+    std::string info;
+    if (tr->ops.show_info && tr->ops.show_info(tr, &info) == 0) INFO(SUB_TRANSPORT, "transport %zu: %s", ti, info.c_str());
+  }
+  for (int pe = 0; pe < r.npes; ++pe) {
+    const int ti = r.transport_of_pe[pe];
+    const uint32_t caps = ti >= 0 ? r.transports[ti]->cap[pe] : 0;
+    uint8_t bits = 0;
+    // Only the built-in transport gives GPU threads direct access; a peer reached by a plugin alone is not
+    // load/store reachable and bring-up refuses it further down (no proxy path is built).
+    if (ti == 0 && (caps & TRANSPORT_CAP_GPU_LD) && (caps & TRANSPORT_CAP_GPU_ST)) bits |= 1;
+    if (ti == 0 && (caps & TRANSPORT_CAP_GPU_ATOMICS)) bits |= 2;
+    if (caps & TRANSPORT_CAP_SAME_DEVICE) bits |= 4;
     t.reach[pe] = bits;
     if (!(bits & 1)) t.all_peers_ldst = false;
     if (!(bits & 2)) t.all_peers_atomics = false;
@@ -369,6 +392,9 @@ int runtime_finalize() {
   }
   watchdog_stop(r);
   teams_finalize(r);
+  for (bshmem_transport* tr : r.transports) transport_destroy(tr);
+  r.transports.clear();
+  r.transport_of_pe.clear();
   if (r.have_gpu) {
     cudaDeviceSynchronize();
     if (r.stream) cudaStreamDestroy(r.stream);

@@ -56,6 +56,8 @@ struct PeInfo {  // all-gathered at init
   char uuid[16];
 };
 
+struct bshmem_transport;
+
 struct Team {
   int idx = -1;
   int start = 0, stride = 1, size = 0, my_pe = -1;
@@ -85,6 +87,8 @@ struct Runtime {
   bool have_gpu = false;
   TopoRecord topo;
   std::vector<PeInfo> pe_info;
+  std::vector<bshmem_transport*> transports;   // [0] is the built-in load/store transport
+  std::vector<int> transport_of_pe;            // index into `transports` of the first transport that reaches each PE (-1: none)
   std::unique_ptr<SymmetricHeap> heap;
   bshmemi_state_t dstate{};
   bshmemi_status_t* status_host = nullptr;   // pinned + mapped (GPU) or plain (host mode)

@@ -22,6 +22,7 @@ static const char* cat_name(OptCat c) {
     case OptCat::Bootstrap: return "Bootstrap options";
     case OptCat::Collectives: return "Collectives options";
     case OptCat::Memory: return "Memory options";
+    case OptCat::Transport: return "Transport options";
     case OptCat::Debug: return "Debugging options";
     default: return "Hidden options";
   }
@@ -48,7 +49,7 @@ int main(int argc, char** argv) {
     printf("  %-36s %s\n", "CUDA architectures", "sm_100a");
     printf("  %-36s %s\n", "Bootstraps", "UID (built in), plugin loader");
     printf("  %-36s %s\n", "Transports", "NVLink load/store, NVLS multicast");
-    printf("  %-36s %s\n", "Remote transports (IB, UCX, OFI)", "not built");
+    printf("  %-36s %s\n", "Remote transports (IB, UCX, OFI)", "none shipped; plugin seam libbshmem_transport_<name>.so (NVSHMEM_REMOTE_TRANSPORT)");
     printf("  %-36s %s\n", "Heap back ends", "CUDA VMM, host shared memory");
     printf("  %-36s %s\n", "Device waits", "bounded (NVSHMEM_WAIT_TIMEOUT_MS)");
     printf("  %-36s %d\n", "Maximum PEs for stack arrays", BSHMEM_MAX_PES);

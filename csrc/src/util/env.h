@@ -15,7 +15,7 @@
 namespace bshmem {
 
 enum class OptKind { Bool, Long, Size, Str };
-enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
+enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug, Hidden };
 
 // clang-format off
 // X(name, ctype, kind, default, category, help)
@@ -38,6 +38,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Debug, Hidden };
   X(DISABLE_NVLS,          bool,        Bool, false,            OpenShmem,   "Do not create NVLink multicast objects even where supported") \
   X(NVLS_TEAM_WINDOWS,     long,        Long, 16,               OpenShmem,   "NVLink multicast windows a PE may hold for teams that do not span the world (0: such teams never get one)") \
   X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Refused on a GPU: the GPU heap needs CUDA virtual memory management (the cudaMalloc + IPC heap of the reference is not built); see NVSHMEM_HEAP_BACKEND") \
+  X(REMOTE_TRANSPORT,      std::string, Str,  "none",           Transport,   "Name of a transport plugin (libbshmem_transport_<name>.so) to load beside the built-in load/store transport; none is shipped") \
   X(DISABLE_P2P,           bool,        Bool, false,            Hidden,      "Treat peers as not load/store reachable (init then fails: no remote transport is built)") \
   X(DISABLE_CE_COLLECTIVES,bool,        Bool, false,            Collectives, "Never use copy engines for on-stream alltoall/fcollect/broadcast") \
   X(CE_COLLECTIVES_MIN_BYTES, size_t,   Size, 0,                Collectives, "On-stream alltoall/fcollect/broadcast of at least this many bytes go through copy engines (0: never)") \

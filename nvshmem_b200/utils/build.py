@@ -136,7 +136,7 @@ def build_sanitized(sanitize: str, jobs: int | None = None) -> dict[str, Path]:
     flags = san + ["-Xcompiler", "-fno-omit-frame-pointer", "-g"]
     built = {}
     for name, srcs, out, libs in (
-            ("host", _sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), lib_dir / "libbshmem_host.so",
+            ("host", _sources("util", "bootstrap", "heap", "team", "state", "transport", "host", "coll"), lib_dir / "libbshmem_host.so",
              ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
             ("plugins", _sources("bootstrap_plugins"), lib_dir / "libbshmem_bootstrap_file.so", [])):
         with ThreadPoolExecutor(jobs) as ex:
@@ -151,7 +151,7 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
     hdr = _headers_mtime()
     jobs = jobs or min(8, os.cpu_count() or 4)
     groups = {
-        "host": (_sources("util", "bootstrap", "heap", "team", "state", "host", "coll"), LIB / "libbshmem_host.so", True,
+        "host": (_sources("util", "bootstrap", "heap", "team", "state", "transport", "host", "coll"), LIB / "libbshmem_host.so", True,
                  ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
         "fused": (_sources("fused"), LIB / "libbshmem_fused.so", True, ["-ldl"]),
         "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),

@@ -232,3 +232,16 @@ def test_unique_id_with_a_foreign_version_is_refused():
     h = lib.bshmem_test_boot_init(C.byref(uid), 0, 1, C.byref(st))
     assert h and st.value == 0
     lib.bshmem_test_boot_finalize(C.c_void_p(h))
+
+
+def test_transport_seam_capabilities_and_plugin_errors(hostlib):
+    """The built-in load/store transport reports no reach across hosts and full capabilities (with the same-device bit)
+    for another PE on the same GPU; a transport plugin that does not exist is a clean error."""
+    import ctypes as C
+    caps, attr = C.c_uint(0), C.c_uint(0)
+    assert hostlib.bshmem_test_transport_caps(0, 0, C.byref(caps), C.byref(attr)) == 0 and caps.value == 0
+    assert attr.value == 0b111                      # no endpoints, no registration, no proxy
+    assert hostlib.bshmem_test_transport_caps(1, 1, C.byref(caps), C.byref(attr)) == 0
+    MAP, LD, ST, ATOM, SAME = 1, 2, 4, 8, 128
+    assert caps.value & (MAP | LD | ST | ATOM | SAME) == (MAP | LD | ST | ATOM | SAME)
+    assert hostlib.bshmem_test_transport_load(b"no_such_transport") != 0

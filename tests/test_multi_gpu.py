@@ -107,6 +107,11 @@ def test_tp_mlp_matches_single_device():
 
 
 @need2
+def test_device_api_wrappers_and_copy_engine_collectives():
+    run_workers("device_api_wrappers_and_copy_engine_collectives", NG, gpu=True, env=NO_NVLS, timeout=300)
+
+
+@need2
 def test_device_module_via_driver_api():
     run_workers("device_module_via_driver_api", NG, gpu=True, env=NO_NVLS, timeout=300)
 

@@ -1351,6 +1351,70 @@ def team_multicast_windows():
 
 
 @worker
+def device_api_wrappers_and_copy_engine_collectives():
+    """(1) One kernel that calls each family of thin device wrappers once: the queue-pair forms, sized puts, byte
+    collectives at thread / warp / block scope.  (2) The copy-engine variants of fcollect / alltoall / broadcast on
+    several PEs (one memcpy per member into the member's window, then a barrier)."""
+    nv = setup()
+    dt = _devtest()
+    n, me = WORLD, RANK
+    right, left = (me + 1) % n, (me - 1) % n
+    words = 64 + 2 * n + 8
+    buf = nv.tensor((words,), torch.int64, zero=True)
+    sig = nv.tensor((1,), torch.int64, zero=True)
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    buf[40:48] = torch.arange(8, device="cuda", dtype=torch.int64) + 1000 * (me + 1)   # source of the block / warp puts
+    buf[48] = 7000 + me                                                                # contribution to the byte collectives
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    assert dt.devtest_api_wrappers(C.c_void_p(buf.data_ptr()), C.c_void_p(sig.data_ptr()), right, C.c_void_p(status.data_ptr()), _stream()) == 0
+    nv.barrier_all()
+    torch.cuda.synchronize()
+    got = buf.cpu().tolist()
+    assert status.tolist()[0] == 0 and nv.error_bits() == 0
+    assert got[0] == 101 and got[1:3] == [202, 203] and got[3:5] == [202, 203] and got[5:7] == [202, 203]      # written by my left neighbour
+    assert got[7] == 202 and got[8] == 202
+    src_left = [1000 * (left + 1) + i for i in range(8)]
+    assert got[16:24] == src_left and got[24:32] == src_left
+    assert int(sig[0]) == 7                                                             # put_signal added 5, signal_op added 2
+    assert got[64:64 + n] == [7000 + p for p in range(n)]                               # fcollectmem
+    assert got[49] == 7000                                                              # broadcastmem from PE 0
+    assert got[64 + n:64 + 2 * n] == [7000 + me] * n                                    # alltoallmem: word `me` of every PE's gathered row
+    assert status.tolist()[1] == 7000 + right                                           # qp g
+    # ---- copy-engine collectives
+    cnt = 1 << 16
+    src, dst = nv.tensor((cnt * n,), torch.float32), nv.tensor((cnt * n,), torch.float32)
+    src.copy_(torch.arange(cnt * n, device="cuda", dtype=torch.float32) + 1e6 * me)
+    allsrc = _gather(src)
+    nv.set_ce_collectives(1)
+    try:
+        dst.zero_()
+        nv.barrier_all()
+        nv.fcollect(0, dst, src[:cnt])
+        nv.barrier_all()
+        torch.cuda.synchronize()
+        assert torch.equal(dst, torch.cat([a[:cnt] for a in allsrc])), "copy-engine fcollect"
+        dst.zero_()
+        nv.barrier_all()
+        nv.alltoall(0, dst, src)
+        nv.barrier_all()
+        torch.cuda.synchronize()
+        assert torch.equal(dst, torch.cat([a[me * cnt:(me + 1) * cnt] for a in allsrc])), "copy-engine alltoall"
+        dst.zero_()
+        nv.barrier_all()
+        nv.broadcast(0, dst, src, root=n - 1)
+        nv.barrier_all()
+        torch.cuda.synchronize()
+        assert torch.equal(dst, allsrc[n - 1]), "copy-engine broadcast"
+    finally:
+        nv.set_ce_collectives(0)
+    assert nv.error_bits() == 0
+    for t in (buf, sig, src, dst):
+        nv.free_tensor(t)
+    teardown(nv)
+
+
+@worker
 def device_module_via_driver_api():
     """Device code in a separately loaded module: a kernel is compiled to a cubin with nvcc, loaded with cuModuleLoadData,
     handed the library state with nvshmemx_cumodule_init, and puts to the next PE."""
