@@ -1,5 +1,7 @@
-"""A minimal PMI-1 ("simple PMI") process manager, enough to start the UNMODIFIED reference perftest
-binaries of ``baseline/_ref`` on the GPUs of one node without MPI, Hydra or Slurm.
+"""A minimal PMI-1 ("simple PMI") and PMI-2 process manager, enough to start the UNMODIFIED reference perftest
+binaries of ``baseline/_ref`` on the GPUs of one node without MPI, Hydra or Slurm.  A client that opens with
+``cmd=init pmi_version=2`` is served the PMI-2 wire protocol from then on (6-digit length + ``cmd=..;key=value;``
+messages: fullinit, job-getid, kvs-put, kvs-get, kvs-fence, finalize, abort).
 
 The reference programs call ``nvshmem_init()``, whose default bootstrap is PMI: each process finds a
 socket in ``PMI_FD`` and speaks a line protocol (init, get_maxes, get_my_kvsname, put, get, barrier_in,
@@ -38,6 +40,8 @@ def launch(n: int, cmd: list[str], timeout: float = 300.0, env_extra: dict | Non
     kvs: dict[str, str] = {}
     socks, procs, bufs = [], [], []
     in_barrier: set[int] = set()
+    v2: set[int] = set()        # connections that negotiated PMI-2
+    in_fence: set[int] = set()
     for rank in range(n):
         parent, child = socket.socketpair()
         env = dict(os.environ)
@@ -64,7 +68,11 @@ def launch(n: int, cmd: list[str], timeout: float = 300.0, env_extra: dict | Non
         kv = parse(line)
         c = kv.get("cmd", "")
         if c == "init":
-            reply(i, "cmd=response_to_init pmi_version=1 pmi_subversion=1 rc=0\n")
+            if kv.get("pmi_version") == "2":
+                v2.add(i)
+                reply(i, "cmd=response_to_init pmi_version=2 pmi_subversion=0 rc=0\n")
+            else:
+                reply(i, "cmd=response_to_init pmi_version=1 pmi_subversion=1 rc=0\n")
         elif c == "get_maxes":
             reply(i, "cmd=maxes kvsname_max=256 keylen_max=256 vallen_max=1024\n")
         elif c == "get_my_kvsname":
@@ -95,6 +103,38 @@ def launch(n: int, cmd: list[str], timeout: float = 300.0, env_extra: dict | Non
                 if p.poll() is None:
                     p.kill()
 
+    def reply2(i: int, body: str) -> None:
+        reply(i, f"{len(body):6d}{body}")
+
+    def handle2(i: int, body: str) -> None:
+        kv = dict(tok.split("=", 1) for tok in body.split(";") if "=" in tok)
+        c = kv.get("cmd", "")
+        if c == "fullinit":
+            reply2(i, f"cmd=fullinit-response;pmi-version=2;pmi-subversion=0;rank={kv.get('pmirank', i)};size={n};appnum=0;debugged=FALSE;pmiverbose=FALSE;rc=0;")
+        elif c == "job-getid":
+            reply2(i, "cmd=job-getid-response;jobid=kvs_ref_0;rc=0;")
+        elif c == "kvs-put":
+            kvs[kv.get("key", "")] = kv.get("value", "")
+            reply2(i, "cmd=kvs-put-response;rc=0;")
+        elif c == "kvs-get":
+            key = kv.get("key", "")
+            if key in kvs:
+                reply2(i, f"cmd=kvs-get-response;found=TRUE;value={kvs[key]};rc=0;")
+            else:
+                reply2(i, "cmd=kvs-get-response;found=FALSE;rc=0;")
+        elif c == "kvs-fence":
+            in_fence.add(i)
+            if len(in_fence) == n:
+                for j in in_fence:
+                    reply2(j, "cmd=kvs-fence-response;rc=0;")
+                in_fence.clear()
+        elif c == "finalize":
+            reply2(i, "cmd=finalize-response;rc=0;")
+        elif c == "abort":
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+
     while live and time.time() < deadline:
         ready, _, _ = select.select([socks[i] for i in live], [], [], 0.2)
         for s in ready:
@@ -109,9 +149,26 @@ def launch(n: int, cmd: list[str], timeout: float = 300.0, env_extra: dict | Non
                 live.discard(i)
                 continue
             bufs[i] += data
-            while b"\n" in bufs[i]:
-                line, bufs[i] = bufs[i].split(b"\n", 1)
-                handle(i, line.decode(errors="replace"))
+            while True:
+                if i in v2 and bufs[i][:4] == b"cmd=":
+                    v2.discard(i)  # a client that finalized and initialises again opens with a PMI-1 style line
+                if i in v2:
+                    if len(bufs[i]) < 6:
+                        break
+                    try:
+                        ln = int(bufs[i][:6])
+                    except ValueError:
+                        bufs[i] = b""
+                        break
+                    if len(bufs[i]) < 6 + ln:
+                        break
+                    body, bufs[i] = bufs[i][6:6 + ln], bufs[i][6 + ln:]
+                    handle2(i, body.decode(errors="replace"))
+                else:
+                    if b"\n" not in bufs[i]:
+                        break
+                    line, bufs[i] = bufs[i].split(b"\n", 1)
+                    handle(i, line.decode(errors="replace"))
         for i in list(live):
             if procs[i].poll() is not None and not select.select([socks[i]], [], [], 0)[0]:
                 live.discard(i)

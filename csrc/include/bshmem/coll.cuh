@@ -24,7 +24,7 @@
 namespace bshmem {
 
 enum ReduceOp { OP_AND = 0, OP_OR = 1, OP_XOR = 2, OP_MIN = 3, OP_MAX = 4, OP_SUM = 5, OP_PROD = 6 };
-enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4, RED_LL = 5, RED_LL128 = 6 };
+enum ReduceAlgo { RED_AUTO = 0, RED_ONESHOT_PULL = 1, RED_TWOSHOT = 2, RED_NVLS_ONESHOT = 3, RED_NVLS_TWOSHOT = 4, RED_LL = 5, RED_LL128 = 6, RED_RECEXCH = 7 };
 enum FcollectAlgo { FC_AUTO = 0, FC_PUSH = 1, FC_LL = 2, FC_NVLS = 3, FC_LL128 = 4 };
 enum RsAlgo { RS_AUTO = 0, RS_PULL = 1, RS_NVLS = 2 };
 enum BcastAlgo { BC_AUTO = 0, BC_PUSH = 1, BC_LL = 2, BC_NVLS = 3, BC_PULL = 4 };
@@ -516,6 +516,79 @@ __device__ __forceinline__ int allreduce_ll(const bshmemi_team_t* t, T* dst, con
   return err;
 }
 
+// ------------------------------------------------------------------ allreduce by recursive exchange
+// log2(size) rounds; in round r member m exchanges its running result with member m ^ (1 << r): it pushes the result
+// into the partner's scratch area of that round, raises the partner's round flag and, once its own flag is up,
+// combines what the partner pushed.  Teams whose size is not a power of two fold first: the members beyond the largest
+// power of two hand their vector to a partner below it and get the final result back.  Every member talks to
+// log2(size) peers instead of size - 1, which is what matters on fabrics where reaching a peer is expensive; on a flat
+// NVSwitch it is never the automatic choice (NVSHMEM_REDUCE_ALGO=7 or an explicit algorithm argument selects it).
+// The neighbour of a round is computed from the member index, so teams carry no neighbour lists.  Scratch: the team's
+// reduction scratch, two halves by generation, each [max-location slots][64 round flags][rounds + 1 vectors]; the generation lives in the
+// collective-epoch word of slot 2 (no flag-in-data collective uses it).
+// (reference: src/include/non_abi/device/coll/reduce.cuh:1050-1156, src/host/team/team_internal.cpp:284-455)
+constexpr size_t RECEXCH_OFFSET = 16 * BSHMEM_MAX_PES;
+template <class T, int OP, int SCOPE>
+__device__ __forceinline__ int allreduce_recexch(const bshmemi_team_t* t, T* dst, const T* src, size_t n) {
+  typedef typename Acc<T>::type A;
+  const int size = t->size, me = t->my_pe;
+  const int rank = group_rank<SCOPE>(), G = group_size<SCOPE>();
+  uint64_t* epochs = (uint64_t*)t->epochs + BSHMEM_SYNC_SLOTS + 2;
+  group_sync<SCOPE>();
+  const uint64_t gen = epochs[0] + 1;
+  char* half = (char*)t->scratch_base + (gen & 1) * t->scratch_bytes;
+  // The first RECEXCH_OFFSET bytes of a half belong to the max-location reduction (one pair per member).
+  uint64_t* flags = (uint64_t*)(half + RECEXCH_OFFSET);                 // [64]
+  T* slots = (T*)(half + RECEXCH_OFFSET + 64 * sizeof(uint64_t));       // [rounds + 1][n]
+  int p2 = 1, rounds = 0;
+  while (p2 * 2 <= size) { p2 *= 2; ++rounds; }
+  const int extra = size - p2;                       // members p2 .. size-1 fold into 0 .. extra-1
+  int err = 0;
+  auto push = [&](int to, int slot_idx, const T* v) {
+    T* remote = translate(slots + (size_t)slot_idx * n, team_world_pe(t, to));
+    for (size_t i = rank; i < n; i += G) remote[i] = v[i];
+    group_sync<SCOPE>();
+    if (rank == 0) {
+      fence_sys();
+      st_relaxed_sys(translate(flags + slot_idx, team_world_pe(t, to)), gen);
+    }
+  };
+  auto wait = [&](int slot_idx) {
+    if (rank == 0) err |= poll_ge<true>(flags + slot_idx, gen);
+    group_sync<SCOPE>();
+  };
+  if (dst != src) {
+    for (size_t i = rank; i < n; i += G) dst[i] = src[i];
+    group_sync<SCOPE>();
+  }
+  if (me >= p2) {
+    push(me - p2, rounds, dst);      // fold in ...
+    wait(rounds);                    // ... and wait for the result
+    for (size_t i = rank; i < n; i += G) dst[i] = slots[(size_t)rounds * n + i];
+  } else {
+    if (me < extra) {
+      wait(rounds);
+      for (size_t i = rank; i < n; i += G) dst[i] = from_acc<T>(combine<A, OP>(to_acc<T>(dst[i]), to_acc<T>(slots[(size_t)rounds * n + i])));
+      group_sync<SCOPE>();
+    }
+    for (int r = 0; r < rounds; ++r) {
+      const int partner = me ^ (1 << r);
+      push(partner, r, dst);
+      wait(r);
+      // Both partners combine in the same order (lower member's value first), so every member ends with the same bits.
+      for (size_t i = rank; i < n; i += G) {
+        const A mine = to_acc<T>(dst[i]), theirs = to_acc<T>(slots[(size_t)r * n + i]);
+        dst[i] = from_acc<T>(me < partner ? combine<A, OP>(mine, theirs) : combine<A, OP>(theirs, mine));
+      }
+      group_sync<SCOPE>();
+    }
+    if (me < extra) push(me + p2, rounds, dst);
+  }
+  group_sync<SCOPE>();
+  if (rank == 0) epochs[0] = gen;
+  return err;
+}
+
 // ------------------------------------------------------------------ reduction inside the switch
 // dst[0, bytes) = reduction over the team of the `bytes` at multicast address mc_src, by the calling group.
 // MC_STORE: dst is a multicast address too and the result is stored to every member (second half of a
@@ -598,6 +671,13 @@ __device__ __forceinline__ int allreduce_range(const bshmemi_team_t* t, T* dst, 
   }
   if (algo == RED_LL128) {
     if (ll128_ok) return allreduce_ll128<T, OP, SCOPE>(t, dst, src, hi, slot);
+    algo = RED_AUTO;
+  }
+  if (algo == RED_RECEXCH) {
+    int rounds = 0;
+    for (int p = 1; p * 2 <= size; p *= 2) ++rounds;
+    const bool fits = lo == 0 && slot == 0 && RECEXCH_OFFSET + 64 * sizeof(uint64_t) + (size_t)(rounds + 1) * bytes <= t->scratch_bytes;
+    if (fits) return allreduce_recexch<T, OP, SCOPE>(t, dst, src, hi);
     algo = RED_AUTO;
   }
   if (algo == RED_AUTO) {

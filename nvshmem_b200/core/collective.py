@@ -9,7 +9,7 @@ from .memory import tensor_ptr
 from .types import NvshmemError, NvshmemInvalid, stream_handle
 
 _OPS = {"and": H.OP_AND, "or": H.OP_OR, "xor": H.OP_XOR, "min": H.OP_MIN, "max": H.OP_MAX, "sum": H.OP_SUM, "prod": H.OP_PROD}
-REDUCE_ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls_oneshot": 3, "nvls_twoshot": 4, "ll": 5, "ll128": 6}
+REDUCE_ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls_oneshot": 3, "nvls_twoshot": 4, "ll": 5, "ll128": 6, "recexch": 7}
 FCOLLECT_ALGOS = {"auto": 0, "push": 1, "ll": 2, "nvls": 3, "ll128": 4}
 RS_ALGOS = {"auto": 0, "pull": 1, "nvls": 2}
 BCAST_ALGOS = {"auto": 0, "push": 1, "ll": 2, "nvls": 3, "pull": 4}

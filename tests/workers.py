@@ -863,7 +863,7 @@ def collectives_on_stream():
     sizes = [1, 3, 8, 30, 255, 1022, 1024, 4097, 8190, 65536, 1 << 20]  # 30 floats: one 120-byte packet; 1022, 8190: a partly filled last packet
     cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.int32, "min"), (torch.int64, "xor"), (torch.float64, "prod"), (torch.uint8, "and"),
              (torch.int16, "or")]
-    red_algos = ["auto", "oneshot", "twoshot", "ll", "ll128"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
+    red_algos = ["auto", "oneshot", "twoshot", "ll", "ll128", "recexch"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
     for dtype, op in cases:
         for count in sizes:
             if dtype.is_floating_point:
