@@ -116,10 +116,11 @@ def reference_arm(args):
     return reference_bench.run(args, M, N, K_LOCAL)
 
 
-def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step):
+def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step, errors=None):
     """Times `step(x, w) -> out` on device-resident inputs (R regions of --steps steps), then the end-to-end run of
     `stack` (an object with `input_shard`, `forward(out_index) -> tensor`, `kernels_per_forward`).  Returns the JSON
-    line (without `impl`).  Both arms of the benchmark go through this function."""
+    line (without `impl`).  Both arms of the benchmark go through this function.  `errors()`, when given, returns a
+    description of what went wrong on the device since its last call, or None (collective over the ranks)."""
     import torch
     import torch.distributed as dist
 
@@ -163,6 +164,7 @@ def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launch
     flops_per_rank = 2.0 * M * N * K_LOCAL
     value = world * flops_per_rank / (ms_per_step * 1e-3) / 1e12
     del xs, ws
+    device_timed_error = errors() if errors else None
 
     # ---------------- end to end: L MLP blocks per step, token shard in from pinned host memory, output shard back out
     rows = M // world
@@ -220,7 +222,8 @@ def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launch
     L = stack.layers
     e2e_value = world * (2 * L * flops_per_rank) / (e2e_ms_per_step * 1e-3) / 1e12
     checksum = float(host_out[(args.steps - 1) & 1].float().abs().mean())
-    return {
+    e2e_error = errors() if errors else None
+    line = {
         "metric": "fused_gemm_reduce_scatter_tflops",
         "value": round(value, 2),
         "unit": "TFLOP/s",
@@ -245,6 +248,11 @@ def timed_runs(step, stack, args, M, N, K_LOCAL, rank, world, local_rank, launch
                 "output_abs_mean": round(checksum, 6)},
         "gpu_launches": args.steps * len(per_step) * launches_per_step,
     }
+    if device_timed_error:
+        line["invalid"] = device_timed_error
+    if e2e_error:
+        line["e2e"]["invalid"] = e2e_error
+    return line
 
 
 def main():
@@ -285,8 +293,8 @@ def main():
     class Stack:
         """The public model object behind the interface the timing harness wants."""
 
-        def __init__(self):
-            self.model = TensorParallelMLPStack(HIDDEN, K_LOCAL * world, M, args.layers, seed=99 + rank)
+        def __init__(self, gather):
+            self.model = TensorParallelMLPStack(HIDDEN, K_LOCAL * world, M, args.layers, seed=99 + rank, gather=gather, wait_limit_ms=3000)
             self.layers = args.layers
             self.kernels_per_forward = self.model.kernels_per_forward
             self.outs = [torch.empty_like(self.model.out) for _ in range(2)]
@@ -296,12 +304,32 @@ def main():
             self.model.out = self.outs[b]
             return self.model.forward()
 
-    stack = Stack()
+    def errors():
+        bad = torch.tensor([fg.take_error(dev)], device=dev, dtype=torch.int32)
+        if world > 1:
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        return "a kernel gave up on a bounded wait" if int(bad.item()) else None
+
+    def works(stack):
+        """Two forward passes; true when no kernel of any rank gave up on a wait (the waits are bounded: a path that
+        does not work on this machine costs seconds, not the run)."""
+        for b in range(2):
+            stack.forward(b)
+        return errors() is None
+
+    stack = Stack("fused")
+    e2e_path = "all-gather fused into the GEMM kernel"
+    if not works(stack):
+        stack.model.close()
+        stack = Stack("collective")
+        e2e_path = "all-gather by the library's fcollect kernel, then the GEMM kernel (the fused all-gather gave up on a wait in the trial passes)"
+        if not works(stack):
+            e2e_path += "; this path gave up on a wait as well: the end-to-end figure is not valid"
     # one fused tcgen05 kernel per step (libbshmem_fused.so): GEMM, partial tiles, flags and the reduction
-    line = timed_runs(lambda x, w: op(x, w), stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=1)
+    line = timed_runs(lambda x, w: op(x, w), stack, args, M, N, K_LOCAL, rank, world, local_rank, launches_per_step=1, errors=errors)
     line["impl"] = "ours"
+    line["e2e"]["path"] = e2e_path
     line["path"] = "one fused kernel per step; partial tiles reduced by " + ("the switch (multimem.ld_reduce)" if op.switch_path else ("pushes to the owner" if world > 1 else "nobody (one PE)"))
-    fg.check_errors(dev)
     stack.model.close()
     op.close()
     nv.finalize()

@@ -51,6 +51,11 @@ typedef struct {
   uint64_t* flags[BSHMEM_MOE_MAX_PES];    /* [4, npes] uint64 barrier flags on every PE */
   /* local scratch: bshmem_moe_scratch_bytes(E) bytes, 256-byte aligned, contents irrelevant on entry */
   void* scratch;
+  /* Optional: [cap_rows] int32 on every PE (symmetric).  When set, a token that goes to several experts of one PE
+   * crosses NVLink once: its row is written to the first of its rows on that PE, the other rows receive only the
+   * number of that first row here, and the receiving PE copies the row locally before the kernel ends.  Null on every
+   * entry = every (token, expert) pair is sent (the only form with one PE). */
+  int* dup_src[BSHMEM_MOE_MAX_PES];
 } bshmem_moe_dispatch_args_t;
 
 typedef struct {

@@ -9,8 +9,11 @@
 //      local expert, then by source PE, so the expert GEMMs read contiguous groups
 //   D  one CTA per token: the row is staged in shared memory once (and quantised once to fp8 with
 //      1x128 fp32 scales when asked), each of its K slots takes the next row of its segment with an
-//      atomic cursor, and the row is pushed with 16-byte stores to the owning PE
-//   E  grid barrier, then a cross-PE barrier: when the kernel ends on one PE, every PE's rows have landed
+//      atomic cursor, and the row is pushed with 16-byte stores to the owning PE.  With `dup_src` a row
+//      crosses NVLink once per destination PE: the first of the token's slots on a PE carries the payload,
+//      the others only the number of that row
+//   E  grid barrier, then a cross-PE barrier: every PE's rows have landed
+//   F  (with `dup_src`) every PE copies the rows that arrived by number from their first row, locally
 // combine (one cooperative kernel): cross-PE barrier on entry (expert outputs are final), then one CTA
 // per token pulls its K rows with 16-byte loads from the owners, multiplies by the routing weights in
 // fp32, rounds once to bf16; a cross-PE barrier on exit lets the owners reuse their buffers.
@@ -128,6 +131,8 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
   unsigned phase = 0;
   int* s_bins = (int*)smem;                     // [E] histogram bins, later my segment starts; [E] more for totals
   __shared__ int s_row[THREADS], s_dest[THREADS];  // slots of one chunk of tokens: [token in chunk][choice]
+  __shared__ int s_first[THREADS];                 // -1: this slot carries the payload; else the row (same PE) that does
+  const bool dedup = a.dup_src[rank] != nullptr;
 
   // ---- A: histogram
   for (int e = threadIdx.x; e < E; e += THREADS) s_bins[e] = 0;
@@ -221,11 +226,28 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
       }
     }
     __syncthreads();
+    {
+      // Which slot of the token carries the payload to each destination PE: the first valid one.
+      const int i = threadIdx.x / K, k = threadIdx.x % K;
+      const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
+      if (i < per_chunk && t < T) {
+        int first = -1;
+        const int row = s_row[i * K + k], dest = s_dest[i * K + k];
+        if (dedup && row >= 0) {
+          for (int j = 0; j < k; ++j)
+            if (s_row[i * K + j] >= 0 && s_dest[i * K + j] == dest) { first = s_row[i * K + j]; break; }
+          a.dup_src[dest][row] = first;  // every row is written by its sender: -1 = payload follows, else copy from `first`
+        }
+        s_first[i * K + k] = first;
+      }
+    }
+    __syncthreads();
     for (int i = 0; i < per_chunk; ++i) {
       const long t = (long)blockIdx.x + (long)(base + i) * gridDim.x;
       if (t >= T) break;
       const int* rows = s_row + i * K;
       const int* dests = s_dest + i * K;
+      const int* firsts = s_first + i * K;
       if (a.payload == BSHMEM_MOE_FP8_E4M3) {
         // Eight lanes per 128-value block, 16 values per lane: a warp quantises four blocks at a time and
         // stores 16 bytes per lane (512 contiguous bytes per warp and destination).  absmax over the eight
@@ -275,7 +297,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
             if (g < nscale) {
               for (int j = 0; j < K; ++j) {
                 const int row = rows[j];
-                if (row < 0) continue;
+                if (row < 0 || firsts[j] >= 0) continue;
                 ((uint4*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes))[g * 8 + part] = q16;
                 if (part == 0) a.recv_scale[dests[j]][(size_t)row * nscale + g] = scale;
               }
@@ -292,7 +314,7 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
             if (c0 + u * THREADS < nvec) v[u] = xrow[c0 + u * THREADS];
           for (int j = 0; j < K; ++j) {
             const int row = rows[j];
-            if (row < 0) continue;
+            if (row < 0 || firsts[j] >= 0) continue;
             uint4* dst = (uint4*)((uint8_t*)a.recv_x[dests[j]] + (size_t)row * row_bytes);
 #pragma unroll
             for (int u = 0; u < 4; ++u)
@@ -306,6 +328,25 @@ __global__ void __launch_bounds__(THREADS) dispatch_kernel(const __grid_constant
   // ---- E: all my rows are out; meet every PE
   if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
   if (blockIdx.x == 0) pe_barrier(a.flags, 1, rank, npes, a.epoch, P.wait_limit_ns, a.error_flag);
+  if (!dedup) return;
+
+  // ---- F: rows that arrived as a row number are copied from that row (always a payload row), locally
+  if (!grid_barrier(&sc->grid_bar, phase, P.wait_limit_ns, a.error_flag)) return;
+  int total = 0;
+  for (int le = 0; le < EL; ++le) total += s_tot[rank * EL + le];
+  if (total > a.cap_rows) total = a.cap_rows;
+  const int* dup = a.dup_src[rank];
+  uint8_t* mine = (uint8_t*)a.recv_x[rank];
+  const int nvec = row_bytes / 16;
+  for (int r = blockIdx.x; r < total; r += gridDim.x) {
+    const int from = __ldcg(dup + r);
+    if (from < 0 || from >= total) continue;
+    const uint4* src = (const uint4*)(mine + (size_t)from * row_bytes);
+    uint4* dst = (uint4*)(mine + (size_t)r * row_bytes);
+    for (int c = threadIdx.x; c < nvec; c += THREADS) dst[c] = __ldcg(src + c);
+    if (a.payload == BSHMEM_MOE_FP8_E4M3)
+      for (int g = threadIdx.x; g < nscale; g += THREADS) a.recv_scale[rank][(size_t)r * nscale + g] = __ldcg(&a.recv_scale[rank][(size_t)from * nscale + g]);
+  }
 }
 
 // Weighted sum of up to KT expert rows into one output row.  Row pointers and weights sit in registers;

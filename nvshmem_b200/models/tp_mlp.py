@@ -47,9 +47,14 @@ class TensorParallelMLPStack:
     ``input_shard`` is where the caller puts this rank's ``[tokens/npes, hidden]`` tokens (it may be the
     target of a host-to-device copy); ``forward()`` returns this rank's ``[tokens/npes, hidden]`` result in a
     tensor owned by the object.
+
+    ``gather="fused"`` (default) is the above.  ``gather="collective"`` runs the all-gather as the library's
+    on-stream ``fcollect`` (its own kernel) followed by the plain GEMM with the same fused GELU: three kernels per
+    block, for comparison and as the path to fall back to when the fused all-gather cannot be used.
     """
 
-    def __init__(self, hidden: int, ffn: int, tokens: int, layers: int, init_std: float = 0.02, seed: int | None = None):
+    def __init__(self, hidden: int, ffn: int, tokens: int, layers: int, init_std: float = 0.02, seed: int | None = None, gather: str = "fused",
+                 wait_limit_ms: int = 0):
         from .. import core
         from ..ops import fused_gemm as fg
         self.npes, self.rank = core.n_pes(), core.my_pe()
@@ -62,21 +67,37 @@ class TensorParallelMLPStack:
         fl = ffn // self.npes
         self.w_up = [torch.empty(fl, hidden, device=dev, dtype=torch.float32).normal_(0.0, init_std, generator=gen).to(torch.bfloat16) for _ in range(layers)]
         self.w_down = [torch.empty(hidden, fl, device=dev, dtype=torch.float32).normal_(0.0, init_std, generator=gen).to(torch.bfloat16) for _ in range(layers)]
-        self.ag = fg.AllGatherGemm(tokens, hidden)
-        self.rs = fg.GemmReduceScatter(tokens, hidden, mode="rs")
+        if gather not in ("fused", "collective"):
+            raise ValueError("gather is 'fused' or 'collective'")
+        self.gather = gather if self.npes > 1 else "fused"
+        self._core, self._fg = core, fg
+        if self.gather == "fused":
+            self.ag = fg.AllGatherGemm(tokens, hidden, wait_limit_ms=wait_limit_ms)
+            self._shard = self.ag.shard
+        else:
+            self.ag = None
+            self.gathered = core.tensor((tokens, hidden), torch.bfloat16)
+            self._shard = core.tensor((tokens // self.npes, hidden), torch.bfloat16)
+        self.rs = fg.GemmReduceScatter(tokens, hidden, mode="rs", wait_limit_ms=wait_limit_ms)
         self.h = torch.empty(tokens, fl, dtype=torch.bfloat16, device=dev)
         self.out = torch.empty(tokens // self.npes, hidden, dtype=torch.bfloat16, device=dev)
-        self.kernels_per_forward = layers * (3 if self.npes > 1 else 2)  # GEMM, GEMM (+ the team sync before each all-gather)
+        # GEMM, GEMM (+ the team sync before each fused all-gather, or the fcollect kernel)
+        self.kernels_per_forward = layers * (3 if self.npes > 1 else 2)
 
     @property
     def input_shard(self) -> torch.Tensor:
-        return self.ag.shard
+        return self._shard
 
     @torch.no_grad()
     def forward(self) -> torch.Tensor:
         for l in range(self.layers):
-            self.ag(self.w_up[l], out=self.h, act="gelu_tanh")
-            self.rs(self.h, self.w_down[l], out=self.ag.shard if l + 1 < self.layers else self.out)
+            if self.gather == "fused":
+                self.ag(self.w_up[l], out=self.h, act="gelu_tanh")
+            else:
+                # fcollect ends with a team barrier, so the previous block's readers of `gathered` are done before it is rewritten
+                self._core.fcollect(self._core.Teams.TEAM_WORLD, self.gathered, self._shard, stream=torch.cuda.current_stream())
+                self._fg.gemm(self.gathered, self.w_up[l], out=self.h, act="gelu_tanh")
+            self.rs(self.h, self.w_down[l], out=self._shard if l + 1 < self.layers else self.out)
         return self.out
 
     __call__ = forward
@@ -91,5 +112,10 @@ class TensorParallelMLPStack:
         return x
 
     def close(self):
-        self.ag.close()
+        if self.ag is not None:
+            self.ag.close()
+        else:
+            torch.cuda.synchronize()
+            self._core.free_tensor(self.gathered)
+            self._core.free_tensor(self._shard)
         self.rs.close()

@@ -9,6 +9,7 @@ weighted sum for this rank's tokens.  ``payload="fp8"`` sends e4m3 with one fp32
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -25,7 +26,7 @@ class _DispatchArgs(C.Structure):
     _fields_ = [("T", C.c_int), ("H", C.c_int), ("K", C.c_int), ("E", C.c_int), ("rank", C.c_int), ("npes", C.c_int), ("payload", C.c_int), ("cap_rows", C.c_int),
                 ("epoch", C.c_uint64), ("wait_limit_ms", C.c_uint32), ("max_ctas", C.c_int), ("error_flag", C.c_void_p), ("x", C.c_void_p), ("topk_idx", C.c_void_p),
                 ("recv_x", C.c_void_p * MAX_PES), ("recv_scale", C.c_void_p * MAX_PES), ("slot_map", C.c_void_p), ("expert_offsets", C.c_void_p),
-                ("src_offsets", C.c_void_p), ("counts", C.c_void_p * MAX_PES), ("flags", C.c_void_p * MAX_PES), ("scratch", C.c_void_p)]
+                ("src_offsets", C.c_void_p), ("counts", C.c_void_p * MAX_PES), ("flags", C.c_void_p * MAX_PES), ("scratch", C.c_void_p), ("dup_src", C.c_void_p * MAX_PES)]
 
 
 class _CombineArgs(C.Structure):
@@ -48,7 +49,12 @@ def _lib():
 
 
 class MoeDispatchCombine:
-    def __init__(self, T: int, H: int, K: int, E: int, payload: str = "bf16", cap_rows: int | None = None, wait_limit_ms: int = 0):
+    """Expert-parallel dispatch and combine.  ``dedup=True`` (with more than one PE): a token that goes to several
+    experts of one PE crosses NVLink once and is replicated into its other rows by the receiving PE (with top-8 of 256
+    experts on 8 PEs a token reaches 5.25 distinct PEs on average, so about a third of the link bytes go away).  The
+    default is the per-pair form; ``BSHMEM_MOE_DEDUP=1`` turns the other one on for objects that do not say."""
+
+    def __init__(self, T: int, H: int, K: int, E: int, payload: str = "bf16", cap_rows: int | None = None, wait_limit_ms: int = 0, dedup: bool | None = None):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
@@ -68,6 +74,10 @@ class MoeDispatchCombine:
         self.recv_raw = alloc((self.cap_rows, row_bytes), torch.uint8)
         self.recv_scale = alloc((self.cap_rows, H // 128), torch.float32) if self.fp8 else None
         self.expert_out = alloc((self.cap_rows, H), torch.bfloat16)
+        if dedup is None:
+            dedup = os.environ.get("BSHMEM_MOE_DEDUP", "0") == "1"
+        self.dedup = bool(dedup) and sym
+        self.dup_src = alloc((self.cap_rows,), torch.int32) if self.dedup else None
         self.counts = alloc((self.npes * E,), torch.int32, True)
         self.flags = alloc((4 * self.npes,), torch.int64, True)
         self.scratch = torch.zeros(_lib().bshmem_moe_scratch_bytes(E) // 4 + 64, dtype=torch.int32, device=self.device)
@@ -75,10 +85,10 @@ class MoeDispatchCombine:
         self.expert_offsets = torch.zeros(self.EL + 1, dtype=torch.int32, device=self.device)
         self.src_offsets = torch.zeros(self.EL, self.npes, dtype=torch.int32, device=self.device)
         self.out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
-        self._tensors = [t for t in (self.recv_raw, self.recv_scale, self.expert_out, self.counts, self.flags) if t is not None]
+        self._tensors = [t for t in (self.recv_raw, self.recv_scale, self.expert_out, self.counts, self.flags, self.dup_src) if t is not None]
         ptr = (lambda t, q: core.peer_ptr(t, q)) if sym else (lambda t, q: t.data_ptr())
         self._peers = {q: {"recv": ptr(self.recv_raw, q), "scale": ptr(self.recv_scale, q) if self.fp8 else 0, "y": ptr(self.expert_out, q),
-                           "counts": ptr(self.counts, q), "flags": ptr(self.flags, q)} for q in range(self.npes)}
+                           "counts": ptr(self.counts, q), "flags": ptr(self.flags, q), "dup": ptr(self.dup_src, q) if self.dedup else 0} for q in range(self.npes)}
         if sym:
             core.barrier_all()
             torch.cuda.synchronize()
@@ -107,6 +117,7 @@ class MoeDispatchCombine:
         for q in range(self.npes):
             a.recv_x[q], a.recv_scale[q] = self._peers[q]["recv"], self._peers[q]["scale"]
             a.counts[q], a.flags[q] = self._peers[q]["counts"], self._peers[q]["flags"]
+            a.dup_src[q] = self._peers[q]["dup"]
         a.slot_map, a.expert_offsets, a.src_offsets = self.slot_map.data_ptr(), self.expert_offsets.data_ptr(), self.src_offsets.data_ptr()
         a.scratch = self.scratch.data_ptr()
         st = _lib().bshmem_moe_dispatch(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream))

@@ -2,7 +2,9 @@
 
 Default: 4096 tokens per rank, hidden 7168, 256 experts, top-8 from the softmax of N(0,1) logits; bf16 and fp8
 (e4m3 + 1x128 fp32 scales) dispatch, bf16 weighted combine.  Reports microseconds per layer and GB/s of payload
-that crosses NVLink (rows whose expert lives on another rank), and the fraction of 770 GB/s.
+that a pair-by-pair exchange moves over NVLink (rows whose expert lives on another rank), and the fraction of
+770 GB/s.  Dispatch runs twice: sending a token once per destination rank (the default; `sent_GB` is what then
+crosses the links) and once per (token, expert) pair.
 The baseline does what a framework without fused kernels does: sort pairs by destination, exchange counts,
 all_to_all_single the rows, and for combine the reverse plus an index_add of the weighted rows.
 
@@ -39,15 +41,22 @@ def main():
     idx = idx.to(torch.int32).contiguous()
     w = w.float().contiguous()
     remote_pairs = int(((idx // EL) != me).sum())
+    dest = (idx // EL).long()
+    reached = torch.zeros(T, n, dtype=torch.bool, device=env.dev).scatter_(1, dest, True)
+    reached[:, me] = False
+    remote_once = int(reached.sum())  # (token, remote rank) pairs: what crosses NVLink when a token is sent once per rank
     cap = int(T * K * 2.0) if n > 1 else T * K  # balanced routing: twice the mean is ample
-    for payload, row_bytes in (("bf16", 2 * H), ("fp8", H + H // 128 * 4)):
-        moe = MoeDispatchCombine(T, H, K, E, payload=payload, cap_rows=cap)
+    for payload, row_bytes, dedup in (("bf16", 2 * H, True), ("bf16", 2 * H, False), ("fp8", H + H // 128 * 4, True), ("fp8", H + H // 128 * 4, False)):
+        if n == 1 and not dedup:
+            continue
+        moe = MoeDispatchCombine(T, H, K, E, payload=payload, cap_rows=cap, dedup=dedup)
         ms = env.time_ms(lambda: moe.dispatch(x, idx), iters=args.iters, warmup=3)
         fg.check_errors()
         gb = remote_pairs * row_bytes / 1e9
-        env.record(test=f"moe_dispatch_{payload}", us=round(ms * 1e3, 1), nvlink_GB=round(gb, 4), GBps=round(gb / (ms * 1e-3), 1), fraction_of_770=round(gb / (ms * 1e-3) / 770, 3), npes=n,
-                   tokens=T, hidden=H, experts=E, topk=K)
-        if payload == "bf16":
+        sent = (remote_once if moe.dedup else remote_pairs) * row_bytes / 1e9
+        env.record(test=f"moe_dispatch_{payload}" + ("" if dedup else "_per_pair"), us=round(ms * 1e3, 1), nvlink_GB=round(gb, 4), GBps=round(gb / (ms * 1e-3), 1),
+                   fraction_of_770=round(gb / (ms * 1e-3) / 770, 3), sent_GB=round(sent, 4), sent_GBps=round(sent / (ms * 1e-3), 1), npes=n, tokens=T, hidden=H, experts=E, topk=K)
+        if payload == "bf16" and dedup:
             rows = int(moe.expert_offsets[-1])
             moe.expert_out[:rows] = moe.recv_x[:rows]
             ms = env.time_ms(lambda: moe.combine(idx, w), iters=args.iters, warmup=3)

@@ -1069,7 +1069,7 @@ def device_collectives_and_tiles():
     teardown(nv)
 
 
-def _moe_check(nv, payload, T, H, K, E, seed):
+def _moe_check(nv, payload, T, H, K, E, seed, dedup=False):
     """Dispatch + combine against a gather-based oracle; returns nothing, asserts."""
     from nvshmem_b200.ops.moe import MoeDispatchCombine
     from nvshmem_b200.ops import fused_gemm as fg
@@ -1083,7 +1083,8 @@ def _moe_check(nv, payload, T, H, K, E, seed):
     idx = idx.to(torch.int32).contiguous()
     idx[0, 0] = -1  # a dropped slot must be skipped everywhere
     w = w.float().contiguous()
-    moe = MoeDispatchCombine(T, H, K, E, payload=payload, wait_limit_ms=5000)
+    moe = MoeDispatchCombine(T, H, K, E, payload=payload, wait_limit_ms=5000, dedup=dedup)
+    assert moe.dedup == (dedup and n > 1)
     for it in range(2):
         recv, offs = moe.dispatch(x, idx)
         torch.cuda.synchronize()
@@ -1139,6 +1140,18 @@ def moe_dispatch_combine():
     _moe_check(nv, "bf16", T=512, H=1024, K=8, E=32 * n if n <= 4 else 256, seed=2)
     _moe_check(nv, "fp8", T=256, H=512, K=4, E=8 * n, seed=3)
     _moe_check(nv, "fp8", T=384, H=7168, K=8, E=16 * n, seed=4)
+    teardown(nv)
+
+
+@worker
+def moe_dispatch_once_per_pe():
+    """A token crosses NVLink once per destination PE and is replicated by the receiver; same oracle as above."""
+    nv = setup()
+    n = WORLD
+    _moe_check(nv, "bf16", T=64, H=256, K=4, E=2 * n, seed=11, dedup=True)   # two experts per PE, top-4: many repeats per PE
+    _moe_check(nv, "bf16", T=512, H=1024, K=8, E=32 * n if n <= 4 else 256, seed=12, dedup=True)
+    _moe_check(nv, "fp8", T=256, H=512, K=4, E=8 * n, seed=13, dedup=True)
+    _moe_check(nv, "fp8", T=384, H=7168, K=8, E=16 * n, seed=14, dedup=True)
     teardown(nv)
 
 
