@@ -409,8 +409,12 @@ int team_destroy(int handle) {
   for (int c : t->children) team_destroy(c);
   uint64_t sync, ll, scratch, ll128;
   team_sync_ptrs(r, handle, &sync, &ll, &scratch, &ll128);
-  local_zero((void*)sync, r.sync_bytes + r.ll_bytes);
-  if (r.ll128_bytes) local_zero((void*)ll128, r.ll128_bytes);
+  // The whole slot: sync flags, flag-in-data packets, both scratch halves (the recursive exchange keeps round flags
+  // there, compared against the team's generation, which restarts at zero for the slot's next team), LL128 lines.
+  local_zero((void*)sync, r.sync_bytes + r.ll_bytes + 2 * r.scratch_bytes + r.ll128_bytes);
+  (void)ll;
+  (void)scratch;
+  (void)ll128;
   local_zero(r.epochs_dev + (size_t)handle * 2 * BSHMEM_SYNC_SLOTS, sizeof(uint64_t) * 2 * BSHMEM_SYNC_SLOTS);
   bshmemi_team_t blank{};
   blank.my_pe = -1;

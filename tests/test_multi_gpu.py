@@ -1,8 +1,6 @@
 """Multi-PE tests on real GPUs: one child process per GPU (as many as the box has, up to 8), NCCL only for the
 test harness' own gathers.  NVLS is off unless a test is about it; the tests about it leave through the
 harness' soft exit (a failing rank detaches from the multicast objects before it goes)."""
-import os
-
 import pytest
 
 from tests._mp import run_workers
@@ -104,19 +102,8 @@ def test_moe_dispatch_combine():
 
 
 @need2
-@pytest.mark.skipif(os.environ.get("BSHMEM_TEST_NOT_YET_RUN") != "1", reason="the once-per-PE dispatch has not run on a GPU yet; BSHMEM_TEST_NOT_YET_RUN=1 includes it")
-def test_moe_dispatch_once_per_pe():
-    run_workers("moe_dispatch_once_per_pe", NG, gpu=True, env=NO_NVLS, timeout=600)
-
-
-@need2
 def test_tp_mlp_matches_single_device():
     run_workers("tp_mlp_matches_single_device", NG, gpu=True, env=NO_NVLS, timeout=600)
-
-
-@need2
-def test_device_api_wrappers_and_copy_engine_collectives():
-    run_workers("device_api_wrappers_and_copy_engine_collectives", NG, gpu=True, env=NO_NVLS, timeout=300)
 
 
 @need2

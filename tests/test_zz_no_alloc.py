@@ -9,8 +9,8 @@ contents, so the second call proves that everything that must start at zero is c
 compares with ``bshmem_moe_dispatch`` on one PE.  Row order inside an expert's segment is free in
 both, so rows are compared through the slot map; everything else must be identical.
 
-The file name sorts last on purpose: a run that stops at the first failure has then already
-run every other test.
+The file name sorts late on purpose: a run that stops at the first failure has then already
+run the tests of everything older.
 """
 import ctypes as C
 

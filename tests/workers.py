@@ -855,6 +855,52 @@ def _close(got, want, dtype):
 
 
 @worker
+def allreduce_recursive_exchange():
+    """Every member exchanges with log2(n) partners; teams of 3, 5, 6 or 7 members fold the members beyond the largest
+    power of two in first.  World team and, with four or more PEs, a three-member sub-team; called several times in a
+    row (the two scratch halves alternate).  Allocation and the oracle's gather involve every PE, the reduction only
+    the team's members."""
+    nv = setup()
+    n = WORLD
+    g = torch.Generator(device="cuda").manual_seed(17 + RANK)
+    teams = [(0, list(range(n)))]
+    sub = None
+    if n >= 4:
+        sub = nv.team_split_strided(0, 0, 1, 3)
+        teams.append((sub, [0, 1, 2]))
+    for team, members in teams:
+        member = RANK in members
+        for dtype, op in ((torch.float32, "sum"), (torch.int32, "max"), (torch.bfloat16, "sum"), (torch.float64, "prod"), (torch.int64, "xor")):
+            for count in (1, 7, 256, 1000, 4096):
+                src, dst, work = nv.tensor((count,), dtype), nv.tensor((count,), dtype), nv.tensor((count,), dtype)
+                for it in range(4):  # the last pass is in place
+                    if dtype.is_floating_point:
+                        scale = 1.0 if op != "prod" else 0.2
+                        src.copy_(((torch.rand(count, device="cuda", generator=g) * 2 - 1) * scale + (1.0 if op == "prod" else 0.0)).to(dtype))
+                    else:
+                        src.copy_(torch.randint(0, 1 << 12, (count,), device="cuda", generator=g).to(dtype))
+                    allsrc = _gather(src)
+                    want = _oracle(op, [allsrc[m] for m in members])
+                    dst.zero_()
+                    work.copy_(src)
+                    nv.barrier_all()
+                    if member:
+                        if it < 3:
+                            nv.reduce(team, dst, src, op, algo="recexch")
+                        else:
+                            nv.reduce(team, work, work, op, algo="recexch")
+                        torch.cuda.synchronize()
+                        got = dst if it < 3 else work
+                        assert _close(got, want, dtype), ("recexch", team != 0, dtype, op, count, it, (got.double() - want.double()).abs().max().item())
+                for t in (src, dst, work):
+                    nv.free_tensor(t)
+    if sub is not None and RANK in (0, 1, 2):
+        nv.team_destroy(sub)
+    assert nv.error_bits() == 0
+    teardown(nv)
+
+
+@worker
 def collectives_on_stream():
     nv = setup()
     n = WORLD
@@ -863,7 +909,7 @@ def collectives_on_stream():
     sizes = [1, 3, 8, 30, 255, 1022, 1024, 4097, 8190, 65536, 1 << 20]  # 30 floats: one 120-byte packet; 1022, 8190: a partly filled last packet
     cases = [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.float16, "max"), (torch.int32, "min"), (torch.int64, "xor"), (torch.float64, "prod"), (torch.uint8, "and"),
              (torch.int16, "or")]
-    red_algos = ["auto", "oneshot", "twoshot", "ll", "ll128", "recexch"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
+    red_algos = ["auto", "oneshot", "twoshot", "ll", "ll128"] + (["nvls_oneshot", "nvls_twoshot"] if nvls else [])
     for dtype, op in cases:
         for count in sizes:
             if dtype.is_floating_point:
