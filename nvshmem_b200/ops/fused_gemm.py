@@ -299,13 +299,14 @@ class AllGatherGemm:
     flight, the flags did not arrive within the wait limit; until that is understood it is an option, not the default.
     """
 
-    def __init__(self, M: int, K: int, wait_limit_ms: int = 0, copy_engine: bool | None = None):
+    def __init__(self, M: int, K: int, wait_limit_ms: int = 0, copy_engine: bool | None = None, max_ctas: int = 0):
         from .. import core
         self.core = core
         self.rank, self.npes = core.my_pe(), core.n_pes()
         if self.npes > MAX_PES:
             raise FusedGemmError(f"at most {MAX_PES} PEs")
         self.M, self.K, self.wait_limit_ms = M, K, wait_limit_ms
+        self.max_ctas = max_ctas  # 0: one CTA per SM; fewer leaves SMs to other work (every PE must pass the same value)
         self.rows = M // self.npes
         self.epoch = 0
         self.device = torch.device("cuda", torch.cuda.current_device())
@@ -344,7 +345,7 @@ class AllGatherGemm:
         a.act = ACTS[act]
         a.A, a.B, a.out = self.gathered.data_ptr(), w.data_ptr(), out.data_ptr()
         a.M, a.N, a.K, a.rank, a.npes, a.mode = self.M, N, self.K, self.rank, self.npes, MODES["ag"]
-        a.epoch, a.wait_limit_ms = self.epoch, self.wait_limit_ms
+        a.epoch, a.wait_limit_ms, a.max_ctas = self.epoch, self.wait_limit_ms, self.max_ctas
         a.error_flag = _error_flag(self.device).data_ptr()
         if self.npes > 1:
             a.ag_flags_local = self.flags.data_ptr()

@@ -1,6 +1,7 @@
 """Source compatibility: every function name that the reference's public headers declare (nvshmem.h + nvshmemx.h,
 macros expanded) is also declared by this library's headers.  Needs the reference's installed headers under
 baseline/_ref/include and nvcc; skipped where either is missing."""
+import os
 import re
 import shutil
 import subprocess
@@ -55,3 +56,33 @@ def test_python_layer_exports_the_reference_names():
     assert core is mine
     missing = [n for n in NVSHMEM4PY_NAMES if not hasattr(core, n)]
     assert not missing, missing
+
+
+def test_flat_bindings_export_the_reference_names():
+    """Every public name of the reference's pointer-level Python bindings (nvshmem4py/nvshmem/bindings/nvshmem.pyx:
+    `cpdef` functions, classes and enums) is reachable as ``nvshmem.bindings.<name>``.  The list is read from that
+    file's text when the reference tree is present, else the test checks the families by pattern."""
+    import re
+    import nvshmem.bindings as b
+    pyx = Path(os.environ.get("BSHMEM_REFERENCE_TREE", str(ROOT.parent / "reference"))) / "nvshmem4py" / "nvshmem" / "bindings" / "nvshmem.pyx"
+    if pyx.exists():
+        names = set(re.findall(r"^(?:cpdef|def)\s+(?:inline\s+)?(?:[\w\[\]]+\s+)??(\w+)\(", pyx.read_text(), flags=re.M))
+        names |= set(re.findall(r"^(?:cdef\s+)?class\s+(\w+)", pyx.read_text(), flags=re.M))
+        names = {n for n in names if not n.startswith("_")}
+        assert len(names) > 200, len(names)
+    else:
+        names = {f"{t}_{k}_on_stream" for t in ("float", "half", "bfloat16", "int32", "uint64", "size", "schar") for k in
+                 ("alltoall", "broadcast", "fcollect", "sum_reduce", "max_reduce", "min_reducescatter")} | {"malloc", "free", "ptr", "mc_ptr", "Team_id", "InitAttr"}
+    missing = sorted(n for n in names if not hasattr(b, n))
+    assert not missing, missing
+
+
+def test_reference_import_paths_name_the_same_modules():
+    """``nvshmem.<path>`` and ``nvshmem_b200.<path>`` are one module object each (one copy of the tracking state), and
+    the submodule paths of the reference package exist."""
+    import importlib
+    for path in ("core", "core.memory", "core.collective", "core.rma", "core.teams", "core.direct", "core.init_fini", "core.nvshmem_types", "core.interop.torch",
+                 "core.interop.cupy", "bindings", "bindings.nvshmem"):
+        assert importlib.import_module("nvshmem." + path) is importlib.import_module("nvshmem_b200." + path), path
+    from nvshmem.core.interop.torch import tensor, get_peer_tensor  # noqa: F401
+    from nvshmem.bindings import malloc, Team_id  # noqa: F401

@@ -54,3 +54,8 @@ def test_typed_host_api_all_types():
 def test_host_atomics_all_types():
     run_workers("host_atomics_all_types", 4)
 
+
+
+@pytest.mark.parametrize("n", [1, 3])
+def test_flat_bindings_on_host_heap(n):
+    run_workers("flat_bindings_on_host_heap", n)

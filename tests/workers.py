@@ -55,6 +55,82 @@ def gather_objects(obj):
 
 # ====================================================================== host-only (also valid on GPU)
 @worker
+def flat_bindings_on_host_heap():
+    """The pointer-level bindings (the reference package's ``nvshmem.bindings`` names) end to end on the host-memory
+    heap: unique-id initialisation through the attribute structs, allocation, peer pointers, a put with signal,
+    typed collectives, a team split, finalisation.  torch only carries the unique id between the processes."""
+    import ctypes as C
+    import numpy as np
+    import nvshmem.bindings as b
+    dist.init_process_group("gloo")
+    n, me = WORLD, RANK
+    assert b.init_status() == b.Init_status.STATUS_NOT_INITIALIZED
+    uid = b.UniqueId()
+    assert len(uid) == 1 and uid.version == (1 << 16) + 128 and int(uid) == uid.ptr
+    if me == 0:
+        b.get_uniqueid(uid.ptr)
+    raw = [bytes(uid._data.tobytes())]
+    dist.broadcast_object_list(raw, src=0)
+    uid = b.UniqueId.from_data(np.frombuffer(bytearray(raw[0]), dtype=b.uniqueid_dtype))
+    attr = b.InitAttr()
+    assert attr.version == (2 << 16) + 144
+    b.set_attr_uniqueid_args(me, n, uid, attr)
+    b.hostlib_init_attr(b.Flags.INIT_WITH_UNIQUEID, attr.ptr)
+    assert b.init_status() >= b.Init_status.STATUS_IS_INITIALIZED
+    assert (b.my_pe(), b.n_pes()) == (me, n) and b.team_n_pes(b.Team_id.TEAM_WORLD) == n
+    major, minor = C.c_int(-1), C.c_int(-1)
+    b.info_get_version(C.addressof(major), C.addressof(minor))
+    assert major.value >= 1 and minor.value >= 0
+    count = 1000
+    src, dst, sig = b.malloc(4 * count), b.calloc(count * n, 4), b.calloc(1, 8)
+    assert src and dst and sig and b.align(256, 1024) % 256 == 0
+    mine = np.ctypeslib.as_array(C.cast(src, C.POINTER(C.c_float)), shape=(count,))
+    out = np.ctypeslib.as_array(C.cast(dst, C.POINTER(C.c_float)), shape=(count * n,))
+    mine[:] = np.arange(count, dtype=np.float32) + 1000 * me
+    b.barrier_all()
+    # typed collectives (counts in elements)
+    b.float_sum_reduce_on_stream(b.Team_id.TEAM_WORLD, dst, src, count, 0)
+    assert np.allclose(out[:count], n * np.arange(count) + 1000 * sum(range(n)))
+    b.float_fcollect_on_stream(b.Team_id.TEAM_WORLD, dst, src, count, 0)
+    assert all(np.array_equal(out[p * count:(p + 1) * count], np.arange(count, dtype=np.float32) + 1000 * p) for p in range(n))
+    b.int32_broadcast_on_stream(b.Team_id.TEAM_WORLD, dst, src, count, n - 1, 0)
+    assert np.array_equal(out[:count], np.arange(count, dtype=np.float32) + 1000 * (n - 1))
+    try:
+        b.float_sum_reduce_on_stream(12345, dst, src, count, 0)  # no such team
+        raise AssertionError("a bad team handle must raise")
+    except b.NVSHMEMError as e:
+        assert e.status != 0
+    # put with signal to the right neighbour, peer pointer of the left one
+    right, left = (me + 1) % n, (me - 1) % n
+    b.barrier_all()
+    b.putmem_signal_on_stream(dst, src, 4 * count, sig, 7, b.Signal_op.SIGNAL_ADD, right, 0)
+    b.quiet_on_stream(0)
+    b.signal_wait_until_on_stream(sig, b.Cmp_type.CMP_GE, 7, 0)
+    assert np.array_equal(out[:count], np.arange(count, dtype=np.float32) + 1000 * left)
+    peer = b.ptr(src, left)
+    assert peer and np.ctypeslib.as_array(C.cast(peer, C.POINTER(C.c_float)), shape=(count,))[5] == 5 + 1000 * left
+    assert b.ptr(src, me) == src and b.mc_ptr(b.Team_id.TEAM_WORLD, src) == 0  # no multicast on host memory
+    # teams: the even PEs
+    cfg, new = b.TeamConfig(), C.c_int(-1)
+    assert cfg.version == (2 << 16) + 64
+    b.team_split_strided(b.Team_id.TEAM_WORLD, 0, 2, (n + 1) // 2, cfg.ptr, 0, C.addressof(new))
+    if me % 2 == 0:
+        assert new.value >= b.Team_id.TEAMS_MIN and b.team_my_pe(new.value) == me // 2
+        assert b.team_translate_pe(new.value, b.team_my_pe(new.value), b.Team_id.TEAM_WORLD) == me
+        b.barrier(new.value)
+        b.team_destroy(new.value)
+    else:
+        assert new.value == b.Team_id.TEAM_INVALID
+    b.barrier_all()
+    for p in (src, dst, sig):
+        b.free(p)
+    b.hostlib_finalize()
+    assert b.init_status() == b.Init_status.STATUS_NOT_INITIALIZED
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@worker
 def python_layer_on_host_heap():
     """The nvshmem4py-style layer end to end with no GPU: symmetric tensors over the host-memory heap, put / get /
     put-with-signal on a 'stream' (immediate on this back end), peer views, teams, tracked frees."""
