@@ -38,6 +38,17 @@ class UniqueId(C.Structure):
     def to_bytes(self) -> bytes:
         return bytes(C.string_at(C.addressof(self), C.sizeof(self)))
 
+    @property
+    def _data(self):
+        """The 128 bytes as a writable NumPy record array over this object's memory (no copy): programs written for
+        the reference package broadcast ``uid._data.view(numpy.int8)`` in place."""
+        import numpy as np
+        return np.frombuffer(self, dtype=np.dtype([("version", np.int32), ("internal", np.int8, (124,))], align=True), count=1).view(np.recarray)
+
+    @property
+    def ptr(self) -> int:
+        return C.addressof(self)
+
     @classmethod
     def from_bytes(cls, raw: bytes) -> "UniqueId":
         if len(raw) != UNIQUEID_BYTES:

@@ -38,6 +38,22 @@ def get_unique_id(empty: bool = False) -> H.UniqueId:
     return uid
 
 
+def _device_ordinal(device) -> int:
+    """CUDA ordinal of `device`: an int, a ``torch.device``, a ``cuda.core`` Device (``device_id``), a CuPy device
+    (``id``); -1 (the current device, or none with the host heap) for None and for a torch CPU device."""
+    if device is None:
+        return -1
+    if isinstance(device, int):
+        return device
+    if hasattr(device, "type"):  # torch.device
+        return device.index if device.type == "cuda" and device.index is not None else -1
+    for attr in ("device_id", "id", "index"):
+        v = getattr(device, attr, None)
+        if isinstance(v, int):
+            return v
+    return int(device)
+
+
 def _uid_via_torch(rank: int, group=None) -> H.UniqueId:
     import torch
     import torch.distributed as dist
@@ -68,11 +84,11 @@ def init(device=None, uid: H.UniqueId | bytes | None = None, rank: int | None = 
         uid = _uid_via_torch(rank)
     if isinstance(uid, (bytes, bytearray)):
         uid = H.UniqueId.from_bytes(bytes(uid))
+    elif not isinstance(uid, H.UniqueId) and hasattr(uid, "_data"):  # the struct wrapper of the pointer-level bindings
+        uid = H.UniqueId.from_bytes(uid._data.tobytes())
     if rank is None or nranks is None:
         raise NvshmemInvalid("rank and nranks are required with a unique id")
-    dev = -1
-    if device is not None:
-        dev = device.index if hasattr(device, "index") and device.index is not None else int(device) if not hasattr(device, "type") else -1
+    dev = _device_ordinal(device)
     st = lib.nvshmemx_b200_init_uid(C.byref(uid), int(rank), int(nranks), int(dev))
     if st != 0:
         raise NvshmemError(f"initialisation failed with status {st}")

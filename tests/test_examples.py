@@ -125,3 +125,19 @@ def test_bootstrap_plugin_collectives(tmp_path):
     status, outs = launch(4, [sys.executable, str(ROOT / "tests" / "plugin_child.py")], timeout=120, capture=True, env_extra=env)
     assert status == 0, outs
     assert "plugin collectives ok" in "".join(outs) and list(tmp_path.iterdir()) == []
+
+
+@pytest.mark.parametrize("script", ["init_fini.py", "on_stream.py"])
+def test_python_examples_run_on_the_host_heap(script):
+    """examples/python/init_fini.py (four ways to start and stop, one after the other in the same processes) and
+    on_stream.py as torchrun jobs of three processes with no GPU; they check their own results."""
+    import os
+    import subprocess
+    import sys
+    from tests._mp import free_port
+    env = dict(os.environ, NVSHMEM_HEAP_BACKEND="HOST", PYTHONPATH=str(ROOT), NVSHMEM_BOOTSTRAP_TIMEOUT_MS="30000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           str(ROOT / "examples" / "python" / script)]
+    res = subprocess.run(cmd, cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "WRONG" not in res.stdout and res.stdout.count(" ok") >= 3
