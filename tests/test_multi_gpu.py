@@ -112,7 +112,7 @@ def test_device_module_via_driver_api():
 
 
 @need2
-@pytest.mark.parametrize("script", ["torch_interop.py", "triton_interop.py", "tp_and_ep_blocks.py", "external_memory.py", "init_fini.py", "on_stream.py"])
+@pytest.mark.parametrize("script", ["torch_interop.py", "triton_interop.py", "tp_and_ep_blocks.py", "external_memory.py"])
 def test_python_examples_run_on_gpus(script):
     """The example programs under examples/python, each as a torchrun job on two GPUs; they check their own results."""
     import os
