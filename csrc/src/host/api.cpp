@@ -258,7 +258,12 @@ int nvshmemx_set_attr_uniqueid_args(int myrank, int nranks, const nvshmemx_uniqu
 }
 int nvshmemx_init_status(void) {
   int s = rt().init_status;
-  return s >= INIT_IS_INITIALIZED ? NVSHMEM_STATUS_IS_INITIALIZED : s == INIT_IS_BOOTSTRAPPED ? NVSHMEM_STATUS_IS_BOOTSTRAPPED : NVSHMEM_STATUS_NOT_INITIALIZED;
+  if (s >= INIT_IS_INITIALIZED) {
+    // Several PEs on one GPU are reported the way the reference reports them (reference: src/host/init/init.cu nvshmemx_init_status).
+    const int mpg = rt().mpg_status;
+    return mpg == MPG_FULL ? NVSHMEM_STATUS_FULL_MPG : mpg == MPG_LIMITED ? NVSHMEM_STATUS_LIMITED_MPG : NVSHMEM_STATUS_IS_INITIALIZED;
+  }
+  return s == INIT_IS_BOOTSTRAPPED ? NVSHMEM_STATUS_IS_BOOTSTRAPPED : NVSHMEM_STATUS_NOT_INITIALIZED;
 }
 void nvshmem_finalize(void) {
   std::lock_guard<std::mutex> lk(rt().mu);

@@ -196,6 +196,44 @@ void watchdog_stop(Runtime& r) {
 }
 
 // ------------------------------------------------------------------ init
+// Share of the GPU's SMs that an MPS server grants this process, in percent; -1 when no MPS server serves it.
+// A client of an MPS server sees the server's pipe directory (CUDA_MPS_PIPE_DIRECTORY, default /tmp/nvidia-mps) with
+// its control file; CUDA_MPS_ACTIVE_THREAD_PERCENTAGE narrows the share (100 when it is not set).
+// (reference: src/host/init/init.cu:724-947 decides LIMITED / FULL the same way: MPS present and the shares of the
+// PEs on a GPU sum to at most 100.)
+static int mps_share_of_this_process() {
+  const char* dir = getenv("CUDA_MPS_PIPE_DIRECTORY");
+  std::string control = std::string(dir && *dir ? dir : "/tmp/nvidia-mps") + "/control";
+  if (access(control.c_str(), F_OK) != 0) return -1;
+  const char* pct = getenv("CUDA_MPS_ACTIVE_THREAD_PERCENTAGE");
+  if (!pct || !*pct) return 100;
+  char* end = nullptr;
+  double v = strtod(pct, &end);
+  if (end == pct || v <= 0 || v > 100) return 100;
+  return (int)(v + 0.999);
+}
+
+// Counts the PEs that share this PE's GPU and decides what they may do together.
+static void classify_gpu_sharing(Runtime& r) {
+  const PeInfo& me = r.pe_info[r.mype];
+  int sharers = 0, share_sum = 0;
+  bool all_mps = true;
+  for (const PeInfo& p : r.pe_info) {
+    if (p.host_hash != me.host_hash || memcmp(p.uuid, me.uuid, sizeof(me.uuid)) != 0) continue;
+    ++sharers;
+    if (p.mps_percent < 0) all_mps = false;
+    else share_sum += p.mps_percent;
+  }
+  r.pes_on_my_gpu = sharers;
+  r.mpg_status = sharers <= 1 ? MPG_NONE : (all_mps && share_sum <= 100) ? MPG_FULL : MPG_LIMITED;
+  if (r.mpg_status == MPG_LIMITED)
+    WARN("%d PEs share the GPU of PE %d and nothing guarantees that their kernels run at the same time (no MPS server, or shares above 100%%): "
+               "host-initiated operations between them work; device code of one PE must not wait for device code of another "
+               "(barriers, collectives and signal waits inside kernels)", sharers, r.mype);
+  else if (r.mpg_status == MPG_FULL)
+    INFO(SUB_INIT, "%d PEs share the GPU of PE %d under an MPS server with %d%% of the SMs between them", sharers, r.mype, share_sum);
+}
+
 static void print_options_if_asked(const Runtime& r) {
   const Options& o = options();
   if (o.VERSION && r.mype == 0) printf("%s version %d.%d.%d\n", BSHMEM_VENDOR_STRING, BSHMEM_MAJOR, BSHMEM_MINOR, BSHMEM_PATCH);
@@ -284,9 +322,12 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   mine.host_hash = host_hash();
   strncpy(mine.pci_bus_id, r.topo.pci_bus_id.c_str(), sizeof(mine.pci_bus_id) - 1);
   if (r.topo.uuid.size() == 16) memcpy(mine.uuid, r.topo.uuid.data(), 16);
+  else if (!use_vmm && o.TEST_FAKE_GPU >= 0) snprintf(mine.uuid, sizeof(mine.uuid), "fakegpu-%ld", o.TEST_FAKE_GPU);
   else snprintf(mine.uuid, sizeof(mine.uuid), "host-%d", r.mype);
+  mine.mps_percent = mps_share_of_this_process();
   r.pe_info.resize(r.npes);
   if (r.boot.allgather(&mine, r.pe_info.data(), sizeof(PeInfo), &r.boot) != 0) return ST_INTERNAL;
+  classify_gpu_sharing(r);
   if (use_vmm) {
     build_reach_map(r);
     if (!r.topo.all_peers_ldst) {

@@ -33,7 +33,10 @@ enum Status {  // public nvshmemx_status values
   ST_INTERNAL = 7,
 };
 
-enum InitStatus { INIT_NOT_INITIALIZED = 0, INIT_IS_BOOTSTRAPPED = 1, INIT_IS_INITIALIZED = 2, INIT_LIMITED_MPG = 4, INIT_FULL_MPG = 8 };
+enum InitStatus { INIT_NOT_INITIALIZED = 0, INIT_IS_BOOTSTRAPPED = 1, INIT_IS_INITIALIZED = 2 };
+// Several PEs on one GPU: NONE (one PE per GPU), LIMITED (their kernels may not run at the same time, so device code of
+// one must not wait for device code of another), FULL (an MPS server gives each its own share of the SMs).
+enum MpgStatus { MPG_NONE = 0, MPG_LIMITED = 1, MPG_FULL = 2 };
 
 struct TopoRecord {
   int device = -1;
@@ -54,6 +57,8 @@ struct PeInfo {  // all-gathered at init
   uint64_t host_hash;
   char pci_bus_id[32];
   char uuid[16];
+  int32_t mps_percent;  // CUDA_MPS_ACTIVE_THREAD_PERCENTAGE of the process when an MPS server serves it, else -1
+  int32_t reserved;
 };
 
 struct bshmem_transport;
@@ -79,6 +84,8 @@ typedef void* (*StateAddrGetter)();
 struct Runtime {
   std::mutex mu;  // serialises public entry points (thread level SERIALIZED)
   int init_status = INIT_NOT_INITIALIZED;
+  int mpg_status = MPG_NONE;
+  int pes_on_my_gpu = 1;
   bool hostlib_only = false;
   bshmem_bootstrap_handle_t boot{};
   bool boot_live = false;

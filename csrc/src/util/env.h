@@ -41,6 +41,7 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug,
   X(DISABLE_CUDA_VMM,      bool,        Bool, false,            Memory,      "Refused on a GPU: the GPU heap needs CUDA virtual memory management (the cudaMalloc + IPC heap of the reference is not built); see NVSHMEM_HEAP_BACKEND") \
   X(REMOTE_TRANSPORT,      std::string, Str,  "none",           Transport,   "Name of a transport plugin (libbshmem_transport_<name>.so) to load beside the built-in load/store transport; none is shipped") \
   X(DISABLE_P2P,           bool,        Bool, false,            Hidden,      "Treat peers as not load/store reachable (init then fails: no remote transport is built)") \
+  X(TEST_FAKE_GPU,         long,        Long, -1,               Hidden,      "Host-memory heap only: this PE reports GPU <n> of its host as its device (tests of the same-GPU teams and of the several-PEs-per-GPU status)") \
   X(DISABLE_CE_COLLECTIVES,bool,        Bool, false,            Collectives, "Never use copy engines for on-stream alltoall/fcollect/broadcast") \
   X(CE_COLLECTIVES_MIN_BYTES, size_t,   Size, 0,                Collectives, "On-stream alltoall/fcollect/broadcast of at least this many bytes go through copy engines (0: never)") \
   X(MAX_TEAMS,             long,        Long, 128,              OpenShmem,   "Maximum number of simultaneous teams")                     \

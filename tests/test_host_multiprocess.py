@@ -59,3 +59,10 @@ def test_host_atomics_all_types():
 @pytest.mark.parametrize("n", [1, 3])
 def test_flat_bindings_on_host_heap(n):
     run_workers("flat_bindings_on_host_heap", n)
+
+
+@pytest.mark.parametrize("mode,n", [("none", 4), ("full", 4), ("over", 3)])
+def test_several_pes_per_gpu_status(mode, n):
+    """LIMITED without an MPS server or with shares above 100 %, FULL with an MPS server and shares that fit; the PE
+    that has a GPU to itself (n = 3) reports the ordinary status."""
+    run_workers("several_pes_per_gpu_status", n, env={"MPG_MODE": mode})

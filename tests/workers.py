@@ -131,6 +131,44 @@ def flat_bindings_on_host_heap():
 
 
 @worker
+def several_pes_per_gpu_status():
+    """Host-memory heap with a pretended GPU per PE (NVSHMEM_TEST_FAKE_GPU = rank // 2, set before init): the
+    same-GPU and GPU-leader teams and the LIMITED / FULL status.  MODE=none: no MPS pipe directory -> LIMITED;
+    MODE=full: a directory with a control file and 50 % each -> FULL; MODE=over: 60 % each -> LIMITED."""
+    import tempfile
+    mode = os.environ["MPG_MODE"]
+    os.environ["NVSHMEM_TEST_FAKE_GPU"] = str(RANK // 2)
+    tmp = tempfile.mkdtemp()
+    if mode == "none":
+        os.environ["CUDA_MPS_PIPE_DIRECTORY"] = os.path.join(tmp, "absent")
+    else:
+        open(os.path.join(tmp, "control"), "w").close()
+        os.environ["CUDA_MPS_PIPE_DIRECTORY"] = tmp
+        os.environ["CUDA_MPS_ACTIVE_THREAD_PERCENTAGE"] = "50" if mode == "full" else "60"
+    nv = setup()
+    n, me = nv.n_pes(), nv.my_pe()
+    sharers = 2 if (me // 2) * 2 + 1 < n else 1
+    want = 2 if sharers == 1 else (4 if mode == "full" else 3)  # IS_INITIALIZED, FULL_MPG, LIMITED_MPG
+    assert nv.init_status() == want, (me, nv.init_status(), want)
+    assert nv.team_n_pes(nv.Teams.TEAM_SAME_GPU) == sharers and nv.team_my_pe(nv.Teams.TEAM_SAME_GPU) == me % 2
+    leaders = (n + 1) // 2
+    if me % 2 == 0:
+        assert nv.team_n_pes(nv.Teams.TEAM_GPU_LEADERS) == leaders and nv.team_my_pe(nv.Teams.TEAM_GPU_LEADERS) == me // 2
+    # host-initiated traffic between PEs of one GPU works in every mode
+    x = nv.tensor((8,), torch.int64)
+    y = nv.tensor((8,), torch.int64, zero=True)
+    x.fill_(me + 1)
+    nv.barrier_all()
+    mate = me ^ 1 if (me ^ 1) < n else me
+    nv.put(y, x, mate)
+    nv.barrier_all()
+    assert int(y[0]) == mate + 1
+    nv.free_tensor(x)
+    nv.free_tensor(y)
+    teardown(nv)
+
+
+@worker
 def python_layer_on_host_heap():
     """The nvshmem4py-style layer end to end with no GPU: symmetric tensors over the host-memory heap, put / get /
     put-with-signal on a 'stream' (immediate on this back end), peer views, teams, tracked frees."""
