@@ -1,6 +1,6 @@
 """Multi-PE GPU tests of the parts that were written last: the MoE dispatch that sends a token once per destination
-PE, the recursive-exchange all-reduce, and one kernel that calls every queue-pair / sized / byte-collective wrapper
-together with the copy-engine collectives on several PEs.
+PE, the recursive-exchange all-reduce, one kernel that calls every queue-pair / sized / byte-collective wrapper
+together with the copy-engine collectives on several PEs, and two Python examples.
 
 The file name sorts last on purpose: a run that stops at the first failure has then already run every other test.
 """
