@@ -54,6 +54,38 @@ def _device_ordinal(device) -> int:
     return int(device)
 
 
+def _init_with_mpi(mpi_comm, dev: int) -> None:
+    """Initialises over MPI (the bootstrap plugin opens the MPI library that is in the process).  `mpi_comm` is an
+    mpi4py communicator, a ctypes object holding an ``MPI_Comm``, the integer address of one, or None for mpi4py's
+    ``COMM_WORLD`` (reference: nvshmem4py/nvshmem/core/init_fini.py, initializer_method="mpi")."""
+    from ..bindings import nvshmem as flat
+    keep = None
+    if mpi_comm is None:
+        try:
+            from mpi4py import MPI
+        except ImportError as e:
+            raise NvshmemInvalid("initializer_method='mpi' without a communicator needs mpi4py") from e
+        mpi_comm = MPI.COMM_WORLD
+    if isinstance(mpi_comm, int):
+        addr = mpi_comm
+    elif isinstance(mpi_comm, (C._SimpleCData, C.Structure)):
+        addr, keep = C.addressof(mpi_comm), mpi_comm
+    else:
+        try:
+            from mpi4py import MPI
+            addr, keep = MPI._addressof(mpi_comm), mpi_comm
+        except (ImportError, TypeError) as e:
+            raise NvshmemInvalid(f"cannot take the address of the MPI communicator in {type(mpi_comm).__name__}") from e
+    attr = flat.InitAttr()
+    flat.set_attr_mpi_comm_args(addr, attr.ptr)
+    attr._data["args"][0].view("int32")[8] = dev  # nvshmemx_init_args_t::cuda_device_id
+    try:
+        flat.hostlib_init_attr(flat.Flags.INIT_WITH_MPI_COMM, attr.ptr)
+    except flat.NVSHMEMError as e:
+        raise NvshmemError(f"initialisation over MPI failed with status {e.status}") from e
+    del keep
+
+
 def _uid_via_torch(rank: int, group=None) -> H.UniqueId:
     import torch
     import torch.distributed as dist
@@ -73,8 +105,13 @@ def init(device=None, uid: H.UniqueId | bytes | None = None, rank: int | None = 
     global _initialized
     if _initialized:
         return
-    if mpi_comm is not None or initializer_method in ("mpi", "emulated_mpi"):
-        raise NvshmemInvalid("the MPI bootstrap is not built; use initializer_method='uid' or 'torch'")
+    if initializer_method == "emulated_mpi":
+        raise NvshmemInvalid("initializer_method='emulated_mpi' is not offered; use 'mpi', 'uid' or 'torch'")
+    if mpi_comm is not None or initializer_method == "mpi":
+        _init_with_mpi(mpi_comm, _device_ordinal(device))
+        _initialized = True
+        atexit.register(finalize)
+        return
     lib = H.load()
     if initializer_method == "torch" or uid is None:
         import torch.distributed as dist

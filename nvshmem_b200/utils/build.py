@@ -5,6 +5,7 @@ Targets (all land in ``nvshmem_b200/lib``):
 * ``libbshmem_host.so``   – host library: bootstrap, heap, teams, host API, on-stream collectives
 * ``libbshmem_fused.so``  – fused tcgen05 GEMM + collective kernels and the MoE dispatch/combine kernels
 * ``libbshmem_devtest.so``– kernels that exercise the device API (used by the test-suite and perftest)
+* ``libbshmem_bootstrap_file.so`` / ``libbshmem_bootstrap_mpi.so`` – bootstrap plugins (file exchange; MPI, opened at run time)
 * ``nvshmem-info``        – prints version, build options and environment variables
 
 Objects are rebuilt when a source or any header is newer.  ``python -m
@@ -138,7 +139,8 @@ def build_sanitized(sanitize: str, jobs: int | None = None) -> dict[str, Path]:
     for name, srcs, out, libs in (
             ("host", _sources("util", "bootstrap", "heap", "team", "state", "transport", "host", "coll"), lib_dir / "libbshmem_host.so",
              ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
-            ("plugins", _sources("bootstrap_plugins"), lib_dir / "libbshmem_bootstrap_file.so", [])):
+            ("plugins", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_file.cpp"], lib_dir / "libbshmem_bootstrap_file.so", []),
+            ("plugin_mpi", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_mpi.cpp"], lib_dir / "libbshmem_bootstrap_mpi.so", ["-ldl"])):
         with ThreadPoolExecutor(jobs) as ex:
             objs = list(ex.map(lambda s: _compile(s, flags, False, hdr, obj_dir), srcs))
         _link(objs, out, True, libs + san)
@@ -155,7 +157,8 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
                  ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
         "fused": (_sources("fused"), LIB / "libbshmem_fused.so", True, ["-ldl"]),
         "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
-        "plugins": (_sources("bootstrap_plugins"), LIB / "libbshmem_bootstrap_file.so", True, []),
+        "plugins": ([CSRC / "src" / "bootstrap_plugins" / "bootstrap_file.cpp"], LIB / "libbshmem_bootstrap_file.so", True, []),
+        "plugin_mpi": ([CSRC / "src" / "bootstrap_plugins" / "bootstrap_mpi.cpp"], LIB / "libbshmem_bootstrap_mpi.so", True, ["-ldl"]),
         "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
     }
     built: dict[str, Path] = {}
