@@ -48,25 +48,27 @@ int bootstrap_plugin_init(const char* path, void* attr, bshmem_bootstrap_handle_
   return BOOT_OK;
 }
 
-int bootstrap_mpi_init(void* mpi_comm, bshmem_bootstrap_handle_t* handle) {
-  std::string p = options().BOOTSTRAP_MPI_PLUGIN;
+// A plugin that this library ships: `name` is a path, or a bare file name that sits in the directory of this library.
+static int shipped_plugin_init(std::string p, void* attr, bshmem_bootstrap_handle_t* handle) {
   if (p.find('/') == std::string::npos) {
-    // A bare file name: the plugin sits in the directory of this library.
     Dl_info info;
-    if (dladdr((void*)&bootstrap_mpi_init, &info) && info.dli_fname) {
+    if (dladdr((void*)&shipped_plugin_init, &info) && info.dli_fname) {
       std::string self = info.dli_fname;
       const size_t slash = self.rfind('/');
       if (slash != std::string::npos) p = self.substr(0, slash + 1) + p;
     }
   }
-  return bootstrap_plugin_init(p.c_str(), mpi_comm, handle);
+  return bootstrap_plugin_init(p.c_str(), attr, handle);
 }
+int bootstrap_mpi_init(void* mpi_comm, bshmem_bootstrap_handle_t* handle) { return shipped_plugin_init(options().BOOTSTRAP_MPI_PLUGIN, mpi_comm, handle); }
+int bootstrap_shmem_init(bshmem_bootstrap_handle_t* handle) { return shipped_plugin_init(options().BOOTSTRAP_SHMEM_PLUGIN, nullptr, handle); }
 
 int bootstrap_init(int mode, const bshmem_uniqueid_t* id, int rank, int nranks, bshmem_bootstrap_handle_t* handle) {
   memset(handle, 0, sizeof(*handle));
   int st;
   if (mode == BOOT_PLUGIN) st = bootstrap_plugin_init(nullptr, (void*)id, handle);
   else if (mode == BOOT_MPI) st = bootstrap_mpi_init((void*)id, handle);
+  else if (mode == BOOT_SHMEM) st = bootstrap_shmem_init(handle);
   else if (mode == BOOT_PMI) st = bootstrap_pmi_init(handle);
   else st = bootstrap_uid_init(id, rank, nranks, handle);
   if (st != BOOT_OK) return st;

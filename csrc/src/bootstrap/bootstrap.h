@@ -41,7 +41,7 @@ typedef int (*bshmem_bootstrap_plugin_init_fn)(void* attr, bshmem_bootstrap_hand
 
 namespace bshmem {
 
-enum BootstrapMode { BOOT_UID = 0, BOOT_PLUGIN = 1, BOOT_PMI = 2, BOOT_MPI = 3 };
+enum BootstrapMode { BOOT_UID = 0, BOOT_PLUGIN = 1, BOOT_PMI = 2, BOOT_MPI = 3, BOOT_SHMEM = 4 };
 
 enum BootstrapStatus {
   BOOT_OK = 0,
@@ -69,6 +69,8 @@ int bootstrap_plugin_init(const char* path, void* attr, bshmem_bootstrap_handle_
 // The MPI bootstrap is a plugin that this library ships (NVSHMEM_BOOTSTRAP_MPI_PLUGIN, looked for beside the host
 // library); `mpi_comm` points at the MPI_Comm to duplicate, or is null for MPI_COMM_WORLD.
 int bootstrap_mpi_init(void* mpi_comm, bshmem_bootstrap_handle_t* handle);
+// The OpenSHMEM bootstrap, shipped the same way (NVSHMEM_BOOTSTRAP_SHMEM_PLUGIN).
+int bootstrap_shmem_init(bshmem_bootstrap_handle_t* handle);
 // Chooses the mode from NVSHMEM_BOOTSTRAP and initialises `handle`.  With BOOT_PLUGIN and BOOT_MPI `id` carries the
 // plugin's attribute (for MPI: the address of the communicator, or null).
 int bootstrap_init(int mode, const bshmem_uniqueid_t* id, int rank, int nranks, bshmem_bootstrap_handle_t* handle);

@@ -182,10 +182,7 @@ int do_init(unsigned int flags, nvshmemx_init_attr_t* attr, bool hostlib_only) {
   std::transform(mode.begin(), mode.end(), mode.begin(), ::toupper);
   int device = -1;
   if (attr && (attr->version >> 16) >= 2) device = attr->args.cuda_device_id;
-  if (flags & NVSHMEMX_INIT_WITH_SHMEM) {
-    ERROR_PRINT("the OpenSHMEM bootstrap is not built; use the unique-id, PMI or MPI bootstrap, or a plugin");
-    return NVSHMEMX_ERROR_NOT_SUPPORTED;
-  }
+  if (flags & NVSHMEMX_INIT_WITH_SHMEM) return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_SHMEM);  // the program has initialised OpenSHMEM
   if (flags & NVSHMEMX_INIT_WITH_MPI_COMM) {
     if (!attr || !attr->mpi_comm) return NVSHMEMX_ERROR_INVALID_VALUE;  // mpi_comm points at the caller's MPI_Comm
     return runtime_init((const bshmem_uniqueid_t*)attr->mpi_comm, 0, 1, device, hostlib_only, BOOT_MPI);
@@ -196,6 +193,7 @@ int do_init(unsigned int flags, nvshmemx_init_attr_t* attr, bool hostlib_only) {
   }
   if (mode == "PLUGIN") return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_PLUGIN);
   if (mode == "MPI") return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_MPI);
+  if (mode == "SHMEM") return runtime_init(nullptr, 0, 1, device, hostlib_only, BOOT_SHMEM);
   // Started by a PMI process manager (mpiexec / nvshmrun / srun): asked for by name, or recognised by the
   // manager's variables when nothing names a rank for the unique-id bootstrap.
   if (mode == "PMI" || (bootstrap_pmi_available() && !getenv("RANK") && !getenv("NVSHMEM_BOOTSTRAP_UID_RANK")))

@@ -29,10 +29,11 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug,
   X(DEBUG_FILE,            std::string, Str,  "",               Debug,       "Log file name; %h expands to the host name and %p to the pid") \
   X(ENABLE_ERROR_CHECKS,   bool,        Bool, false,            Debug,       "Check symmetry of collective allocation calls")             \
   X(NVTX,                  std::string, Str,  "off",            Debug,       "Comma list of NVTX range groups (off, common, all, init, alloc, launch, coll, wait, memorder, rma, atomic)") \
-  X(BOOTSTRAP,             std::string, Str,  "UID",            Bootstrap,   "Bootstrap used by nvshmem_init: UID, PMI, MPI or PLUGIN")             \
+  X(BOOTSTRAP,             std::string, Str,  "UID",            Bootstrap,   "Bootstrap used by nvshmem_init: UID, PMI, MPI, SHMEM or PLUGIN")             \
   X(BOOTSTRAP_PMI,         std::string, Str,  "PMI",            Bootstrap,   "PMI flavour spoken with the process manager: PMI (PMI-1) or PMI-2") \
   X(BOOTSTRAP_PLUGIN,      std::string, Str,  "",               Bootstrap,   "Path of a bootstrap plugin shared object")                  \
   X(BOOTSTRAP_MPI_PLUGIN,  std::string, Str,  "libbshmem_bootstrap_mpi.so", Bootstrap, "MPI bootstrap plugin: a path, or a file name beside the host library (the plugin opens the job's MPI library itself: NVSHMEM_BOOTSTRAP_MPI_LIB)") \
+  X(BOOTSTRAP_SHMEM_PLUGIN, std::string, Str, "libbshmem_bootstrap_shmem.so", Bootstrap, "OpenSHMEM bootstrap plugin: a path, or a file name beside the host library (the plugin finds the OpenSHMEM library itself: NVSHMEM_BOOTSTRAP_SHMEM_LIB; NVSHMEM_BOOTSTRAP_SHMEM_INIT=1 lets it call shmem_init)") \
   X(BOOTSTRAP_UID_SOCK_IFNAME, std::string, Str, "",            Bootstrap,   "Network interface for the UID bootstrap (prefix match; ^ excludes, = exact)") \
   X(BOOTSTRAP_UID_SOCK_FAMILY, std::string, Str, "AF_INET",     Bootstrap,   "Address family for the UID bootstrap: AF_INET or AF_INET6")  \
   X(BOOTSTRAP_UID_SESSION_ID,  std::string, Str, "",            Bootstrap,   "Fixed <address>:<port> of the UID root, replacing the unique-id exchange") \

@@ -5,7 +5,7 @@ Targets (all land in ``nvshmem_b200/lib``):
 * ``libbshmem_host.so``   – host library: bootstrap, heap, teams, host API, on-stream collectives
 * ``libbshmem_fused.so``  – fused tcgen05 GEMM + collective kernels and the MoE dispatch/combine kernels
 * ``libbshmem_devtest.so``– kernels that exercise the device API (used by the test-suite and perftest)
-* ``libbshmem_bootstrap_file.so`` / ``libbshmem_bootstrap_mpi.so`` – bootstrap plugins (file exchange; MPI, opened at run time)
+* ``libbshmem_bootstrap_file.so`` / ``_mpi.so`` / ``_shmem.so`` – bootstrap plugins (file exchange; MPI and OpenSHMEM, opened at run time)
 * ``nvshmem-info``        – prints version, build options and environment variables
 
 Objects are rebuilt when a source or any header is newer.  ``python -m
@@ -140,7 +140,8 @@ def build_sanitized(sanitize: str, jobs: int | None = None) -> dict[str, Path]:
             ("host", _sources("util", "bootstrap", "heap", "team", "state", "transport", "host", "coll"), lib_dir / "libbshmem_host.so",
              ["-ldl", "-lpthread", "-lrt", "-Xlinker", f"--version-script={CSRC / 'bshmem_host.sym'}"]),
             ("plugins", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_file.cpp"], lib_dir / "libbshmem_bootstrap_file.so", []),
-            ("plugin_mpi", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_mpi.cpp"], lib_dir / "libbshmem_bootstrap_mpi.so", ["-ldl"])):
+            ("plugin_mpi", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_mpi.cpp"], lib_dir / "libbshmem_bootstrap_mpi.so", ["-ldl"]),
+            ("plugin_shmem", [CSRC / "src" / "bootstrap_plugins" / "bootstrap_shmem.cpp"], lib_dir / "libbshmem_bootstrap_shmem.so", ["-ldl"])):
         with ThreadPoolExecutor(jobs) as ex:
             objs = list(ex.map(lambda s: _compile(s, flags, False, hdr, obj_dir), srcs))
         _link(objs, out, True, libs + san)
@@ -159,6 +160,7 @@ def build_all(verbose: bool = False, jobs: int | None = None, only: str | None =
         "devtest": (_sources("devtest"), LIB / "libbshmem_devtest.so", True, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
         "plugins": ([CSRC / "src" / "bootstrap_plugins" / "bootstrap_file.cpp"], LIB / "libbshmem_bootstrap_file.so", True, []),
         "plugin_mpi": ([CSRC / "src" / "bootstrap_plugins" / "bootstrap_mpi.cpp"], LIB / "libbshmem_bootstrap_mpi.so", True, ["-ldl"]),
+        "plugin_shmem": ([CSRC / "src" / "bootstrap_plugins" / "bootstrap_shmem.cpp"], LIB / "libbshmem_bootstrap_shmem.so", True, ["-ldl"]),
         "info": (_sources("tools"), LIB / "nvshmem-info", False, ["-L", str(LIB), "-lbshmem_host", "-Xlinker", "-rpath=$ORIGIN"]),
     }
     built: dict[str, Path] = {}

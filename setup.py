@@ -18,7 +18,7 @@ class BuildWithNative(build_py):
         import sys
         sys.path.insert(0, str(ROOT))
         from nvshmem_b200.utils.build import build_all
-        for name in ("host", "fused", "devtest", "plugins", "plugin_mpi", "info"):
+        for name in ("host", "fused", "devtest", "plugins", "plugin_mpi", "plugin_shmem", "info"):
             build_all(only=name)
         dst = ROOT / "nvshmem_b200" / "include"
         if dst.exists():

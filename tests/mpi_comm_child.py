@@ -1,4 +1,4 @@
-"""Child of tests/test_mpi_bootstrap.py: a program that has initialised MPI itself hands its communicator to the
+"""Child of tests/test_mpi_shmem_bootstrap.py: a program that has initialised MPI itself hands its communicator to the
 library (NVSHMEMX_INIT_WITH_MPI_COMM through the pointer-level bindings), works on the host-memory heap, and
 finalises MPI itself afterwards.  The MPI library is the stand-in built from tests/data/fake_mpi.c."""
 import ctypes as C

@@ -1,7 +1,8 @@
-"""The MPI bootstrap plugin on CPU.  No MPI installation exists here, so the tests build a stand-in MPI library
-(tests/data/fake_mpi.c: the entry points the plugin uses, over files) once with each of the two binary interfaces
-that the plugin speaks (integer handles of the MPICH family, pointer handles of Open MPI).  The stand-in aborts on
-a handle that does not belong to its interface, so a mix-up fails the test."""
+"""The MPI and OpenSHMEM bootstrap plugins on CPU.  Neither is installed here, so the tests build stand-ins:
+tests/data/fake_mpi.c (the entry points the MPI plugin uses, over files), once with each of the two binary
+interfaces that the plugin speaks (integer handles of the MPICH family, pointer handles of Open MPI; the stand-in
+aborts on a handle that does not belong to its interface, so a mix-up fails the test), and tests/data/fake_shmem.c
+(symmetric heaps as shared file mappings)."""
 import shutil
 import subprocess
 import sys
@@ -72,3 +73,47 @@ def test_mpi_bootstrap_without_an_mpi_library_says_so(tmp_path):
     env = {"NVSHMEM_BOOTSTRAP": "MPI", "NVSHMEM_BOOTSTRAP_MPI_LIB": str(tmp_path / "no_such_libmpi.so"), "NVSHMEM_HEAP_BACKEND": "HOST", "PYTHONPATH": str(ROOT)}
     status, outs = launch(1, [sys.executable, "-m", "perftest.plumbing"], timeout=60, capture=True, env_extra=env)
     assert status != 0 and "NVSHMEM_BOOTSTRAP_MPI_LIB" in "".join(outs)
+
+
+# ---------------------------------------------------------------------------------------------- OpenSHMEM
+@pytest.fixture(scope="module")
+def fake_shmem(tmp_path_factory):
+    so = tmp_path_factory.mktemp("fake_shmem") / "liboshmem_fake.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-w", "-o", str(so), str(ROOT / "tests" / "data" / "fake_shmem.c")], check=True)
+    return so
+
+
+def _shmem_plugin():
+    from nvshmem_b200.bindings import host as H
+    p = H.lib_path("libbshmem_bootstrap_shmem.so")
+    assert p.exists(), "python -m nvshmem_b200.utils.build --only=plugin_shmem"
+    return p
+
+
+def test_shmem_plugin_collectives(fake_shmem, tmp_path):
+    """allgather / alltoall / barrier with odd and large sizes over puts and barriers of the OpenSHMEM library, which
+    the plugin opens and therefore initialises and finalises itself."""
+    from nvshmem_b200.launch import launch
+    env = {"NVSHMEM_BOOTSTRAP_PLUGIN": str(_shmem_plugin()), "NVSHMEM_BOOTSTRAP_SHMEM_LIB": str(fake_shmem), "FAKE_SHMEM_DIR": str(tmp_path)}
+    status, outs = launch(4, [sys.executable, str(ROOT / "tests" / "plugin_child.py")], timeout=120, capture=True, env_extra=env)
+    assert status == 0, outs
+    assert "plugin collectives ok" in "".join(outs)
+    assert len(list(tmp_path.glob("finalized.*"))) == 4
+
+
+def test_shmem_bootstrap_carries_a_job(fake_shmem, tmp_path):
+    from nvshmem_b200.launch import launch
+    env = {"NVSHMEM_BOOTSTRAP": "SHMEM", "NVSHMEM_BOOTSTRAP_SHMEM_LIB": str(fake_shmem), "FAKE_SHMEM_DIR": str(tmp_path), "NVSHMEM_HEAP_BACKEND": "HOST",
+           "PYTHONPATH": str(ROOT)}
+    status, outs = launch(3, [sys.executable, "-m", "perftest.plumbing"], timeout=120, capture=True, env_extra=env)
+    assert status == 0, outs
+    assert '"offsets_identical": true' in "".join(outs)
+
+
+def test_init_beside_the_programs_openshmem(fake_shmem, tmp_path):
+    """NVSHMEMX_INIT_WITH_SHMEM: the program has initialised OpenSHMEM; the bootstrap uses it and leaves it running."""
+    from nvshmem_b200.launch import launch
+    env = {"FAKE_SHMEM_LIB": str(fake_shmem), "FAKE_SHMEM_DIR": str(tmp_path), "NVSHMEM_HEAP_BACKEND": "HOST", "PYTHONPATH": str(ROOT)}
+    status, outs = launch(3, [sys.executable, str(ROOT / "tests" / "shmem_child.py")], timeout=120, capture=True, env_extra=env)
+    assert status == 0, outs
+    assert "".join(outs).count("init beside the program's OpenSHMEM ok") == 3
