@@ -32,15 +32,16 @@ def test_moe_dispatch_once_per_pe():
 
 
 @need2
-@pytest.mark.parametrize("script", ["on_stream.py", "init_fini.py"])
+@pytest.mark.parametrize("script", ["on_stream.py", "init_fini.py", "triton_device_api.py"])
 def test_late_python_examples_run_on_gpus(script):
-    """examples/python/on_stream.py and init_fini.py (which starts and stops the library four times in one process) as
-    torchrun jobs on two GPUs; they check their own results.  Both run on the host heap in the CPU suite."""
+    """examples/python/on_stream.py, init_fini.py (which starts and stops the library four times in one process) and
+    triton_device_api.py (Triton kernels that signal and wait by themselves) as torchrun jobs on two GPUs; they check
+    their own results.  The first two also run on the host heap in the CPU suite; the third compiles there."""
     import os
     import subprocess
     import sys
     from tests._mp import ROOT, free_port
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NVSHMEM_DISABLE_NVLS="1", NVSHMEM_WAIT_TIMEOUT_MS="5000", PYTHONPATH=ROOT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NVSHMEM_DISABLE_NVLS="1", NVSHMEM_WAIT_TIMEOUT_MS="5000", PYTHONPATH=ROOT)  # no multicast: plain peer stores only
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "examples", "python", script)]
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
