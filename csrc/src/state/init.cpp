@@ -225,7 +225,8 @@ static void classify_gpu_sharing(Runtime& r) {
     else share_sum += p.mps_percent;
   }
   r.pes_on_my_gpu = sharers;
-  r.mpg_status = sharers <= 1 ? MPG_NONE : (all_mps && share_sum <= 100) ? MPG_FULL : MPG_LIMITED;
+  const bool shares_fit = share_sum <= 100 || options().IGNORE_CUDA_MPS_ACTIVE_THREAD_PERCENTAGE;
+  r.mpg_status = sharers <= 1 ? MPG_NONE : (all_mps && shares_fit) ? MPG_FULL : MPG_LIMITED;
   if (r.mpg_status == MPG_LIMITED)
     WARN("%d PEs share the GPU of PE %d and nothing guarantees that their kernels run at the same time (no MPS server, or shares above 100%%): "
                "host-initiated operations between them work; device code of one PE must not wait for device code of another "
@@ -260,6 +261,19 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   nvtx_init();
   const Options& o = options();
   r.hostlib_only = hostlib_only;
+  if (o.DEBUG_ATTACH_DELAY > 0) {
+    fprintf(stderr, "bshmem: pid %d waits %ld s for a debugger (NVSHMEM_DEBUG_ATTACH_DELAY)\n", (int)getpid(), o.DEBUG_ATTACH_DELAY);
+    sleep((unsigned)o.DEBUG_ATTACH_DELAY);
+  }
+  {
+    std::string kind = o.HEAP_KIND;
+    std::transform(kind.begin(), kind.end(), kind.begin(), ::toupper);
+    if (kind != "VIDMEM") {
+      ERROR_PRINT("NVSHMEM_HEAP_KIND=%s: only VIDMEM is built (a heap in pinned host memory is not); NVSHMEM_HEAP_BACKEND=HOST gives a host-memory heap for runs without a GPU",
+                  o.HEAP_KIND.c_str());
+      return ST_NOT_SUPPORTED;
+    }
+  }
 
   int st = bootstrap_init(boot_mode, id, rank, nranks, &r.boot);
   if (st != BOOT_OK) {
@@ -312,6 +326,8 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
       return ST_GPU_NOT_SELECTED;
     }
     log_set_device(r.device);
+    if (o.CUDA_LIMIT_STACK_SIZE > 0 && cudaDeviceSetLimit(cudaLimitStackSize, o.CUDA_LIMIT_STACK_SIZE) != cudaSuccess)
+      WARN("NVSHMEM_CUDA_LIMIT_STACK_SIZE=%zu was refused by the CUDA runtime", o.CUDA_LIMIT_STACK_SIZE);
     if (probe_topology(r) != ST_SUCCESS) return ST_INTERNAL;
   }
 
@@ -362,7 +378,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
     int least = 0, greatest = 0;
     cudaDeviceGetStreamPriorityRange(&least, &greatest);
     cudaStreamCreateWithPriority(&r.stream, cudaStreamNonBlocking, greatest);
-    r.peer_streams.resize(std::min(r.npes, 8));
+    r.peer_streams.resize((size_t)std::max<long>(1, std::min<long>(r.npes, o.MAX_PEER_STREAMS)));
     for (auto& s : r.peer_streams) cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
     r.peer_stream_used.assign(r.peer_streams.size(), false);
     cudaEventCreateWithFlags(&r.ev_a, cudaEventDisableTiming);
@@ -399,7 +415,7 @@ int runtime_init(const bshmem_uniqueid_t* id, int rank, int nranks, int device_h
   d.reduce_nvls_threshold = o.REDUCE_NVLS_THRESHOLD;
   d.reduce_oneshot_threshold = o.REDUCE_ONESHOT_THRESHOLD;
   d.fcollect_ll_threshold = o.FCOLLECT_LL_THRESHOLD;
-  d.ll128_threshold = o.LL128_THRESHOLD;
+  d.ll128_threshold = o.FCOLLECT_LL128_THRESHOLD_set ? o.FCOLLECT_LL128_THRESHOLD : o.LL128_THRESHOLD;
   d.fcollect_nvls_threshold = o.FCOLLECT_NVLS_THRESHOLD;
   d.reducescatter_nvls_threshold = o.REDUCESCATTER_NVLS_THRESHOLD;
 

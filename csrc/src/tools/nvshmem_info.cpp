@@ -24,6 +24,7 @@ static const char* cat_name(OptCat c) {
     case OptCat::Memory: return "Memory options";
     case OptCat::Transport: return "Transport options";
     case OptCat::Debug: return "Debugging options";
+    case OptCat::Accepted: return "Options of the reference that are accepted and change nothing here";
     default: return "Hidden options";
   }
 }

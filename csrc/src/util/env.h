@@ -15,7 +15,7 @@
 namespace bshmem {
 
 enum class OptKind { Bool, Long, Size, Str };
-enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug, Hidden };
+enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug, Accepted, Hidden };
 
 // clang-format off
 // X(name, ctype, kind, default, category, help)
@@ -72,7 +72,30 @@ enum class OptCat { OpenShmem, Bootstrap, Collectives, Memory, Transport, Debug,
   X(BCAST_TREE_KVAL,       long,        Long, 2,                Collectives, "Radix of the broadcast tree when peers are not all load/store reachable") \
   X(WAIT_TIMEOUT_MS,       long,        Long, 30000,            Debug,       "Milliseconds a device-side wait may spin before it records a timeout and returns") \
   X(DISABLE_WATCHDOG,      bool,        Bool, false,            Hidden,      "Do not start the host thread that services device-side global_exit and time-outs") \
-  X(WATCHDOG_ABORT,        bool,        Bool, false,            Debug,       "Let the watchdog end the process when a device wait times out (default: report only)")
+  X(WATCHDOG_ABORT,        bool,        Bool, false,            Debug,       "Let the watchdog end the process when a device wait times out (default: report only)") \
+  X(DEBUG_ATTACH_DELAY,    long,        Long, 0,                Debug,       "Seconds every PE sleeps at the start of initialisation (prints its pid first) so that a debugger can attach") \
+  X(CUDA_LIMIT_STACK_SIZE, size_t,      Size, 0,                Debug,       "Per-thread stack size of GPU threads set at initialisation (cudaLimitStackSize); 0 leaves the CUDA default") \
+  X(MAX_PEER_STREAMS,      long,        Long, 8,                Transport,   "Internal streams for non-blocking host-initiated copies to different peers (at most one per PE)") \
+  X(IGNORE_CUDA_MPS_ACTIVE_THREAD_PERCENTAGE, bool, Bool, false, OpenShmem,  "Several PEs on one GPU under an MPS server: report NVSHMEM_STATUS_FULL_MPG even when their shares of the SMs exceed 100%") \
+  X(FCOLLECT_LL128_THRESHOLD, size_t,   Size, 0,                Collectives, "The reference's name for the LL128 limit of fcollect: when set it replaces NVSHMEM_LL128_THRESHOLD (one limit serves fcollect, allreduce and broadcast here)") \
+  X(HEAP_KIND,             std::string, Str,  "VIDMEM",         Memory,      "VIDMEM (GPU memory).  SYSMEM (a heap in pinned host memory) is not built and is refused") \
+  X(ENABLE_ALIGNED_MALLOC, bool,        Bool, false,            Accepted,    "No effect: every symmetric allocation is already aligned to 512 bytes")   \
+  X(REDUCE_RECEXCH_KVAL,   long,        Long, 2,                Accepted,    "No effect: the recursive-exchange all-reduce always pairs PEs (radix 2)") \
+  X(REDMAXLOC_ALGO,        long,        Long, 0,                Accepted,    "No effect: the max-location reduction has one algorithm")           \
+  X(ASSERT_ATOMICS_SYNC,   bool,        Bool, false,            Accepted,    "No effect: atomics to load/store peers need no proxy synchronisation") \
+  X(BOOTSTRAP_TWO_STAGE,   bool,        Bool, false,            Accepted,    "No effect: the bootstraps here are single stage")                   \
+  X(BYPASS_ACCESSIBILITY_CHECK, bool,   Bool, false,            Accepted,    "No effect: symmetric-address checks are governed by NVSHMEM_ENABLE_ERROR_CHECKS") \
+  X(BYPASS_FLUSH,          bool,        Bool, false,            Accepted,    "No effect: no network transport, nothing to flush")                 \
+  X(CUDA_PATH,             std::string, Str,  "",               Accepted,    "No effect: the CUDA driver is found through the dynamic loader")    \
+  X(DISABLE_LOCAL_ONLY_PROXY, bool,     Bool, false,            Accepted,    "No effect: there is no proxy thread (a watchdog serves global exit and time-outs)") \
+  X(DISABLE_MNNVL,         bool,        Bool, false,            Accepted,    "No effect: one node; multi-node NVLink handles are not used")       \
+  X(DISABLE_NCCL,          bool,        Bool, false,            Accepted,    "No effect: collectives never go through NCCL")                      \
+  X(DISABLE_NVLS_SHARING,  bool,        Bool, false,            Accepted,    "No effect: every team window is its own multicast object")          \
+  X(DISABLE_SELF_WRITE_CE_COLL, bool,   Bool, false,            Accepted,    "No effect: copy-engine collectives always copy the PE's own part too") \
+  X(ENABLE_NIC_PE_MAPPING, bool,        Bool, false,            Accepted,    "No effect: no network transport")                                   \
+  X(ENABLE_RAIL_OPT,       bool,        Bool, false,            Accepted,    "No effect: no network transport")                                   \
+  X(IB_ENABLE_IBGDA,       bool,        Bool, false,            Accepted,    "No effect: no network transport")                                   \
+  X(PROXY_REQUEST_BATCH_MAX, long,      Long, 32,               Accepted,    "No effect: there is no proxy thread")
 // clang-format on
 
 struct Options {

@@ -86,3 +86,20 @@ def test_reference_import_paths_name_the_same_modules():
         assert importlib.import_module("nvshmem." + path) is importlib.import_module("nvshmem_b200." + path), path
     from nvshmem.core.interop.torch import tensor, get_peer_tensor  # noqa: F401
     from nvshmem.bindings import malloc, Team_id  # noqa: F401
+
+
+def test_every_environment_variable_of_the_reference_is_known():
+    """Each NVSHMEM_<NAME> that the reference's option table defines is a row of this library's table (with an effect,
+    or listed as accepted without one), so `nvshmem-info -a` documents what a job script's settings do here."""
+    ref_defs = Path(os.environ.get("BSHMEM_REFERENCE_TREE", str(ROOT.parent / "reference"))) / "src" / "include"
+    if not ref_defs.exists():
+        pytest.skip("the reference tree is not present")
+    ref = set()
+    for p in ref_defs.rglob("*.h"):
+        ref |= set(re.findall(r"NVSHMEMI_ENV_DEF\(([A-Z0-9_]+)", p.read_text(errors="replace")))
+    ref -= {"NAME"}  # the macro's own parameter name in its definition
+    assert len(ref) > 40, len(ref)
+    mine = set(re.findall(r"^  X\(([A-Z0-9_]+)", (ROOT / "csrc" / "src" / "util" / "env.h").read_text(), flags=re.M))
+    # out-of-scope transports have their own variables in the reference (IB / UCX / libfabric tables are separate files)
+    missing = sorted(ref - mine)
+    assert not missing, missing
