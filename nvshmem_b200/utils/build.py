@@ -67,7 +67,9 @@ def sanitizer_env(sanitize: str, log_dir: str | None = None) -> dict[str, str]:
     for s in sanitize.split(","):
         name = {"address": "libasan.so", "undefined": "libubsan.so", "thread": "libtsan.so"}[s]
         libs.append(sp.run(["gcc", f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip())
-    env = {"LD_PRELOAD": ":".join(libs), "BSHMEM_LIB_DIR": str(sanitizer_dirs(sanitize)[0]),
+    # Instrumented processes run several times slower: the bound of the library's waits grows with them, so that a busy
+    # machine shows up as a slow run and not as a peer that "did not arrive".
+    env = {"LD_PRELOAD": ":".join(libs), "BSHMEM_LIB_DIR": str(sanitizer_dirs(sanitize)[0]), "NVSHMEM_WAIT_TIMEOUT_MS": "30000",
            "ASAN_OPTIONS": "detect_leaks=0:abort_on_error=1:protect_shadow_gap=0", "UBSAN_OPTIONS": "halt_on_error=1:print_stacktrace=1",
            "TSAN_OPTIONS": f"halt_on_error=0:exitcode=0:report_signal_unsafe=0:suppressions={ROOT / 'tests' / 'data' / 'tsan.supp'}"
                            + (f":log_path={log_dir}/tsan" if log_dir else "")}
