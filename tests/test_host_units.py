@@ -245,3 +245,39 @@ def test_transport_seam_capabilities_and_plugin_errors(hostlib):
     MAP, LD, ST, ATOM, SAME = 1, 2, 4, 8, 128
     assert caps.value & (MAP | LD | ST | ATOM | SAME) == (MAP | LD | ST | ATOM | SAME)
     assert hostlib.bshmem_test_transport_load(b"no_such_transport") != 0
+
+
+def test_flat_binding_structs_are_views_of_c_memory():
+    """The struct wrappers of nvshmem.bindings: defaults, field access, arrays, wrapping foreign memory."""
+    import ctypes as C
+    import numpy as np
+    import nvshmem.bindings as b
+    u = b.UniqueId(3)
+    assert len(u) == 3 and list(u.version) == [(1 << 16) + 128] * 3 and u.ptr == u._data.ctypes.data
+    with pytest.raises(TypeError):
+        int(u)
+    one = u[1]
+    one.version = 7
+    assert list(u.version) == [(1 << 16) + 128, 7, (1 << 16) + 128] and u[-2].version == 7  # a view, not a copy
+    with pytest.raises(IndexError):
+        u[3]
+    raw = (C.c_char * 128)()
+    w = b.UniqueId.from_ptr(C.addressof(raw))
+    w.version = 0x01020304
+    assert bytes(raw[:4]) == (0x01020304).to_bytes(4, "little")
+    ro = b.UniqueId.from_ptr(C.addressof(raw), readonly=True)
+    with pytest.raises(ValueError):
+        ro.version = 1
+    with pytest.raises(ValueError):
+        b.UniqueId.from_ptr(0)
+    cfg = b.TeamConfig()
+    cfg.num_contexts, cfg.uniqueid = 2, 99
+    assert (cfg.version, cfg.num_contexts, cfg.uniqueid) == ((2 << 16) + 64, 2, 99) and b.TeamConfig() != cfg and b.TeamConfig() == b.TeamConfig()
+    attr = b.InitAttr()
+    args = attr._data["args"][0].view(np.int32)
+    assert attr.mpi_comm == 0 and args[0] == (2 << 16) + 128 and (args[6], args[7], args[8]) == (-1, -1, -1)
+    assert b.Team_id.TEAM_WORLD == 0 and b.Signal_op.SIGNAL_ADD == 10 and b.Status.SUCCESS == 0
+    with pytest.raises(b.NVSHMEMError):
+        b.check_status(3)
+    with pytest.raises(AttributeError):
+        b.no_such_function
